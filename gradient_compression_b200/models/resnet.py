@@ -1,0 +1,90 @@
+"""CIFAR ResNets: 3x3 stem at stride 1, no max-pool, four stages of widths 64/128/256/512 with
+strides 1/2/2/2, 4x4 average pool and a 10-way linear head (reference: models/resnet.py:14-129).
+Attribute names match the reference so ``state_dict`` keys are interchangeable."""
+from __future__ import annotations
+
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .layers import bn, conv, linear
+
+
+def _projection(cin, cout, stride):
+    if stride == 1 and cin == cout:
+        return nn.Sequential()
+    return nn.Sequential(conv(cin, cout, 1, stride=stride), bn(cout))
+
+
+class BasicBlock(nn.Module):
+    expansion = 1
+
+    def __init__(self, in_planes, planes, stride=1):
+        super().__init__()
+        self.conv1, self.bn1 = conv(in_planes, planes, 3, stride, 1), bn(planes)
+        self.conv2, self.bn2 = conv(planes, planes, 3, 1, 1), bn(planes)
+        self.shortcut = _projection(in_planes, planes * self.expansion, stride)
+
+    def forward(self, x):
+        y = F.relu(self.bn1(self.conv1(x)))
+        y = self.bn2(self.conv2(y))
+        return F.relu(y + self.shortcut(x))
+
+
+class Bottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, in_planes, planes, stride=1):
+        super().__init__()
+        self.conv1, self.bn1 = conv(in_planes, planes, 1), bn(planes)
+        self.conv2, self.bn2 = conv(planes, planes, 3, stride, 1), bn(planes)
+        self.conv3, self.bn3 = conv(planes, planes * self.expansion, 1), bn(planes * self.expansion)
+        self.shortcut = _projection(in_planes, planes * self.expansion, stride)
+
+    def forward(self, x):
+        y = F.relu(self.bn1(self.conv1(x)))
+        y = F.relu(self.bn2(self.conv2(y)))
+        y = self.bn3(self.conv3(y))
+        return F.relu(y + self.shortcut(x))
+
+
+class ResNet(nn.Module):
+    def __init__(self, block, num_blocks, num_classes=10):
+        super().__init__()
+        self.in_planes = 64
+        self.conv1, self.bn1 = conv(3, 64, 3, 1, 1), bn(64)
+        for i, (width, depth, stride) in enumerate(zip((64, 128, 256, 512), num_blocks, (1, 2, 2, 2)), start=1):
+            setattr(self, f"layer{i}", self._stage(block, width, depth, stride))
+        self.linear = linear(512 * block.expansion, num_classes)
+
+    def _stage(self, block, planes, depth, stride):
+        blocks = []
+        for s in [stride] + [1] * (depth - 1):
+            blocks.append(block(self.in_planes, planes, s))
+            self.in_planes = planes * block.expansion
+        return nn.Sequential(*blocks)
+
+    def forward(self, x):
+        x = F.relu(self.bn1(self.conv1(x)))
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        x = F.avg_pool2d(x, 4)
+        return self.linear(x.flatten(1))
+
+
+def ResNet18():
+    return ResNet(BasicBlock, [2, 2, 2, 2])
+
+
+def ResNet34():
+    return ResNet(BasicBlock, [3, 4, 6, 3])
+
+
+def ResNet50():
+    return ResNet(Bottleneck, [3, 4, 6, 3])
+
+
+def ResNet101():
+    return ResNet(Bottleneck, [3, 4, 23, 3])
+
+
+def ResNet152():
+    return ResNet(Bottleneck, [3, 8, 36, 3])

@@ -1,0 +1,49 @@
+"""CIFAR VGG family: 3x3 convolutions with bias + BN + ReLU, 2x2 max-pools, a 512 -> 10 linear head
+(reference: models/vgg.py:6-110).  ``features.N`` / ``classifier`` key names match the reference
+(including the parameter-free ``AvgPool2d(1, 1)`` that closes ``features``)."""
+from __future__ import annotations
+
+import torch.nn as nn
+
+from .layers import bn, conv, linear
+
+CFG = {
+    "VGG11": [64, "M", 128, "M", 256, 256, "M", 512, 512, "M", 512, 512, "M"],
+    "VGG13": [64, 64, "M", 128, 128, "M", 256, 256, "M", 512, 512, "M", 512, 512, "M"],
+    "VGG16": [64, 64, "M", 128, 128, "M", 256, 256, 256, "M", 512, 512, 512, "M", 512, 512, 512, "M"],
+    "VGG19": [64, 64, "M", 128, 128, "M", 256, 256, 256, 256, "M", 512, 512, 512, 512, "M", 512, 512, 512, 512, "M"],
+}
+
+
+class VGG(nn.Module):
+    def __init__(self, vgg_name="VGG16"):
+        super().__init__()
+        layers, cin = [], 3
+        for item in CFG[vgg_name]:
+            if item == "M":
+                layers.append(nn.MaxPool2d(kernel_size=2, stride=2))
+            else:
+                layers += [conv(cin, item, 3, padding=1, bias=True), bn(item), nn.ReLU(inplace=True)]
+                cin = item
+        layers.append(nn.AvgPool2d(kernel_size=1, stride=1))
+        self.features = nn.Sequential(*layers)
+        self.classifier = linear(512, 10)
+
+    def forward(self, x):
+        return self.classifier(self.features(x).flatten(1))
+
+
+def VGG11():
+    return VGG("VGG11")
+
+
+def VGG13():
+    return VGG("VGG13")
+
+
+def VGG16():
+    return VGG("VGG16")
+
+
+def VGG19():
+    return VGG("VGG19")

@@ -1,0 +1,133 @@
+"""ctypes bindings to the in-tree native libraries.
+
+The host library is always available (built on first import when missing).  The CUDA library is
+required whenever a CUDA device is visible: ops never fall back to PyTorch on a GPU box, they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .. import build as _build
+
+c_void_p, c_int, c_i64, c_u64, c_u32, c_float = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64,
+                                                 ctypes.c_uint32, ctypes.c_float)
+
+_host = None
+_cuda = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _declare(lib, name, restype, argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+def host():
+    global _host
+    if _host is None:
+        path = _build.host_lib_path()
+        if not os.path.exists(path) or os.environ.get("GCB200_REBUILD"):
+            path = _build.build_host()
+        else:
+            try:
+                path = _build.build_host()  # no-op when the stamp matches the sources
+            except Exception:
+                pass
+        lib = ctypes.CDLL(path)
+        P = c_void_p
+        _declare(lib, "gc_host_abi_version", c_int, [])
+        _declare(lib, "gc_host_philox_u32", None, [c_u64, c_u32, c_u32, c_i64, P])
+        _declare(lib, "gc_host_philox_uniform", None, [c_u64, c_u32, c_u32, c_i64, P])
+        _declare(lib, "gc_host_philox_normal", None, [c_u64, c_u32, c_u32, c_i64, P])
+        _declare(lib, "gc_host_absmax", c_float, [P, c_i64])
+        _declare(lib, "gc_host_quantize_levels", None, [P, c_i64, c_float, c_int, c_int, c_u64, c_u32, c_u32, P])
+        _declare(lib, "gc_host_dequantize_levels", None, [P, c_i64, c_float, c_int, c_int, P])
+        _declare(lib, "gc_host_pack", None, [P, c_i64, c_int, P, P])
+        _declare(lib, "gc_host_unpack", None, [P, P, c_i64, c_int, P])
+        _declare(lib, "gc_host_plane_pack", None, [P, c_i64, P])
+        _declare(lib, "gc_host_plane_unpack", None, [P, c_i64, P])
+        _declare(lib, "gc_host_varpack", c_i64, [P, c_i64, P])
+        _declare(lib, "gc_host_varunpack", c_i64, [P, c_i64, P])
+        _declare(lib, "gc_host_bytepack", None, [P, c_i64, P])
+        _declare(lib, "gc_host_byteunpack", None, [P, c_i64, P])
+        _declare(lib, "gc_host_randk_indices", None, [c_u64, c_u32, c_i64, c_i64, c_i64, P])
+        _declare(lib, "gc_host_gram_schmidt", None, [P, c_i64, c_int, c_float])
+        _declare(lib, "gc_host_topk_abs", None, [P, c_i64, c_i64, P])
+        _declare(lib, "gc_host_sgd_step", None, [P, P, P, c_i64, c_float, c_float, c_float, c_int])
+        _declare(lib, "gc_host_elias_encode", c_i64, [P, c_i64, c_float, P, c_i64])
+        _declare(lib, "gc_host_elias_decode", c_i64, [P, c_i64, P, P, c_i64])
+        _host = lib
+    return _host
+
+
+def cuda_available():
+    return torch.cuda.is_available()
+
+
+def cuda():
+    """The CUDA kernel library.  Raises when it cannot be loaded: there is no eager fallback."""
+    global _cuda
+    if _cuda is None:
+        path = _build.cuda_lib_path()
+        try:
+            path = _build.build_cuda()  # no-op when up to date
+        except Exception as exc:
+            if not os.path.exists(path):
+                raise NativeError(f"libgcb200_cuda.so is missing and could not be built: {exc}") from exc
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:
+            raise NativeError(f"cannot load {path}: {exc}") from exc
+        P = c_void_p
+        _declare(lib, "gc_cuda_abi_version", c_int, [])
+        _declare(lib, "gc_cuda_sm_count", c_int, [])
+        _declare(lib, "gc_cuda_philox_fill", c_int, [c_int, c_u64, c_u32, c_u32, c_i64, P, P])
+        _declare(lib, "gc_cuda_absmax_scratch_bytes", c_i64, [])
+        _declare(lib, "gc_cuda_absmax", c_int, [P, c_i64, P, P, P])
+        _declare(lib, "gc_cuda_quantize_levels", c_int, [P, c_i64, P, c_int, c_int, c_u64, c_u32, c_u32, P, c_int, P])
+        _declare(lib, "gc_cuda_dequantize_levels", c_int, [P, c_int, c_i64, P, c_int, c_int, P, P])
+        _declare(lib, "gc_cuda_qsgd_pack", c_int, [P, c_i64, P, c_int, c_u64, c_u32, c_u32, P, P, P])
+        _declare(lib, "gc_cuda_qsgd_unpack_dequant", c_int, [P, P, c_i64, P, c_int, c_int, P, P])
+        _declare(lib, "gc_cuda_pack_levels", c_int, [P, c_i64, c_int, P, P, P])
+        _declare(lib, "gc_cuda_unpack_levels", c_int, [P, P, c_i64, c_int, P, P])
+        _declare(lib, "gc_cuda_randk_gather", c_int, [P, c_i64, c_u64, c_u32, c_i64, c_i64, P, P, P])
+        _declare(lib, "gc_cuda_randk_scatter", c_int, [P, c_i64, c_u64, c_u32, c_i64, c_i64, P, c_float, P])
+        _declare(lib, "gc_cuda_scale", c_int, [P, c_i64, c_float, P])
+        _declare(lib, "gc_cuda_sgd_step", c_int, [P, P, P, c_i64, P, c_int, P])
+        _cuda = lib
+    return _cuda
+
+
+_launches = 0
+
+
+def count_launch(n=1):
+    """Bookkeeping of how many of this library's kernels were launched (read by the benchmark)."""
+    global _launches
+    _launches += n
+
+
+def launches():
+    return _launches
+
+
+def check(err, what):
+    if err != 0:
+        raise NativeError(f"{what}: CUDA error {err}")
+    count_launch()
+
+
+def stream_ptr():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t):
+    return t.data_ptr() if t is not None else None

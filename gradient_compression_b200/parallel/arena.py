@@ -1,0 +1,117 @@
+"""Flat parameter / gradient / momentum arenas.
+
+All parameters of a model are re-pointed into one contiguous fp32 buffer, and so are their ``.grad``
+tensors and the optimiser's momentum.  Consequences: the reducer sees the gradient as one vector with
+no ``torch.cat`` (reference: reducer.py:62) and no per-tensor "accumulate" copy (trainer.py:188-190);
+the optimiser is ONE kernel over N elements (``ops.sgd_step``) instead of a per-tensor loop; zeroing
+gradients is one memset.  Each tensor starts on a 16-byte boundary (4 floats) so vector loads apply
+to per-tensor views as well.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+
+class FlatArena:
+    def __init__(self, params, align=4, with_momentum=True):
+        self.params = [p for p in params]
+        dev = self.params[0].device
+        self.offsets, off = [], 0
+        for p in self.params:
+            assert p.dtype == torch.float32, "the arena holds fp32 parameters"
+            self.offsets.append(off)
+            off += (p.numel() + align - 1) // align * align
+        self.total = off
+        self.numel = sum(p.numel() for p in self.params)
+        self.flat_params = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.flat_grads = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.flat_momentum = torch.zeros(self.total, dtype=torch.float32, device=dev) if with_momentum else None
+        self.grad_views, self.param_views = [], []
+        with torch.no_grad():
+            for p, o in zip(self.params, self.offsets):
+                pv = self.flat_params[o: o + p.numel()].view(p.shape)
+                pv.copy_(p.data)
+                p.data = pv
+                gv = self.flat_grads[o: o + p.numel()].view(p.shape)
+                p.grad = gv
+                self.param_views.append(pv)
+                self.grad_views.append(gv)
+        self.dense = self.total == self.numel   # no padding holes: the list aliases the flat buffer exactly
+
+    def zero_grad(self):
+        self.flat_grads.zero_()
+        for p, gv in zip(self.params, self.grad_views):
+            if p.grad is not gv:           # someone set .grad to None / a new tensor: re-attach
+                p.grad = gv
+
+    def grads(self):
+        return self.grad_views
+
+    def sgd_step(self, hyper=None, lr=None, momentum=0.9, weight_decay=5e-4, nesterov=True):
+        ops.sgd_step(self.flat_params, self.flat_grads, self.flat_momentum, lr=lr, momentum=momentum,
+                     weight_decay=weight_decay, nesterov=nesterov, hyper=hyper)
+
+    def state_dict(self):
+        return {"momentum": self.flat_momentum.clone() if self.flat_momentum is not None else None}
+
+    def load_state_dict(self, sd):
+        if sd.get("momentum") is not None and self.flat_momentum is not None:
+            self.flat_momentum.copy_(sd["momentum"])
+
+
+class FlatSGD:
+    """SGD(momentum, Nesterov, weight decay) over a ``FlatArena`` with a scheduler-friendly ``lr``.
+
+    Mirrors what the reference configures with ``optim.SGD(..., momentum=0.9, weight_decay=5e-4,
+    nesterov=True)`` + ``CosineAnnealingLR`` (trainer.py:163-166), as one fused kernel.  The
+    hyper-parameters live in a 3-float device tensor, so a captured CUDA graph sees new values."""
+
+    def __init__(self, arena, lr=0.1, momentum=0.9, weight_decay=5e-4, nesterov=True):
+        self.arena = arena
+        self.base_lr = lr
+        self.lr, self.momentum, self.weight_decay, self.nesterov = lr, momentum, weight_decay, nesterov
+        self.hyper = torch.tensor([lr, momentum, weight_decay], dtype=torch.float32, device=arena.flat_params.device)
+
+    def set_lr(self, lr):
+        self.lr = float(lr)
+        self.hyper[0] = self.lr
+
+    def step(self):
+        self.arena.sgd_step(hyper=self.hyper, nesterov=self.nesterov)
+
+    def zero_grad(self):
+        self.arena.zero_grad()
+
+    def state_dict(self):
+        return {"lr": self.lr, "base_lr": self.base_lr, "momentum_buf": self.arena.flat_momentum.clone()}
+
+    def load_state_dict(self, sd):
+        self.base_lr = sd["base_lr"]
+        self.set_lr(sd["lr"])
+        self.arena.flat_momentum.copy_(sd["momentum_buf"])
+
+
+class CosineSchedule:
+    """eta_t = eta_min + (base - eta_min) * (1 + cos(pi * t / T_max)) / 2, stepped once per epoch
+    (``CosineAnnealingLR(T_max=num_epochs, eta_min=0)``, trainer.py:166,198)."""
+
+    def __init__(self, optimizer, T_max, eta_min=0.0):
+        self.opt, self.T_max, self.eta_min, self.epoch = optimizer, T_max, eta_min, 0
+
+    def get_last_lr(self):
+        return [self.opt.lr]
+
+    def step(self):
+        import math
+
+        self.epoch += 1
+        lr = self.eta_min + (self.opt.base_lr - self.eta_min) * (1 + math.cos(math.pi * self.epoch / self.T_max)) / 2
+        self.opt.set_lr(lr)
+
+    def state_dict(self):
+        return {"epoch": self.epoch}
+
+    def load_state_dict(self, sd):
+        self.epoch = int(sd["epoch"])
