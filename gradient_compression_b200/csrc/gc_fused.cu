@@ -1,0 +1,845 @@
+// Fused compress + collective kernels over the symmetric arena (one persistent cooperative launch
+// per reducer step and rank):
+//   fused_allreduce   fp32 two-shot all-reduce (AllReduce-SGD)
+//   fused_qsgd        QSGD-MaxNorm: abs-max -> max exchange -> stochastic quantise + pack ->
+//                     owner-pull packed reduce-scatter with int32 accumulators -> push of narrow
+//                     integer sums to every peer -> dequantise into the fp32 gradient
+//   fused_twoscale    two-scale variant: adds the 1-bit "fits the low scale" agreement round
+//   fused_randk       shared-index gather -> (two-scale) quantised one-shot reduce -> scatter
+//   fused_small_sum   one-shot fp32 sum of short vectors (PowerSGD P / Q / rank-1 tensors)
+// Peers are reached with plain loads / stores through their mapped arenas; no TMA is involved.
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "gc_comm.cuh"
+#include "gc_perm.h"
+
+using namespace gc;
+
+namespace {
+
+constexpr int THREADS = 512;
+enum Phase : int { PH_READY = 0, PH_DONE = 1, PH_MASK = 2, PH_STAGE = 3, PH_AUX = 4 };
+
+struct Common {
+  int64_t n;
+  int world;
+  int step_from_device;   // 1: Philox step = step + launches so far on this rank (for CUDA-graph replay)
+  unsigned long long timeout_ns;
+  uint32_t seed_lo, seed_hi, step;
+};
+
+__device__ __forceinline__ RngKey rng_key(const Common& c, uint32_t step, int rank, uint32_t purpose) {
+  RngKey k;
+  k.k0 = c.seed_lo;
+  k.k1 = c.seed_hi;
+  k.step = step;
+  k.stream = ((uint32_t)rank << 8) | purpose;
+  return k;
+}
+
+struct Ctx {   // per-block view of "which virtual rank am I"
+  const RankView* v;
+  ArenaHeader* hdr;
+  int bid, nblocks;
+  int64_t warp, nwarps;
+  int lane;
+};
+
+__device__ __forceinline__ Ctx make_ctx(const LaunchViews& lv) {
+  Ctx c;
+  int vr = blockIdx.x / lv.blocks_per_rank;
+  c.v = &lv.r[vr];
+  c.hdr = reinterpret_cast<ArenaHeader*>(c.v->arena[c.v->rank]);
+  c.bid = blockIdx.x % lv.blocks_per_rank;
+  c.nblocks = lv.blocks_per_rank;
+  c.lane = threadIdx.x & 31;
+  c.warp = (int64_t)c.bid * (THREADS / 32) + (threadIdx.x >> 5);
+  c.nwarps = (int64_t)c.nblocks * (THREADS / 32);
+  return c;
+}
+
+__device__ __forceinline__ float quad_absmax(float4 a) {
+  return fmaxf(fmaxf(abs_for_max(a.x), abs_for_max(a.y)), fmaxf(abs_for_max(a.z), abs_for_max(a.w)));
+}
+
+__device__ __forceinline__ float local_absmax(const Ctx& c, const float* __restrict__ x, int64_t n, bool al) {
+  float m = 0.0f;
+  int64_t nq = (n + 3) / 4;
+  int64_t stride = (int64_t)c.nblocks * THREADS;
+  int64_t q = (int64_t)c.bid * THREADS + threadIdx.x;
+  for (; q + stride < nq; q += 2 * stride) {
+    float4 a = load_quad(x, q * 4, n, al);
+    float4 b = load_quad(x, (q + stride) * 4, n, al);
+    m = fmaxf(m, fmaxf(quad_absmax(a), quad_absmax(b)));
+  }
+  if (q < nq) m = fmaxf(m, quad_absmax(load_quad(x, q * 4, n, al)));
+  return m;
+}
+
+template <int SUMB>
+__device__ __forceinline__ void store_row_sums(uint8_t* __restrict__ sums, int64_t row, int lane, const int (&a)[4]) {
+  if (SUMB == 1) {
+    uint32_t v = (uint32_t)(a[0] & 0xff) | ((uint32_t)(a[1] & 0xff) << 8) | ((uint32_t)(a[2] & 0xff) << 16) |
+                 ((uint32_t)(a[3] & 0xff) << 24);
+    reinterpret_cast<uint32_t*>(sums)[row * 32 + lane] = v;
+  } else if (SUMB == 2) {
+    uint2 v;
+    v.x = (uint32_t)(a[0] & 0xffff) | ((uint32_t)(a[1] & 0xffff) << 16);
+    v.y = (uint32_t)(a[2] & 0xffff) | ((uint32_t)(a[3] & 0xffff) << 16);
+    reinterpret_cast<uint2*>(sums)[row * 32 + lane] = v;
+  } else {
+    reinterpret_cast<int4*>(sums)[row * 32 + lane] = make_int4(a[0], a[1], a[2], a[3]);
+  }
+}
+template <int SUMB>
+__device__ __forceinline__ void load_row_sums(const uint8_t* __restrict__ sums, int64_t row, int lane, int (&a)[4]) {
+  if (SUMB == 1) {
+    uint32_t v = reinterpret_cast<const uint32_t*>(sums)[row * 32 + lane];
+    a[0] = (int8_t)(v & 0xff); a[1] = (int8_t)((v >> 8) & 0xff); a[2] = (int8_t)((v >> 16) & 0xff); a[3] = (int8_t)(v >> 24);
+  } else if (SUMB == 2) {
+    uint2 v = reinterpret_cast<const uint2*>(sums)[row * 32 + lane];
+    a[0] = (int16_t)(v.x & 0xffff); a[1] = (int16_t)(v.x >> 16); a[2] = (int16_t)(v.y & 0xffff); a[3] = (int16_t)(v.y >> 16);
+  } else {
+    int4 v = reinterpret_cast<const int4*>(sums)[row * 32 + lane];
+    a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ QSGD-MaxNorm
+struct QsgdParams {
+  Common c;
+  int s;                  // 2^b - 1
+  int64_t off_mags, off_signs, off_sums;   // byte offsets inside every arena
+  int64_t chunk_rows;     // rows owned by each rank in the reduce-scatter
+};
+
+// Owner-pull reduce of the rows this rank owns, then push of the integer sums to every rank.
+template <int MW, int SUMB>
+__device__ __forceinline__ void reduce_scatter_rows(const Ctx& c, int world, int64_t rows, int64_t chunk_rows,
+                                                    int64_t off_mags, int64_t off_signs, int64_t off_sums) {
+  const RankView& v = *c.v;
+  int64_t r0 = (int64_t)v.rank * chunk_rows;
+  int64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
+  for (int64_t row = r0 + c.warp; row < r1; row += c.nwarps) {
+    int m[MAXW][4];
+    bool sg[MAXW][4];
+#pragma unroll
+    for (int src = 0; src < MAXW; ++src) {
+      if (src < world) {
+        load_row_mags<MW>(v.arena[src] + off_mags, row, c.lane, m[src]);
+        load_row_plane(reinterpret_cast<const uint32_t*>(v.arena[src] + off_signs), row, c.lane, sg[src]);
+      }
+    }
+    int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int src = 0; src < MAXW; ++src) {
+      if (src < world) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] += sg[src][j] ? -m[src][j] : m[src][j];
+      }
+    }
+#pragma unroll
+    for (int dst = 0; dst < MAXW; ++dst)
+      if (dst < world) store_row_sums<SUMB>(v.arena[dst] + off_sums, row, c.lane, acc);
+  }
+}
+
+template <int MW, int SUMB>
+__global__ void __launch_bounds__(THREADS) qsgd_fused_kernel(LaunchViews lv, QsgdParams p) {
+  __shared__ float smem[32];
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t rows = (n + 127) / 128;
+
+  // P0: global max-norm
+  float m = rank_max(w, local_absmax(c, v.in, n, al_in), c.bid, c.nblocks, smem, 0x20);
+  commit_epoch(c.hdr, epoch, c.bid);
+  float norm = (world > 1) ? exchange_max(w, v, world, epoch, m, c.bid == 0, smem) : m;
+  float scale = (norm > 0.0f) ? (float)p.s / norm : 0.0f;
+  float dq = dequant_scale(norm, p.s, world);
+  RngKey key = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND);
+
+  if (world == 1) {
+    // single worker: quantise and dequantise in registers, one pass
+    for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+      int64_t e0 = row * 128 + c.lane * 4;
+      float4 x = load_quad(v.in, e0, n, al_in);
+      U4 r = philox_block(key, (uint64_t)(e0 >> 2));
+      float4 y;
+      y.x = mul_rn(dq, (float)quantize_level(x.x, scale, p.s, r.x));
+      y.y = mul_rn(dq, (float)quantize_level(x.y, scale, p.s, r.y));
+      y.z = mul_rn(dq, (float)quantize_level(x.z, scale, p.s, r.z));
+      y.w = mul_rn(dq, (float)quantize_level(x.w, scale, p.s, r.w));
+      store_quad(v.out, e0, n, al_out, y);
+    }
+    return;
+  }
+
+  // P1: quantise + pack into this rank's arena
+  uint8_t* my = v.arena[v.rank];
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int64_t e0 = row * 128 + c.lane * 4;
+    float4 x = load_quad(v.in, e0, n, al_in);
+    U4 r = philox_block(key, (uint64_t)(e0 >> 2));
+    int q0 = quantize_level(x.x, scale, p.s, r.x), q1 = quantize_level(x.y, scale, p.s, r.y);
+    int q2 = quantize_level(x.z, scale, p.s, r.z), q3 = quantize_level(x.w, scale, p.s, r.w);
+    int mg[4] = {abs(q0), abs(q1), abs(q2), abs(q3)};
+    bool sg[4] = {q0 < 0, q1 < 0, q2 < 0, q3 < 0};
+    store_row_mags<MW>(my + p.off_mags, row, c.lane, mg);
+    store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_signs), row, c.lane, sg);
+  }
+  grid_barrier(w, c.nblocks, 0x21);
+  if (c.bid == 0) signal_all(v, world, PH_READY, epoch);
+  wait_all(w, world, PH_READY, epoch);
+
+  // P2: packed reduce-scatter (pull) + push of the sums
+  reduce_scatter_rows<MW, SUMB>(c, world, rows, p.chunk_rows, p.off_mags, p.off_signs, p.off_sums);
+  grid_barrier(w, c.nblocks, 0x22);
+  if (c.bid == 0) signal_all(v, world, PH_DONE, epoch);
+  wait_all(w, world, PH_DONE, epoch);
+
+  // P3: dequantise the summed levels into the fp32 gradient (1/W folded into dq)
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int a[4];
+    load_row_sums<SUMB>(my + p.off_sums, row, c.lane, a);
+    float4 y = make_float4(mul_rn(dq, (float)a[0]), mul_rn(dq, (float)a[1]), mul_rn(dq, (float)a[2]),
+                           mul_rn(dq, (float)a[3]));
+    store_quad(v.out, row * 128 + c.lane * 4, n, al_out, y);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ two-scale
+struct TwoScaleParams {
+  Common c;
+  int s_lo, s_hi;
+  int64_t off_mags, off_signs, off_sums, off_mask_local, off_mask_final;
+  int64_t chunk_rows;
+};
+
+template <int MW, int SUMB>
+__global__ void __launch_bounds__(THREADS) twoscale_fused_kernel(LaunchViews lv, TwoScaleParams p) {
+  __shared__ float smem[32];
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t rows = (n + 127) / 128;
+  uint8_t* my = v.arena[v.rank];
+
+  float m = rank_max(w, local_absmax(c, v.in, n, al_in), c.bid, c.nblocks, smem, 0x30);
+  commit_epoch(c.hdr, epoch, c.bid);
+  float norm = (world > 1) ? exchange_max(w, v, world, epoch, m, c.bid == 0, smem) : m;
+  float sc_lo = (norm > 0.0f) ? (float)p.s_lo / norm : 0.0f;
+  float sc_hi = (norm > 0.0f) ? (float)p.s_hi / norm : 0.0f;
+  float dq_lo = dequant_scale(norm, p.s_lo, world), dq_hi = dequant_scale(norm, p.s_hi, world);
+  RngKey k_lo = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND), k_hi = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND_HI);
+
+  // P1a: which elements' rounded high-scale level still fits the low range (this rank's vote)
+  if (world > 1) {
+    for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+      int64_t e0 = row * 128 + c.lane * 4;
+      float4 x = load_quad(v.in, e0, n, al_in);
+      U4 r = philox_block(k_hi, (uint64_t)(e0 >> 2));
+      bool fit[4] = {abs(quantize_level(x.x, sc_hi, p.s_hi, r.x)) <= p.s_lo,
+                     abs(quantize_level(x.y, sc_hi, p.s_hi, r.y)) <= p.s_lo,
+                     abs(quantize_level(x.z, sc_hi, p.s_hi, r.z)) <= p.s_lo,
+                     abs(quantize_level(x.w, sc_hi, p.s_hi, r.w)) <= p.s_lo};
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_mask_local), row, c.lane, fit);
+    }
+    grid_barrier(w, c.nblocks, 0x31);
+    if (c.bid == 0) signal_all(v, world, PH_MASK, epoch);
+    wait_all(w, world, PH_MASK, epoch);
+  }
+
+  // P1b: AND of all votes (one-shot read of every peer's bit plane), pick the scale, quantise
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int64_t e0 = row * 128 + c.lane * 4;
+    float4 x = load_quad(v.in, e0, n, al_in);
+    U4 rh = philox_block(k_hi, (uint64_t)(e0 >> 2));
+    U4 rl = philox_block(k_lo, (uint64_t)(e0 >> 2));
+    int qh[4] = {quantize_level(x.x, sc_hi, p.s_hi, rh.x), quantize_level(x.y, sc_hi, p.s_hi, rh.y),
+                 quantize_level(x.z, sc_hi, p.s_hi, rh.z), quantize_level(x.w, sc_hi, p.s_hi, rh.w)};
+    int ql[4] = {quantize_level(x.x, sc_lo, p.s_lo, rl.x), quantize_level(x.y, sc_lo, p.s_lo, rl.y),
+                 quantize_level(x.z, sc_lo, p.s_lo, rl.z), quantize_level(x.w, sc_lo, p.s_lo, rl.w)};
+    bool use_hi[4];
+    if (world > 1) {
+      uint4 andw = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+#pragma unroll
+      for (int src = 0; src < MAXW; ++src) {
+        if (src < world) {
+          uint4 t = reinterpret_cast<const uint4*>(v.arena[src] + p.off_mask_local)[row];
+          andw.x &= t.x; andw.y &= t.y; andw.z &= t.z; andw.w &= t.w;
+        }
+      }
+      use_hi[0] = (andw.x >> c.lane) & 1u; use_hi[1] = (andw.y >> c.lane) & 1u;
+      use_hi[2] = (andw.z >> c.lane) & 1u; use_hi[3] = (andw.w >> c.lane) & 1u;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) use_hi[j] = abs(qh[j]) <= p.s_lo;
+    }
+    int q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = use_hi[j] ? qh[j] : ql[j];
+    if (world == 1) {
+      float4 y;
+      y.x = mul_rn(use_hi[0] ? dq_hi : dq_lo, (float)q[0]);
+      y.y = mul_rn(use_hi[1] ? dq_hi : dq_lo, (float)q[1]);
+      y.z = mul_rn(use_hi[2] ? dq_hi : dq_lo, (float)q[2]);
+      y.w = mul_rn(use_hi[3] ? dq_hi : dq_lo, (float)q[3]);
+      store_quad(v.out, e0, n, al_out, y);
+    } else {
+      int mg[4] = {abs(q[0]), abs(q[1]), abs(q[2]), abs(q[3])};
+      bool sg[4] = {q[0] < 0, q[1] < 0, q[2] < 0, q[3] < 0};
+      store_row_mags<MW>(my + p.off_mags, row, c.lane, mg);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_signs), row, c.lane, sg);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_mask_final), row, c.lane, use_hi);
+    }
+  }
+  if (world == 1) return;
+  grid_barrier(w, c.nblocks, 0x32);
+  if (c.bid == 0) signal_all(v, world, PH_READY, epoch);
+  wait_all(w, world, PH_READY, epoch);
+
+  reduce_scatter_rows<MW, SUMB>(c, world, rows, p.chunk_rows, p.off_mags, p.off_signs, p.off_sums);
+  grid_barrier(w, c.nblocks, 0x33);
+  if (c.bid == 0) signal_all(v, world, PH_DONE, epoch);
+  wait_all(w, world, PH_DONE, epoch);
+
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int a[4];
+    bool hi[4];
+    load_row_sums<SUMB>(my + p.off_sums, row, c.lane, a);
+    load_row_plane(reinterpret_cast<const uint32_t*>(my + p.off_mask_final), row, c.lane, hi);
+    float4 y = make_float4(mul_rn(hi[0] ? dq_hi : dq_lo, (float)a[0]), mul_rn(hi[1] ? dq_hi : dq_lo, (float)a[1]),
+                           mul_rn(hi[2] ? dq_hi : dq_lo, (float)a[2]), mul_rn(hi[3] ? dq_hi : dq_lo, (float)a[3]));
+    store_quad(v.out, row * 128 + c.lane * 4, n, al_out, y);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ fp32 all-reduce
+struct AllreduceParams {
+  Common c;
+  int64_t off_stage, off_result;
+  int64_t chunk_quads;
+  float alpha;   // 1 / W
+};
+
+__global__ void __launch_bounds__(THREADS) allreduce_fused_kernel(LaunchViews lv, AllreduceParams p) {
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t nq = (n + 3) / 4;
+  const int64_t stride = (int64_t)c.nblocks * THREADS;
+  const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
+  if (world == 1) {
+    if (v.in != v.out)
+      for (int64_t q = tid; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, load_quad(v.in, q * 4, n, al_in));
+    return;
+  }
+  float4* stage = reinterpret_cast<float4*>(v.arena[v.rank] + p.off_stage);
+  for (int64_t q = tid; q < nq; q += stride) stage[q] = load_quad(v.in, q * 4, n, al_in);
+  grid_barrier(w, c.nblocks, 0x40);
+  commit_epoch(c.hdr, epoch, c.bid);
+  if (c.bid == 0) signal_all(v, world, PH_STAGE, epoch);
+  wait_all(w, world, PH_STAGE, epoch);
+
+  int64_t q0 = (int64_t)v.rank * p.chunk_quads;
+  int64_t q1 = q0 + p.chunk_quads < nq ? q0 + p.chunk_quads : nq;
+  for (int64_t q = q0 + tid; q < q1; q += stride) {
+    float4 part[MAXW];
+#pragma unroll
+    for (int src = 0; src < MAXW; ++src)
+      if (src < world) part[src] = reinterpret_cast<const float4*>(v.arena[src] + p.off_stage)[q];
+    float4 acc = part[0];
+#pragma unroll
+    for (int src = 1; src < MAXW; ++src)
+      if (src < world) { acc.x += part[src].x; acc.y += part[src].y; acc.z += part[src].z; acc.w += part[src].w; }
+    acc.x *= p.alpha; acc.y *= p.alpha; acc.z *= p.alpha; acc.w *= p.alpha;
+#pragma unroll
+    for (int dst = 0; dst < MAXW; ++dst)
+      if (dst < world) reinterpret_cast<float4*>(v.arena[dst] + p.off_result)[q] = acc;
+  }
+  grid_barrier(w, c.nblocks, 0x41);
+  if (c.bid == 0) signal_all(v, world, PH_DONE, epoch);
+  wait_all(w, world, PH_DONE, epoch);
+
+  const float4* res = reinterpret_cast<const float4*>(v.arena[v.rank] + p.off_result);
+  for (int64_t q = tid; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, res[q]);
+}
+
+// ------------------------------------------------------------------------------------------ small one-shot fp32 sum
+struct SmallSumParams {
+  Common c;
+  int64_t off_buf;   // double-buffered by epoch parity: off_buf + parity * stride_bytes
+  int64_t stride_bytes;
+  float alpha;
+};
+
+__global__ void __launch_bounds__(THREADS) small_sum_kernel(LaunchViews lv, SmallSumParams p) {
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const int64_t stride = (int64_t)c.nblocks * THREADS;
+  const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
+  if (world == 1) {
+    for (int64_t i = tid; i < n; i += stride) v.out[i] = v.in[i] * p.alpha;
+    return;
+  }
+  int64_t off = p.off_buf + (int64_t)(epoch & 1) * p.stride_bytes;
+  float* mine = reinterpret_cast<float*>(v.arena[v.rank] + off);
+  for (int64_t i = tid; i < n; i += stride) mine[i] = v.in[i];
+  grid_barrier(w, c.nblocks, 0x50);
+  commit_epoch(c.hdr, epoch, c.bid);
+  if (c.bid == 0) signal_all(v, world, PH_AUX, epoch);
+  wait_all(w, world, PH_AUX, epoch);
+  for (int64_t i = tid; i < n; i += stride) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int src = 0; src < MAXW; ++src)
+      if (src < world) acc += reinterpret_cast<const float*>(v.arena[src] + off)[i];
+    v.out[i] = acc * p.alpha;
+  }
+}
+
+// ------------------------------------------------------------------------------------------ Rand-K
+struct RandkParams {
+  Common c;
+  PermKey perm;
+  int64_t start, k;
+  int s_lo, s_hi;          // s_hi == 0: single scale
+  int zero_unselected;     // 0: unselected coordinates become in / W ; 1: zero
+  int64_t off_vals, off_levels, off_mask;   // scratch regions (levels / mask double-buffered by parity)
+  int64_t stride_bytes;
+};
+
+__global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, RandkParams p) {
+  __shared__ float smem[32];
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n, k = p.k;
+  const int world = p.c.world;
+  const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t stride = (int64_t)c.nblocks * THREADS;
+  const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
+  uint8_t* my = v.arena[v.rank];
+  float* vals = reinterpret_cast<float*>(my + p.off_vals);
+  const int par = epoch & 1;
+  int32_t* levels = reinterpret_cast<int32_t*>(my + p.off_levels + par * p.stride_bytes);
+  uint8_t* mask = my + p.off_mask + par * p.stride_bytes;
+
+  // gather the K selected coordinates first (the dense pass below may overwrite them in place)
+  float m = 0.0f;
+  for (int64_t i = tid; i < k; i += stride) {
+    float x = v.in[perm_eval(p.perm, (uint64_t)(p.start + i))];
+    vals[i] = x;
+    m = fmaxf(m, abs_for_max(x));
+  }
+  m = rank_max(w, m, c.bid, c.nblocks, smem, 0x60);   // grid barrier inside: every gather is done
+  commit_epoch(c.hdr, epoch, c.bid);
+  // dense pass: what the unselected coordinates become
+  {
+    float alpha = p.zero_unselected ? 0.0f : 1.0f / (float)world;
+    if (!(alpha == 1.0f && v.in == v.out)) {
+      int64_t nq = (n + 3) / 4;
+      for (int64_t q = tid; q < nq; q += stride) {
+        float4 x = load_quad(v.in, q * 4, n, al_in);
+        x.x *= alpha; x.y *= alpha; x.z *= alpha; x.w *= alpha;
+        store_quad(v.out, q * 4, n, al_out, x);
+      }
+    }
+  }
+  float norm = (world > 1) ? exchange_max(w, v, world, epoch, m, c.bid == 0, smem) : m;
+  const bool two = p.s_hi > 0;
+  float sc_lo = (norm > 0.0f) ? (float)p.s_lo / norm : 0.0f;
+  float sc_hi = (norm > 0.0f && two) ? (float)p.s_hi / norm : 0.0f;
+  float dq_lo = dequant_scale(norm, p.s_lo, world), dq_hi = two ? dequant_scale(norm, p.s_hi, world) : 0.0f;
+  RngKey k_lo = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND), k_hi = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND_HI);
+
+  auto word_of = [](const U4& r, int j) { return j == 0 ? r.x : j == 1 ? r.y : j == 2 ? r.z : r.w; };
+
+  if (two && world > 1) {
+    for (int64_t i = tid; i < k; i += stride) {
+      U4 rh = philox_block(k_hi, (uint64_t)(i >> 2));
+      int qh = quantize_level(vals[i], sc_hi, p.s_hi, word_of(rh, (int)(i & 3)));
+      mask[i] = abs(qh) <= p.s_lo ? 1 : 0;
+    }
+    grid_barrier(w, c.nblocks, 0x61);
+    if (c.bid == 0) signal_all(v, world, PH_MASK, epoch);
+    wait_all(w, world, PH_MASK, epoch);
+  }
+  for (int64_t i = tid; i < k; i += stride) {
+    float x = vals[i];
+    U4 rl = philox_block(k_lo, (uint64_t)(i >> 2));
+    int q = quantize_level(x, sc_lo, p.s_lo, word_of(rl, (int)(i & 3)));
+    bool hi = false;
+    if (two) {
+      U4 rh = philox_block(k_hi, (uint64_t)(i >> 2));
+      int qh = quantize_level(x, sc_hi, p.s_hi, word_of(rh, (int)(i & 3)));
+      hi = abs(qh) <= p.s_lo;
+      if (world > 1) {
+#pragma unroll
+        for (int src = 0; src < MAXW; ++src)
+          if (src < world) hi = hi && (v.arena[src] + p.off_mask + par * p.stride_bytes)[i] != 0;
+      }
+      if (hi) q = qh;
+    }
+    levels[i] = q;
+    vals[i] = hi ? 1.0f : 0.0f;   // the gathered value is consumed; keep the agreed scale flag in its place
+  }
+  if (world > 1) {
+    grid_barrier(w, c.nblocks, 0x62);
+    if (c.bid == 0) signal_all(v, world, PH_READY, epoch);
+    wait_all(w, world, PH_READY, epoch);
+  } else {
+    grid_barrier(w, c.nblocks, 0x62);
+  }
+  for (int64_t i = tid; i < k; i += stride) {
+    int acc = 0;
+#pragma unroll
+    for (int src = 0; src < MAXW; ++src)
+      if (src < world) acc += reinterpret_cast<const int32_t*>(v.arena[src] + p.off_levels + par * p.stride_bytes)[i];
+    bool hi = two && vals[i] != 0.0f;
+    v.out[perm_eval(p.perm, (uint64_t)(p.start + i))] = mul_rn(hi ? dq_hi : dq_lo, (float)acc);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+struct CommCtx {
+  int world, rank, device;
+  int64_t bytes;
+  uint8_t* local;
+  uint8_t* peers[MAXW];
+  bool ipc_opened[MAXW];
+  int step_from_device;
+  int sm_count;
+};
+
+int max_coresident(const void* kernel, int sm_count) {
+  int per_sm = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, 0);
+  if (per_sm < 1) per_sm = 1;
+  return per_sm * sm_count;
+}
+
+int fill_views(CommCtx** ctxs, int n_virtual, const float* const* ins, float* const* outs, int coresident,
+               int max_blocks, LaunchViews* lv) {
+  if (n_virtual < 1 || n_virtual > MAXW) return -1;
+  int world = ctxs[0]->world;
+  int total = coresident;
+  if (max_blocks > 0 && max_blocks * n_virtual < total) total = max_blocks * n_virtual;
+  int per = total / n_virtual;
+  if (per > MAX_PARTIALS / 2) per = MAX_PARTIALS / 2;
+  if (per < 1) return -2;
+  lv->n_virtual = n_virtual;
+  lv->blocks_per_rank = per;
+  for (int i = 0; i < n_virtual; ++i) {
+    RankView& r = lv->r[i];
+    for (int p = 0; p < MAXW; ++p) r.arena[p] = p < world ? ctxs[i]->peers[p] : nullptr;
+    r.in = ins[i];
+    r.out = outs[i];
+    r.rank = ctxs[i]->rank;
+    r.pad = 0;
+    for (int p = 0; p < world; ++p)
+      if (r.arena[p] == nullptr) return -3;
+  }
+  return 0;
+}
+
+template <typename P>
+int coop_launch(const void* kernel, const LaunchViews& lv, const P& params, cudaStream_t st) {
+  void* args[2] = {(void*)&lv, (void*)&params};
+  dim3 grid((unsigned)(lv.n_virtual * lv.blocks_per_rank)), block(THREADS);
+  cudaError_t e = cudaLaunchCooperativeKernel(kernel, grid, block, args, 0, st);
+  return (int)e;
+}
+
+Common make_common(CommCtx** ctxs, int n_virtual, int64_t n, uint64_t seed, uint32_t step, int timeout_ms) {
+  Common c;
+  c.n = n;
+  c.world = ctxs[0]->world;
+  c.step_from_device = ctxs[0]->step_from_device;
+  (void)n_virtual;
+  c.timeout_ns = (unsigned long long)(timeout_ms > 0 ? timeout_ms : 30000) * 1000000ull;
+  c.seed_lo = (uint32_t)seed;
+  c.seed_hi = (uint32_t)(seed >> 32);
+  c.step = step;
+  return c;
+}
+
+inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+extern "C" {
+
+int64_t gc_comm_header_bytes() { return ARENA_HEADER_BYTES; }
+int gc_comm_max_world() { return MAXW; }
+
+// Bytes of arena needed by the largest fused op on an n-element gradient.
+int64_t gc_comm_required_bytes(int64_t n) {
+  int64_t npad = pad128(n);
+  int64_t qsgd = mag_bytes(npad, 16) + 3 * plane_bytes(npad) + npad * 4;   // mags(16b) + signs + 2 masks + int32 sums
+  int64_t ar = 2 * npad * 4;                                               // fp32 stage + result
+  int64_t need = qsgd > ar ? qsgd : ar;
+  return ARENA_HEADER_BYTES + need + 4096;
+}
+
+int gc_comm_create(int world, int rank, int64_t bytes, void** out_ctx) {
+  if (world < 1 || world > MAXW || rank < 0 || rank >= world || bytes < ARENA_HEADER_BYTES) return (int)cudaErrorInvalidValue;
+  CommCtx* c = new CommCtx();
+  memset(c, 0, sizeof(*c));
+  c->world = world;
+  c->rank = rank;
+  c->bytes = bytes;
+  cudaGetDevice(&c->device);
+  cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
+  cudaError_t e = cudaMalloc((void**)&c->local, (size_t)bytes);
+  if (e != cudaSuccess) { delete c; return (int)e; }
+  e = cudaMemset(c->local, 0, (size_t)bytes);
+  if (e != cudaSuccess) { cudaFree(c->local); delete c; return (int)e; }
+  cudaDeviceSynchronize();
+  c->peers[rank] = c->local;
+  *out_ctx = c;
+  return 0;
+}
+
+int gc_comm_ipc_handle(void* ctx, void* out64) {
+  CommCtx* c = (CommCtx*)ctx;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, c->local);
+  if (e != cudaSuccess) return (int)e;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(out64, &h, 64);
+  return 0;
+}
+
+// handles: world * 64 bytes, entry r = rank r's handle (own entry ignored).
+int gc_comm_open_peers(void* ctx, const void* handles) {
+  CommCtx* c = (CommCtx*)ctx;
+  for (int r = 0; r < c->world; ++r) {
+    if (r == c->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const uint8_t*)handles + 64 * r, 64);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return (int)e;
+    c->peers[r] = (uint8_t*)p;
+    c->ipc_opened[r] = true;
+  }
+  return 0;
+}
+
+// Same-process wiring (single-GPU emulation of a group, or tests): rank r's arena is at `ptr`.
+int gc_comm_set_peer(void* ctx, int r, void* ptr) {
+  CommCtx* c = (CommCtx*)ctx;
+  if (r < 0 || r >= c->world) return (int)cudaErrorInvalidValue;
+  c->peers[r] = (uint8_t*)ptr;
+  return 0;
+}
+
+void* gc_comm_arena_ptr(void* ctx) { return ((CommCtx*)ctx)->local; }
+int64_t gc_comm_arena_bytes(void* ctx) { return ((CommCtx*)ctx)->bytes; }
+// 1: kernels add the rank's launch counter to the Philox step (set before capturing a CUDA graph).
+void gc_comm_set_step_from_device(void* ctx, int on) { ((CommCtx*)ctx)->step_from_device = on ? 1 : 0; }
+
+// Reads (status, detail) of this rank's arena; synchronises the given stream.
+int gc_comm_status(void* ctx, uint32_t* out2, void* cs) {
+  CommCtx* c = (CommCtx*)ctx;
+  ArenaHeader* h = (ArenaHeader*)c->local;
+  cudaError_t e = cudaMemcpyAsync(out2, &h->status, 8, cudaMemcpyDeviceToHost, (cudaStream_t)cs);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize((cudaStream_t)cs);
+}
+
+int gc_comm_clear_status(void* ctx, void* cs) {
+  CommCtx* c = (CommCtx*)ctx;
+  ArenaHeader* h = (ArenaHeader*)c->local;
+  // status, status_detail, abort are adjacent; the barrier words are reset too (a timed-out barrier
+  // may have left arrivals behind)
+  return (int)cudaMemsetAsync(&h->bar_count, 0, 5 * sizeof(uint32_t), (cudaStream_t)cs);   // bar_count .. abort
+}
+
+int gc_comm_destroy(void* ctx) {
+  CommCtx* c = (CommCtx*)ctx;
+  if (!c) return 0;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < c->world; ++r)
+    if (c->ipc_opened[r]) cudaIpcCloseMemHandle(c->peers[r]);
+  cudaFree(c->local);
+  delete c;
+  return 0;
+}
+
+#define GC_KERNEL_TABLE(NAME, KERNEL)                                         \
+  static const void* NAME(int mw, int sumb) {                                 \
+    switch (mw * 8 + sumb) {                                                  \
+      case 1 * 8 + 1: return (const void*)KERNEL<1, 1>;                       \
+      case 1 * 8 + 2: return (const void*)KERNEL<1, 2>;                       \
+      case 1 * 8 + 4: return (const void*)KERNEL<1, 4>;                       \
+      case 2 * 8 + 1: return (const void*)KERNEL<2, 1>;                       \
+      case 2 * 8 + 2: return (const void*)KERNEL<2, 2>;                       \
+      case 2 * 8 + 4: return (const void*)KERNEL<2, 4>;                       \
+      case 4 * 8 + 1: return (const void*)KERNEL<4, 1>;                       \
+      case 4 * 8 + 2: return (const void*)KERNEL<4, 2>;                       \
+      case 4 * 8 + 4: return (const void*)KERNEL<4, 4>;                       \
+      case 8 * 8 + 1: return (const void*)KERNEL<8, 1>;                       \
+      case 8 * 8 + 2: return (const void*)KERNEL<8, 2>;                       \
+      case 8 * 8 + 4: return (const void*)KERNEL<8, 4>;                       \
+      case 16 * 8 + 1: return (const void*)KERNEL<16, 1>;                     \
+      case 16 * 8 + 2: return (const void*)KERNEL<16, 2>;                     \
+      case 16 * 8 + 4: return (const void*)KERNEL<16, 4>;                     \
+    }                                                                         \
+    return nullptr;                                                           \
+  }
+GC_KERNEL_TABLE(qsgd_kernel_for, qsgd_fused_kernel)
+GC_KERNEL_TABLE(twoscale_kernel_for, twoscale_fused_kernel)
+
+// One QSGD-MaxNorm reduce step.  ctxs: n_virtual contexts (1 in multi-GPU runs; all ranks of an
+// emulated group otherwise); ins / outs: one gradient pointer per context.
+int gc_fused_qsgd(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n, int bits,
+                  uint64_t seed, uint32_t step, int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  int world = ctxs[0]->world;
+  int s = (1 << bits) - 1, mw = mag_width(bits), sumb = sum_container_bytes(s, world);
+  int64_t npad = pad128(n);
+  QsgdParams p;
+  p.s = s;
+  p.off_mags = ARENA_HEADER_BYTES;
+  p.off_signs = align_up(p.off_mags + mag_bytes(npad, mw), 256);
+  p.off_sums = align_up(p.off_signs + plane_bytes(npad), 256);
+  if (p.off_sums + npad * sumb > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  int64_t rows = npad / 128;
+  p.chunk_rows = (rows + world - 1) / world;
+  const void* kern = qsgd_kernel_for(mw, sumb);
+  if (kern == nullptr) return (int)cudaErrorInvalidValue;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+int gc_fused_twoscale(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n, int bits_lo,
+                      int bits_hi, uint64_t seed, uint32_t step, int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  int world = ctxs[0]->world;
+  int s_lo = (1 << bits_lo) - 1, s_hi = (1 << bits_hi) - 1, mw = mag_width(bits_lo);
+  int sumb = sum_container_bytes(s_lo, world);
+  int64_t npad = pad128(n);
+  TwoScaleParams p;
+  p.s_lo = s_lo;
+  p.s_hi = s_hi;
+  p.off_mags = ARENA_HEADER_BYTES;
+  p.off_signs = align_up(p.off_mags + mag_bytes(npad, mw), 256);
+  p.off_mask_local = align_up(p.off_signs + plane_bytes(npad), 256);
+  p.off_mask_final = align_up(p.off_mask_local + plane_bytes(npad), 256);
+  p.off_sums = align_up(p.off_mask_final + plane_bytes(npad), 256);
+  if (p.off_sums + npad * sumb > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  int64_t rows = npad / 128;
+  p.chunk_rows = (rows + world - 1) / world;
+  const void* kern = twoscale_kernel_for(mw, sumb);
+  if (kern == nullptr) return (int)cudaErrorInvalidValue;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+int gc_fused_allreduce(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n,
+                       int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  int world = ctxs[0]->world;
+  int64_t npad = pad128(n);
+  AllreduceParams p;
+  p.off_stage = ARENA_HEADER_BYTES;
+  p.off_result = align_up(p.off_stage + npad * 4, 256);
+  if (world > 1 && p.off_result + npad * 4 > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  int64_t nq = npad / 4;
+  p.chunk_quads = (nq + world - 1) / world;
+  p.alpha = 1.0f / (float)world;
+  const void* kern = (const void*)allreduce_fused_kernel;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+// out = alpha * sum over ranks of in, for short vectors (n * 4 * 2 bytes of arena after the header).
+int gc_fused_small_sum(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n, float alpha,
+                       int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  SmallSumParams p;
+  p.off_buf = ARENA_HEADER_BYTES;
+  p.stride_bytes = align_up(n * 4, 256);
+  if (ctxs[0]->world > 1 && p.off_buf + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  p.alpha = alpha;
+  const void* kern = (const void*)small_sum_kernel;
+  LaunchViews lv;
+  int blocks = (int)((n + THREADS - 1) / THREADS);
+  if (blocks < 1) blocks = 1;
+  if (max_blocks <= 0 || blocks < max_blocks) max_blocks = blocks;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+// One Rand-K (optionally two-scale: bits_hi > 0) reduce step on the window [start, start + k) of the
+// keyed permutation of [0, n).
+int gc_fused_randk(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n, uint64_t seed,
+                   uint32_t npass, int64_t start, int64_t k, int bits_lo, int bits_hi, int zero_unselected,
+                   uint32_t step, int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  RandkParams p;
+  p.perm = make_perm_key((uint64_t)n, seed, npass);
+  p.start = start;
+  p.k = k;
+  p.s_lo = (1 << bits_lo) - 1;
+  p.s_hi = bits_hi > 0 ? (1 << bits_hi) - 1 : 0;
+  p.zero_unselected = zero_unselected;
+  p.stride_bytes = align_up(k * 4, 256);
+  p.off_vals = ARENA_HEADER_BYTES;
+  p.off_levels = p.off_vals + p.stride_bytes;
+  p.off_mask = p.off_levels + 2 * p.stride_bytes;
+  if (p.off_mask + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  const void* kern = (const void*)randk_fused_kernel;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+}  // extern "C"

@@ -70,7 +70,8 @@ float gc_host_absmax(const float* x, int64_t n) {
   float m = 0.0f;
   for (int64_t i = 0; i < n; ++i) {
     float a = fabsf(x[i]);
-    if (a > m || std::isnan(a)) m = a;
+    if (std::isnan(a)) a = INFINITY;   // same rule as the device kernel: a poisoned gradient shows as +inf
+    if (a > m) m = a;
   }
   return m;
 }

@@ -102,6 +102,27 @@ def cuda():
         _declare(lib, "gc_cuda_randk_scatter", c_int, [P, c_i64, c_u64, c_u32, c_i64, c_i64, P, c_float, P])
         _declare(lib, "gc_cuda_scale", c_int, [P, c_i64, c_float, P])
         _declare(lib, "gc_cuda_sgd_step", c_int, [P, P, P, c_i64, P, c_int, P])
+        PP = ctypes.POINTER(c_void_p)
+        _declare(lib, "gc_comm_header_bytes", c_i64, [])
+        _declare(lib, "gc_comm_max_world", c_int, [])
+        _declare(lib, "gc_comm_required_bytes", c_i64, [c_i64])
+        _declare(lib, "gc_comm_create", c_int, [c_int, c_int, c_i64, PP])
+        _declare(lib, "gc_comm_ipc_handle", c_int, [P, P])
+        _declare(lib, "gc_comm_open_peers", c_int, [P, P])
+        _declare(lib, "gc_comm_set_peer", c_int, [P, c_int, P])
+        _declare(lib, "gc_comm_arena_ptr", c_void_p, [P])
+        _declare(lib, "gc_comm_arena_bytes", c_i64, [P])
+        _declare(lib, "gc_comm_set_step_from_device", None, [P, c_int])
+        _declare(lib, "gc_comm_status", c_int, [P, P, P])
+        _declare(lib, "gc_comm_clear_status", c_int, [P, P])
+        _declare(lib, "gc_comm_destroy", c_int, [P])
+        _declare(lib, "gc_fused_qsgd", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_u64, c_u32, c_int, c_int, P])
+        _declare(lib, "gc_fused_twoscale", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, c_u64, c_u32, c_int,
+                                                   c_int, P])
+        _declare(lib, "gc_fused_allreduce", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, P])
+        _declare(lib, "gc_fused_small_sum", c_int, [PP, c_int, PP, PP, c_i64, c_float, c_int, c_int, P])
+        _declare(lib, "gc_fused_randk", c_int, [PP, c_int, PP, PP, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int,
+                                                c_int, c_u32, c_int, c_int, P])
         _cuda = lib
     return _cuda
 

@@ -1,0 +1,176 @@
+"""Python front end of the fused compress+collective kernels (``csrc/gc_fused.cu``).
+
+``FusedOps`` wraps the launches for a ``SymmetricArena`` (one rank per process) or a ``LocalGroup``
+(all ranks in one launch).  ``FusedEngine`` adapts them to the reducers' ``reduce(grad_in, grad_out)``
+contract.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..ops import _native as nat
+from . import comm
+
+
+class FusedOps:
+    def __init__(self, arena, timeout_ms=None, max_blocks=0):
+        self.arena = arena
+        self.timeout_ms = int(timeout_ms if timeout_ms is not None else os.environ.get("GCB200_TIMEOUT_MS", 30000))
+        self.max_blocks = int(max_blocks)
+
+    def _prep(self, ins, outs):
+        ins = [ins] if torch.is_tensor(ins) else list(ins)
+        outs = [outs] if torch.is_tensor(outs) else list(outs)
+        assert len(ins) == len(outs) == len(self.arena.ctxs)
+        for t in ins + outs:
+            assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()
+        return ins, outs, self.arena._launch_arrays(ins, outs)
+
+    def _run(self, what, err):
+        nat.check(err, what)
+
+    def qsgd(self, ins, outs, bits, seed, step):
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_qsgd", nat.cuda().gc_fused_qsgd(ctxs, nv, ia, oa, ins[0].numel(), int(bits), int(seed),
+                                                            int(step), self.timeout_ms, self.max_blocks,
+                                                            nat.stream_ptr()))
+
+    def twoscale(self, ins, outs, bits_lo, bits_hi, seed, step):
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_twoscale", nat.cuda().gc_fused_twoscale(ctxs, nv, ia, oa, ins[0].numel(), int(bits_lo),
+                                                                    int(bits_hi), int(seed), int(step),
+                                                                    self.timeout_ms, self.max_blocks,
+                                                                    nat.stream_ptr()))
+
+    def allreduce(self, ins, outs):
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_allreduce", nat.cuda().gc_fused_allreduce(ctxs, nv, ia, oa, ins[0].numel(),
+                                                                      self.timeout_ms, self.max_blocks,
+                                                                      nat.stream_ptr()))
+
+    def small_sum(self, ins, outs, alpha=1.0):
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_small_sum", nat.cuda().gc_fused_small_sum(ctxs, nv, ia, oa, ins[0].numel(), float(alpha),
+                                                                      self.timeout_ms, self.max_blocks,
+                                                                      nat.stream_ptr()))
+
+    def randk(self, ins, outs, seed, npass, start, k, bits_lo, bits_hi=0, zero_unselected=False, step=0):
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_randk", nat.cuda().gc_fused_randk(ctxs, nv, ia, oa, ins[0].numel(), int(seed), int(npass),
+                                                              int(start), int(k), int(bits_lo), int(bits_hi),
+                                                              int(bool(zero_unselected)), int(step), self.timeout_ms,
+                                                              self.max_blocks, nat.stream_ptr()))
+
+    def check(self):
+        self.arena.check()
+
+
+_shared_arena = {}
+
+
+def shared_arena(nbytes, device, group=None):
+    """One arena per (device, group), grown collectively when a larger gradient shows up."""
+    key = (str(device), id(group))
+    cur = _shared_arena.get(key)
+    if cur is None or cur.bytes < nbytes:
+        if cur is not None:
+            torch.cuda.synchronize(device)
+            cur.close()
+        cur = comm.SymmetricArena(nbytes, device, group)
+        _shared_arena[key] = cur
+    return cur
+
+
+class FusedEngine:
+    """Glue between a reducer and ``FusedOps``: arena sizing, in/out aliasing, bit accounting."""
+
+    def __init__(self, reducer):
+        self.device = reducer._device
+        self.group = reducer._group
+        self.ops = None
+        self._n = 0
+
+    @classmethod
+    def for_reducer(cls, reducer):
+        if reducer._device.type != "cuda":
+            return None
+        return cls(reducer)
+
+    def _ensure(self, n):
+        if self.ops is None or n > self._n:
+            arena = shared_arena(comm.required_bytes(n), self.device, self.group)
+            self.ops = FusedOps(arena)
+            self._n = n
+        return self.ops
+
+    @staticmethod
+    def _out_flat(flat, grad_out):
+        """The flat destination: the aliased flat view of grad_out when it has one."""
+        from ..reducers.base import TensorBuffer
+
+        alias = TensorBuffer._aliased_flat(grad_out)
+        if alias is not None and alias.numel() == flat.buffer.numel():
+            return alias, None
+        tmp = torch.empty_like(flat.buffer)
+        return tmp, tmp
+
+    def _finish(self, flat, grad_out, dest, tmp):
+        if tmp is not None:
+            buf = flat.buffer
+            flat.buffer = tmp
+            flat.is_view = False
+            flat.scatter_to(grad_out)
+            flat.buffer = buf
+
+    def qsgd_maxnorm(self, reducer, flat, grad_out):
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        with reducer._timer("reduce.fused", verbosity=2):
+            ops.qsgd(flat.buffer, dest, reducer._quantization_level, reducer._noise.seed, reducer._noise.next_step())
+        self._finish(flat, grad_out, dest, tmp)
+        container = 8 if reducer._quantization_level < 8 else 32
+        reducer.last_wire_bits = reducer._wire_bits(n)
+        return 32 + container * n
+
+    def qsgd_twoscale(self, reducer, flat, grad_out):
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        with reducer._timer("reduce.fused", verbosity=2):
+            ops.twoscale(flat.buffer, dest, reducer._lower_quantization_level, reducer._higher_quantization_level,
+                         reducer._noise.seed, reducer._noise.next_step())
+        self._finish(flat, grad_out, dest, tmp)
+        container = 8 if reducer._lower_quantization_level < 8 else 32
+        return 32 + 8 * n + container * n
+
+    def allreduce_mean(self, reducer, flat, grad_out):
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        ops.allreduce(flat.buffer, dest)
+        self._finish(flat, grad_out, dest, tmp)
+        return True
+
+    def randk(self, reducer, flat, grad_out, start, k, npass):
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        lo = reducer._quantization_level
+        hi = getattr(reducer, "_higher_quantization_level", 0)
+        with reducer._timer("reduce.fused", verbosity=2):
+            ops.randk(flat.buffer, dest, reducer._queue.seed, npass, start, k, lo, hi,
+                      reducer._unselected == "zero", reducer._noise.next_step())
+        self._finish(flat, grad_out, dest, tmp)
+        container = 8 if lo < 8 else 32
+        return 32 + container * k + (8 * k if hi else 0)
+
+    def powersgd(self, reducer, flat, grad_out, plan, fresh):
+        return None

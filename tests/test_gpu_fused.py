@@ -1,0 +1,166 @@
+"""T4 on one GPU: the fused compress+collective kernels with W ranks emulated inside ONE cooperative
+launch (``LocalGroup``), compared bit for bit against the CPU oracle evaluated per rank."""
+import pytest
+import torch
+
+from gradient_compression_b200 import ops
+from gradient_compression_b200.ops import philox
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(world, n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randn(n, generator=g) * (1e-3 * (r + 1)) for r in range(world)]
+
+
+def _group(world, n):
+    from gradient_compression_b200.parallel import comm
+    from gradient_compression_b200.parallel.engine import FusedOps
+
+    grp = comm.LocalGroup(world, comm.required_bytes(n))
+    return grp, FusedOps(grp, timeout_ms=5000)
+
+
+def _oracle_qsgd(xs, bits, seed, step):
+    world, s = len(xs), (1 << bits) - 1
+    norm = max(float(x.abs().max()) for x in xs)
+    tot = sum(ops.quantize_levels(x, norm, s, seed, philox.stream_id(r, philox.PURPOSE_ROUND), step).to(torch.int32)
+              for r, x in enumerate(xs))
+    return ops.dequantize_levels(tot.to(torch.int32), norm, s, world)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("n,bits", [(1, 4), (4099, 2), (4099, 4), (100003, 8), (100003, 12), ((1 << 20) + 3, 4)])
+def test_fused_qsgd_emulated(world, n, bits):
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, n + bits)
+        ins = [x.cuda() for x in xs]
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        for step in range(2):          # two calls: epochs advance, buffers are reused
+            fo.qsgd(ins, outs, bits, 42, step)
+            fo.check()
+            expect = _oracle_qsgd(xs, bits, 42, step)
+            for o in outs:
+                assert torch.equal(o.cpu(), expect)
+    finally:
+        grp.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_fused_qsgd_in_place(world):
+    n = 50001
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, 7)
+        bufs = [x.cuda() for x in xs]
+        fo.qsgd(bufs, bufs, 4, 1, 0)
+        fo.check()
+        expect = _oracle_qsgd(xs, 4, 1, 0)
+        assert all(torch.equal(b.cpu(), expect) for b in bufs)
+    finally:
+        grp.close()
+
+
+def _oracle_twoscale(xs, lo, hi, seed, step):
+    world, s_lo, s_hi = len(xs), (1 << lo) - 1, (1 << hi) - 1
+    norm = max(float(x.abs().max()) for x in xs)
+    q_lo = [ops.quantize_levels(x, norm, s_lo, seed, philox.stream_id(r, philox.PURPOSE_ROUND), step) for r, x in enumerate(xs)]
+    q_hi = [ops.quantize_levels(x, norm, s_hi, seed, philox.stream_id(r, philox.PURPOSE_ROUND_HI), step) for r, x in enumerate(xs)]
+    mask = torch.ones_like(q_lo[0], dtype=torch.bool)
+    for q in q_hi:
+        mask &= q.abs() <= s_lo
+    tot = sum(torch.where(mask, h, l) for h, l in zip(q_hi, q_lo))
+    a = ops.dequantize_levels(tot.to(torch.int32), norm, s_hi, world)
+    b = ops.dequantize_levels(tot.to(torch.int32), norm, s_lo, world)
+    return torch.where(mask, a, b)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("n,lo,hi", [(4099, 2, 6), (100003, 6, 10), (100003, 8, 12)])
+def test_fused_twoscale_emulated(world, n, lo, hi):
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, n + lo)
+        ins = [x.cuda() for x in xs]
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        for step in range(2):
+            fo.twoscale(ins, outs, lo, hi, 9, step)
+            fo.check()
+            expect = _oracle_twoscale(xs, lo, hi, 9, step)
+            for o in outs:
+                assert torch.equal(o.cpu(), expect)
+    finally:
+        grp.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("n", [5, 4099, (1 << 20) + 3])
+def test_fused_allreduce_emulated(world, n):
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, n)
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        fo.allreduce([x.cuda() for x in xs], outs)
+        fo.check()
+        acc = xs[0].clone()
+        for x in xs[1:]:
+            acc += x               # same left-to-right order as the kernel
+        expect = acc * (1.0 / world)
+        for o in outs:
+            assert torch.equal(o.cpu(), expect)
+        small = [torch.empty(n, device="cuda") for _ in range(world)]
+        fo.small_sum([x.cuda() for x in xs], small, alpha=0.5)
+        fo.check()
+        acc = torch.zeros(n)
+        for x in xs:
+            acc += x
+        assert all(torch.equal(o.cpu(), acc * 0.5) for o in small)
+    finally:
+        grp.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("hi", [0, 6])
+@pytest.mark.parametrize("zero", [False, True])
+def test_fused_randk_emulated(world, hi, zero):
+    n, k, start, lo, seed = 100003, 1000, 3000, 2 if hi else 4, 11
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, 5)
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        fo.randk([x.cuda() for x in xs], outs, seed, 0, start, k, lo, hi, zero, step=3)
+        fo.check()
+        idx = ops.randk_indices(seed, n, start, k)
+        sel = [x[idx] for x in xs]
+        vals = _oracle_twoscale(sel, lo, hi, seed, 3) if hi else _oracle_qsgd(sel, lo, seed, 3)
+        for r, o in enumerate(outs):
+            expect = torch.zeros(n) if zero else xs[r] * (1.0 / world)
+            expect[idx] = vals
+            assert torch.equal(o.cpu(), expect), (r, world)
+    finally:
+        grp.close()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A rank whose peers never launch: every wait runs out after the (short) limit, the kernel
+    returns, the host reads STATUS_TIMEOUT, and the same context then completes a normal step."""
+    from gradient_compression_b200.parallel import comm
+    from gradient_compression_b200.parallel.engine import FusedOps
+
+    n = 4099
+    grp = comm.LocalGroup(2, comm.required_bytes(n))
+    try:
+        lonely = comm._ArenaBase()
+        lonely.ctxs, lonely.device = (grp.ctxs[0],), grp.device     # launch rank 0 alone: rank 1 never signals
+        fo = FusedOps(lonely, timeout_ms=200)
+        x = torch.randn(n, device="cuda")
+        fo.qsgd([x], [torch.empty_like(x)], 4, 1, 0)
+        with pytest.raises(comm.CollectiveTimeout) as e:
+            fo.check()
+        assert e.value.peer == 1
+        torch.cuda.synchronize()
+        assert float(ops.absmax(x)) > 0        # the CUDA context is alive
+    finally:
+        grp.close()

@@ -1,0 +1,110 @@
+"""T3: every single-GPU sm_100a kernel against its C++ oracle, bit for bit (same Philox counters),
+on small and odd sizes."""
+import pytest
+import torch
+
+from gradient_compression_b200 import ops
+from gradient_compression_b200.ops import philox
+
+pytestmark = pytest.mark.gpu
+SIZES = [1, 31, 1024, 4099, (1 << 20) + 3]
+
+
+def _x(n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(n, generator=g) * 1e-3
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_philox_fills(n):
+    for kind in (philox.uniform, philox.u32):
+        assert torch.equal(kind(n, 42, 77, 3, device="cuda").cpu(), kind(n, 42, 77, 3))
+    assert torch.allclose(philox.normal(n, 42, 77, 3, device="cuda").cpu(), philox.normal(n, 42, 77, 3), atol=2e-5)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_absmax(n):
+    x = _x(n)
+    assert float(ops.absmax(x.cuda())) == float(x.abs().max())
+    # unaligned base pointer and repeated calls (the ticket counter re-arms itself)
+    y = _x(n + 1).cuda()[1:]
+    for _ in range(3):
+        assert float(ops.absmax(y)) == float(y.cpu().abs().max())
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("mode,s", [(ops.MODE_STOCHASTIC, 15), (ops.MODE_STOCHASTIC, 255), (ops.MODE_BIASED, 63),
+                                    (ops.MODE_NU, 64), (ops.MODE_NU_BIASED, 64)])
+def test_quantize_dequantize(n, mode, s):
+    x = _x(n, 1)
+    norm = ops.absmax(x)
+    for dtype in (torch.int8 if s < 128 else torch.int32, torch.int32):
+        q = ops.quantize_levels(x.cuda(), norm.cuda(), s, 42, 257, 9, mode=mode, dtype=dtype)
+        qc = ops.quantize_levels(x, norm, s, 42, 257, 9, mode=mode, dtype=dtype)
+        assert torch.equal(q.cpu(), qc)
+        assert torch.equal(ops.dequantize_levels(q, norm.cuda(), s, 4).cpu(), ops.dequantize_levels(qc, norm, s, 4))
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("bits", [1, 2, 4, 6, 8, 12])
+def test_qsgd_pack_unpack(n, bits):
+    x = _x(n, 2)
+    norm = ops.absmax(x)
+    mags, signs = ops.qsgd_pack(x.cuda(), norm.cuda(), bits, 5, 513, 2)
+    mc, sc = ops.qsgd_pack(x, norm, bits, 5, 513, 2)
+    nb = ops.packed_sizes(n, bits)
+    assert torch.equal(mags.cpu()[: nb[0]], mc) and torch.equal(signs.cpu(), sc)
+    y = ops.qsgd_unpack_dequant(mags, signs, n, norm.cuda(), bits, 2)
+    assert torch.equal(y.cpu(), ops.qsgd_unpack_dequant(mc, sc, n, norm, bits, 2))
+    s = (1 << bits) - 1
+    q = torch.randint(-s, s + 1, (n,), dtype=torch.int32)
+    m2, s2 = ops.pack_levels(q.cuda(), bits)
+    assert torch.equal(ops.unpack_levels(m2, s2, n, bits).cpu(), q)
+    m3, s3 = ops.pack_levels(q, bits)
+    assert torch.equal(m2.cpu(), m3) and torch.equal(s2.cpu(), s3)
+
+
+def test_randk_gather_scatter():
+    n, k = 100003, 1000
+    x = _x(n, 3)
+    vals, idx = ops.randk_gather(x.cuda(), 42, 5000, k, want_indices=True)
+    ref_idx = ops.randk_indices(42, n, 5000, k)
+    assert torch.equal(idx.cpu(), ref_idx) and torch.equal(vals.cpu(), x[ref_idx])
+    y = torch.zeros(n, device="cuda")
+    ops.randk_scatter(y, vals, 42, 5000, alpha=0.5)
+    expect = torch.zeros(n)
+    expect[ref_idx] = x[ref_idx] * 0.5
+    assert torch.equal(y.cpu(), expect)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_sgd_step(n):
+    p, g, m = _x(n, 4), _x(n, 5), _x(n, 6)
+    pc, mc = p.clone(), m.clone()
+    pd, md = p.cuda(), m.cuda()
+    for _ in range(2):
+        ops.sgd_step(pc, g, mc, lr=0.1, momentum=0.9, weight_decay=5e-4, nesterov=True)
+        ops.sgd_step(pd, g.cuda(), md, lr=0.1, momentum=0.9, weight_decay=5e-4, nesterov=True)
+    assert torch.equal(pd.cpu(), pc) and torch.equal(md.cpu(), mc)
+
+
+def test_reducers_on_gpu_match_cpu_single_worker():
+    from gradient_compression_b200 import reducers as R
+
+    shapes = [(16, 3, 3, 3), (16,), (32, 16, 3, 3), (32,), (10, 32), (10,)]
+    cfg = dict(seed=42, K=50, quantization_level=4, higher_quantization_level=8, quantization_levels=[2, 6, 10],
+               compression=0.1, rank=2)
+    g = torch.Generator().manual_seed(0)
+    grads = [torch.randn(s, generator=g) * 1e-2 for s in shapes]
+    for name in ["QSGDMaxNormReducer", "QSGDMaxNormTwoScaleReducer", "GlobalRandKMaxNormReducer",
+                 "GlobalRandKMaxNormTwoScaleReducer", "QSGDMaxNormMultiScaleReducer", "NoneAllReducer",
+                 "QSGDMaxNormBiasedReducer", "TernGradModReducer"]:
+        outs = {}
+        for dev, backend in (("cpu", "dist"), ("cuda", "dist"), ("cuda", "fused")):
+            red = R.make_reducer(name, dev, None, dict(cfg, backend=backend))
+            out = [torch.empty_like(t, device=dev) for t in grads]
+            for _ in range(2):
+                red.reduce([t.clone().to(dev) for t in grads], out)
+            outs[(dev, backend)] = torch.cat([o.reshape(-1).cpu() for o in out])
+        assert torch.equal(outs[("cpu", "dist")], outs[("cuda", "dist")]), name
+        assert torch.equal(outs[("cpu", "dist")], outs[("cuda", "fused")]), name
