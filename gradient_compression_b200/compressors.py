@@ -257,9 +257,10 @@ class QSGDMaxNormTwoScaleCompressor(_Codec):
 
     def decompress(self, norm, sign_xi_array, higher_resolution_mask, world=1):
         s_lo, s_hi = _levels(self._lower_quantization_level), _levels(self._higher_quantization_level)
-        norm = torch.as_tensor(norm, dtype=torch.float32, device=sign_xi_array.device).reshape(())
-        scale = torch.where(higher_resolution_mask.bool(), norm / (s_hi * world), norm / (s_lo * world))
-        return scale * sign_xi_array
+        # both candidates come from the native dequantiser so CPU, GPU and the fused kernel agree bit for bit
+        fine = ops.dequantize_levels(sign_xi_array, norm, s_hi, world)
+        coarse = ops.dequantize_levels(sign_xi_array, norm, s_lo, world)
+        return torch.where(higher_resolution_mask.bool(), fine, coarse)
 
 
 class GlobalRandKMaxNormTwoScaleCompressor(QSGDMaxNormTwoScaleCompressor):
@@ -300,9 +301,11 @@ class QSGDMaxNormMultiScaleCompressor(_Codec):
         return out.to(self._dtype)
 
     def decompress(self, norm, sign_xi_array, resolution_mask, world=1):
-        norm = torch.as_tensor(norm, dtype=torch.float32, device=sign_xi_array.device).reshape(())
-        scales = torch.stack([norm / (_levels(b) * world) for b in self._quantization_levels])
-        return scales[resolution_mask.long()] * sign_xi_array
+        out = ops.dequantize_levels(sign_xi_array, norm, _levels(self._quantization_levels[0]), world)
+        for ind in range(1, len(self._quantization_levels)):
+            cand = ops.dequantize_levels(sign_xi_array, norm, _levels(self._quantization_levels[ind]), world)
+            out = torch.where(resolution_mask == ind, cand, out)
+        return out
 
 
 class QSGDBPCompressor(_Codec):
