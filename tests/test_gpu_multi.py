@@ -1,0 +1,76 @@
+"""T4 on real GPUs: one process per GPU, arenas mapped into each other with CUDA IPC, the fused
+kernels of every rank running concurrently on different devices.  Results are compared bit for bit with
+the CPU oracle evaluated for every rank's input and random stream."""
+import os
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+N = 300007
+
+
+def _inputs(world, n):
+    return [torch.randn(n, generator=torch.Generator().manual_seed(1000 + r)) * (1e-3 * (r + 1)) for r in range(world)]
+
+
+def _body(rank, world):
+    import torch.distributed as dist
+
+    from gradient_compression_b200 import ops, reducers as R
+    from gradient_compression_b200.ops import philox
+    from tests.test_gpu_fused import _oracle_qsgd, _oracle_twoscale
+
+    dev = torch.device("cuda", rank)
+    xs = _inputs(world, N)
+    mine = xs[rank].to(dev)
+
+    red = R.QSGDMaxNormReducer(dev, quantization_level=4, seed=42, backend="fused")
+    for step in range(3):
+        out = [torch.empty(N, device=dev)]
+        red.reduce([mine.clone()], out)
+        red._fused.ops.check()
+        assert torch.equal(out[0].cpu(), _oracle_qsgd(xs, 4, 42, step)), f"qsgd step {step}"
+
+    # same numbers through the collective backend (our kernels + NCCL)
+    ref = R.QSGDMaxNormReducer(dev, quantization_level=4, seed=42, backend="dist")
+    out2 = [torch.empty(N, device=dev)]
+    ref.reduce([mine.clone()], out2)
+    assert torch.equal(out2[0].cpu(), _oracle_qsgd(xs, 4, 42, 0))
+
+    ts = R.QSGDMaxNormTwoScaleReducer(dev, lower_quantization_level=2, higher_quantization_level=6, seed=7, backend="fused")
+    out = [torch.empty(N, device=dev)]
+    ts.reduce([mine.clone()], out)
+    ts._fused.ops.check()
+    assert torch.equal(out[0].cpu(), _oracle_twoscale(xs, 2, 6, 7, 0)), "twoscale"
+
+    ar = R.NoneAllReducer(dev, backend="fused")
+    out = [torch.empty(N, device=dev)]
+    ar.reduce([mine.clone()], out)
+    ar._fused.ops.check()
+    acc = xs[0].clone()
+    for x in xs[1:]:
+        acc += x
+    assert torch.equal(out[0].cpu(), acc * (1.0 / world)), "allreduce"
+    nccl = mine.clone()
+    dist.all_reduce(nccl)
+    assert torch.allclose(out[0], nccl / world, atol=1e-7)
+
+    rk = R.GlobalRandKMaxNormReducer(dev, seed=5, K=10000, quantization_level=8, backend="fused")
+    out = [torch.empty(N, device=dev)]
+    rk.reduce([mine.clone()], out)
+    rk._fused.ops.check()
+    idx = ops.randk_indices(5, N, 0, 10000)
+    expect = xs[rank] * (1.0 / world)
+    expect[idx] = _oracle_qsgd([x[idx] for x in xs], 8, 5, 0)
+    assert torch.equal(out[0].cpu(), expect), "randk"
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_reducers_across_gpus(dist_runner, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist_runner(_body, world=world, backend="nccl")
