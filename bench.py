@@ -213,8 +213,7 @@ def run_ours(args, world, rank, local_rank):
 def run_reference(args, world, rank, local_rank):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.exists(os.path.join(ref_dir, "reducer.py")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (see DESIGN.md)"}))
-        return None
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed"}
     sys.path.insert(0, ref_dir)
     import torchvision
 
@@ -319,14 +318,23 @@ def run_reference(args, world, rank, local_rank):
 
 def main():
     args = parse_args()
+    # libraries (NCCL's version banner) write to stdout; keep fd 1 clean for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
+
     if not torch.cuda.is_available():
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device in this process"}))
+            emit({"impl": "reference", "unavailable": "no CUDA device in this process"})
             return
         raise SystemExit("bench.py needs a CUDA device")
     world, rank, local_rank = setup_dist(args.gpus)
     out = (run_ours if args.impl == "ours" else run_reference)(args, world, rank, local_rank)
-    if out is None:
+    if isinstance(out, dict):
+        if rank == 0:
+            emit(out)
         return
     dev_ms, launches, clocks, e2e, extra = out
     if rank == 0:
@@ -347,7 +355,7 @@ def main():
                        "published_baseline": "reference logs, 2 GPUs of unnamed hardware, scaled per GPU", **extra},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
-        print(json.dumps(line))
+        emit(line)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -1,0 +1,313 @@
+// Fused batch-norm (+ residual add) (+ ReLU), forward and backward, for NHWC fp32 activations
+// x[M, C] with M = N*H*W.  Replaces the reference's chain  bn -> (+= shortcut) -> relu  (resnet.py:71-75,
+// vgg.py:105-106), which costs 3 kernels and ~6 passes over the activation forward and ~8 backward, by
+//   forward : stats (1 read)  +  apply (1 read [+1 residual], 1 write)
+//   backward: reduce (2-3 reads) + apply (2-3 reads, 1-2 writes)
+// The ReLU mask is never stored: it is recomputed from x (or read from the saved output when a
+// residual was added).  Both "apply" kernels walk the tensor in REVERSE tile order so that they start
+// with the lines the preceding reduction touched last and find them in the 126 MB L2.
+// Reductions are deterministic: per-block partial sums go to scratch memory and a small second kernel
+// (32 channels per block, coalesced over the partials) combines them in double precision.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gc_device.cuh"
+
+using namespace gc;
+
+namespace {
+
+constexpr int BN_THREADS = 512;
+constexpr int BN_MAX_BLOCKS = 592;   // 148 SMs x 4
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+
+// Per-block accumulation of two per-channel sums.  Thread t owns the float4 column (t % vec) and visits
+// rows (t / vec) + k * (BN_THREADS / vec).  Requires C % 4 == 0, vec = C / 4 <= BN_THREADS and
+// BN_THREADS % vec == 0.  F(row-quad data) -> two float4 contributions.
+template <typename F>
+__device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_begin, int64_t row_end, F f,
+                                               float* __restrict__ partial_out /* [2C] for this block */) {
+  extern __shared__ float smem[];   // 2 * BN_THREADS * 4 floats
+  const int vec = C >> 2;
+  const int col = threadIdx.x % vec;
+  const int rofs = threadIdx.x / vec;
+  const int rstep = BN_THREADS / vec;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  for (int64_t r = row_begin + rofs; r < row_end; r += rstep) f(r, col, a, b);
+  float4* sa = reinterpret_cast<float4*>(smem);
+  float4* sb = sa + BN_THREADS;
+  sa[threadIdx.x] = a;
+  sb[threadIdx.x] = b;
+  __syncthreads();
+  // tree over the rstep threads that share a column
+  for (int s = rstep >> 1; s > 0; s >>= 1) {
+    if (rofs < s) {
+      float4 o = sa[threadIdx.x + s * vec], p = sb[threadIdx.x + s * vec];
+      float4 m = sa[threadIdx.x], q = sb[threadIdx.x];
+      sa[threadIdx.x] = make_float4(m.x + o.x, m.y + o.y, m.z + o.z, m.w + o.w);
+      sb[threadIdx.x] = make_float4(q.x + p.x, q.y + p.y, q.z + p.z, q.w + p.w);
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x < vec) {
+    st4(partial_out + 4 * threadIdx.x, sa[threadIdx.x]);
+    st4(partial_out + C + 4 * threadIdx.x, sb[threadIdx.x]);
+  }
+}
+
+// Combine the per-block partials of 32 consecutive channels (both sums) in double precision.
+// block = (32, 8, 2): x = channel in the group, y strides over partial blocks, z = which of the two sums.
+__device__ __forceinline__ void combine_partials(const float* __restrict__ partials, int nparts, int C, double (&out)[2]) {
+  __shared__ double red[2][8][32];
+  int c = blockIdx.x * 32 + threadIdx.x;
+  double acc = 0.0;
+  if (c < C)
+    for (int b = threadIdx.y; b < nparts; b += 8) acc += (double)partials[(int64_t)b * 2 * C + threadIdx.z * C + c];
+  red[threadIdx.z][threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  out[0] = out[1] = 0.0;
+  if (threadIdx.y == 0 && threadIdx.z == 0) {
+    for (int k = 0; k < 8; ++k) { out[0] += red[0][k][threadIdx.x]; out[1] += red[1][k][threadIdx.x]; }
+  }
+}
+
+// ---------------------------------------------------------------------------------- forward statistics
+// out stats[0:C] = mean, stats[C:2C] = rstd; running stats updated in place when given.
+__global__ void __launch_bounds__(BN_THREADS) bn_stats_kernel(const float* __restrict__ x, int64_t M, int C,
+                                                              int64_t rows_per_block, float* __restrict__ partials) {
+  int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  int64_t r1 = r0 + rows_per_block < M ? r0 + rows_per_block : M;
+  // shifted sums: k = the channel's value in row 0, so that sum (x-k)^2 does not cancel against
+  // (sum (x-k))^2 when |mean| is large compared with the standard deviation
+  const float4 k = ld4(x + 4 * (threadIdx.x % (C >> 2)));
+  block_two_sums(M, C, r0, r1,
+                 [&](int64_t r, int col, float4& a, float4& b) {
+                   float4 v = ld4(x + r * C + 4 * col);
+                   v.x -= k.x; v.y -= k.y; v.z -= k.z; v.w -= k.w;
+                   a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+                   b.x = fmaf(v.x, v.x, b.x); b.y = fmaf(v.y, v.y, b.y); b.z = fmaf(v.z, v.z, b.z); b.w = fmaf(v.w, v.w, b.w);
+                 },
+                 partials + (int64_t)blockIdx.x * 2 * C);
+}
+
+__global__ void bn_stats_finalize_kernel(const float* __restrict__ partials, const float* __restrict__ x, int nparts,
+                                         int64_t M, int C, float* __restrict__ stats, float* __restrict__ running_mean,
+                                         float* __restrict__ running_var, float momentum, float eps) {
+  double sums[2];
+  combine_partials(partials, nparts, C, sums);
+  int c = blockIdx.x * 32 + threadIdx.x;
+  if (threadIdx.y != 0 || threadIdx.z != 0 || c >= C) return;
+  double dmean = sums[0] / (double)M;              // mean of the shifted values
+  double var = sums[1] / (double)M - dmean * dmean;
+  if (var < 0.0) var = 0.0;
+  double mean = (double)x[c] + dmean;
+  stats[c] = (float)mean;
+  stats[C + c] = (float)(1.0 / sqrt(var + (double)eps));
+  if (running_mean != nullptr) {
+    double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+    running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * (float)mean;
+    running_var[c] = (1.0f - momentum) * running_var[c] + momentum * (float)unbiased;
+  }
+}
+
+// ---------------------------------------------------------------------------------- forward apply
+// y = act(gamma * (x - mean) * rstd + beta [+ residual]); quads visited from the end of the tensor backwards.
+__global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(const float* __restrict__ x, int64_t M, int C,
+                                                              const float* __restrict__ stats,
+                                                              const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                              const float* __restrict__ residual, int relu,
+                                                              float* __restrict__ y) {
+  const int vec = C >> 2;
+  const int64_t nq = M * vec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nq; i += stride) {
+    int64_t q = nq - 1 - i;
+    int c4 = (int)(q % vec) * 4;
+    float4 v = ld4(x + q * 4);
+    float4 mu = ld4(stats + c4), rs = ld4(stats + C + c4), g = ld4(gamma + c4), b = ld4(beta + c4);
+    float4 o;
+    o.x = fmaf((v.x - mu.x) * rs.x, g.x, b.x);
+    o.y = fmaf((v.y - mu.y) * rs.y, g.y, b.y);
+    o.z = fmaf((v.z - mu.z) * rs.z, g.z, b.z);
+    o.w = fmaf((v.w - mu.w) * rs.w, g.w, b.w);
+    if (residual != nullptr) {
+      float4 r = ld4(residual + q * 4);
+      o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+    }
+    if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+    st4(y + q * 4, o);
+  }
+}
+
+// ---------------------------------------------------------------------------------- backward reduce
+// g = dy * mask (mask = act output > 0; from the saved output y when given, else recomputed from x);
+// sums[0:C] = sum g (= dbeta), sums[C:2C] = sum g * xhat (= dgamma).
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                   const float* __restrict__ y, int64_t M, int C,
+                                                                   int64_t rows_per_block, const float* __restrict__ stats,
+                                                                   const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                   int relu, float* __restrict__ partials) {
+  int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  int64_t r1 = r0 + rows_per_block < M ? r0 + rows_per_block : M;
+  const int col = threadIdx.x % (C >> 2);
+  const float4 mu = ld4(stats + 4 * col), rs = ld4(stats + C + 4 * col);
+  const float4 gm = ld4(gamma + 4 * col), bt = ld4(beta + 4 * col);
+  block_two_sums(M, C, r0, r1,
+                 [&](int64_t r, int cc, float4& a, float4& b) {
+                   float4 d = ld4(dy + r * C + 4 * cc);
+                   float4 v = ld4(x + r * C + 4 * cc);
+                   float4 xh = make_float4((v.x - mu.x) * rs.x, (v.y - mu.y) * rs.y, (v.z - mu.z) * rs.z, (v.w - mu.w) * rs.w);
+                   if (relu) {
+                     if (y != nullptr) {
+                       float4 o = ld4(y + r * C + 4 * cc);
+                       d.x = o.x > 0.f ? d.x : 0.f; d.y = o.y > 0.f ? d.y : 0.f; d.z = o.z > 0.f ? d.z : 0.f; d.w = o.w > 0.f ? d.w : 0.f;
+                     } else {
+                       d.x = fmaf(xh.x, gm.x, bt.x) > 0.f ? d.x : 0.f; d.y = fmaf(xh.y, gm.y, bt.y) > 0.f ? d.y : 0.f;
+                       d.z = fmaf(xh.z, gm.z, bt.z) > 0.f ? d.z : 0.f; d.w = fmaf(xh.w, gm.w, bt.w) > 0.f ? d.w : 0.f;
+                     }
+                   }
+                   a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+                   b.x = fmaf(d.x, xh.x, b.x); b.y = fmaf(d.y, xh.y, b.y); b.z = fmaf(d.z, xh.z, b.z); b.w = fmaf(d.w, xh.w, b.w);
+                 },
+                 partials + (int64_t)blockIdx.x * 2 * C);
+}
+
+__global__ void bn_sums_finalize_kernel(const float* __restrict__ partials, int nparts, int C, float* __restrict__ sums) {
+  double out[2];
+  combine_partials(partials, nparts, C, out);
+  int c = blockIdx.x * 32 + threadIdx.x;
+  if (threadIdx.y != 0 || threadIdx.z != 0 || c >= C) return;
+  sums[c] = (float)out[0];
+  sums[C + c] = (float)out[1];
+}
+
+// ---------------------------------------------------------------------------------- backward apply
+// dx = gamma * rstd * (g - dbeta / M - xhat * dgamma / M); optionally dres = g (gradient of the residual).
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                  const float* __restrict__ y, int64_t M, int C,
+                                                                  const float* __restrict__ stats, const float* __restrict__ gamma,
+                                                                  const float* __restrict__ beta, const float* __restrict__ sums,
+                                                                  int relu, float* __restrict__ dx, float* __restrict__ dres) {
+  const int vec = C >> 2;
+  const int64_t nq = M * vec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const float inv_m = 1.0f / (float)M;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nq; i += stride) {
+    int64_t q = nq - 1 - i;
+    int c4 = (int)(q % vec) * 4;
+    float4 d = ld4(dy + q * 4), v = ld4(x + q * 4);
+    float4 mu = ld4(stats + c4), rs = ld4(stats + C + c4), gm = ld4(gamma + c4);
+    float4 db = ld4(sums + c4), dg = ld4(sums + C + c4);
+    float4 xh = make_float4((v.x - mu.x) * rs.x, (v.y - mu.y) * rs.y, (v.z - mu.z) * rs.z, (v.w - mu.w) * rs.w);
+    if (relu) {
+      if (y != nullptr) {
+        float4 o = ld4(y + q * 4);
+        d.x = o.x > 0.f ? d.x : 0.f; d.y = o.y > 0.f ? d.y : 0.f; d.z = o.z > 0.f ? d.z : 0.f; d.w = o.w > 0.f ? d.w : 0.f;
+      } else {
+        float4 bt = ld4(beta + c4);
+        d.x = fmaf(xh.x, gm.x, bt.x) > 0.f ? d.x : 0.f; d.y = fmaf(xh.y, gm.y, bt.y) > 0.f ? d.y : 0.f;
+        d.z = fmaf(xh.z, gm.z, bt.z) > 0.f ? d.z : 0.f; d.w = fmaf(xh.w, gm.w, bt.w) > 0.f ? d.w : 0.f;
+      }
+    }
+    if (dres != nullptr) st4(dres + q * 4, d);
+    float4 o;
+    o.x = gm.x * rs.x * (d.x - db.x * inv_m - xh.x * dg.x * inv_m);
+    o.y = gm.y * rs.y * (d.y - db.y * inv_m - xh.y * dg.y * inv_m);
+    o.z = gm.z * rs.z * (d.z - db.z * inv_m - xh.z * dg.z * inv_m);
+    o.w = gm.w * rs.w * (d.w - db.w * inv_m - xh.w * dg.w * inv_m);
+    st4(dx + q * 4, o);
+  }
+}
+
+int bn_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+inline bool bn_shape_ok(int64_t M, int C) {
+  if (M < 1 || C < 4 || (C & 3)) return false;
+  int vec = C >> 2;
+  return vec <= BN_THREADS && (BN_THREADS % vec) == 0;
+}
+
+inline int reduce_grid(int64_t M, int C, int64_t* rows_per_block) {
+  int vec = C >> 2;
+  int rstep = BN_THREADS / vec;
+  int64_t min_rows = (int64_t)rstep * 8;                  // at least 8 rows per thread
+  int64_t blocks = (M + min_rows - 1) / min_rows;
+  int64_t cap = (int64_t)bn_sm_count() * 4;
+  if (cap > BN_MAX_BLOCKS) cap = BN_MAX_BLOCKS;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  *rows_per_block = (M + blocks - 1) / blocks;
+  return (int)((M + *rows_per_block - 1) / *rows_per_block);
+}
+
+inline int apply_grid(int64_t nq) {
+  int64_t need = (nq + BN_THREADS - 1) / BN_THREADS;
+  int64_t cap = (int64_t)bn_sm_count() * 4;
+  return (int)(need < cap ? (need < 1 ? 1 : need) : cap);
+}
+
+}  // namespace
+
+extern "C" {
+
+// Scratch for the two reductions: BN_MAX_BLOCKS * 2 * C floats (no initialisation needed).
+int64_t gc_cuda_bn_scratch_bytes(int max_channels) { return (int64_t)BN_MAX_BLOCKS * 2 * max_channels * 4; }
+
+int gc_cuda_bn_supported(int64_t M, int C) { return bn_shape_ok(M, C) ? 1 : 0; }
+
+// stats[0:C] = batch mean, stats[C:2C] = 1/sqrt(biased var + eps); running stats (may be NULL) get the
+// momentum update with the unbiased variance, as torch.nn.BatchNorm2d does.
+int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* stats, float* running_mean,
+                     float* running_var, float momentum, float eps, void* cs) {
+  if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
+  int64_t rpb;
+  int grid = reduce_grid(M, C, &rpb);
+  size_t smem = 2 * BN_THREADS * sizeof(float4);
+  bn_stats_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(x, M, C, rpb, (float*)scratch);
+  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, 8, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, x, grid, M, C, stats,
+                                                                                  running_mean, running_var, momentum, eps);
+  return (int)cudaGetLastError();
+}
+
+int gc_cuda_bn_apply(const float* x, int64_t M, int C, const float* stats, const float* gamma, const float* beta,
+                     const float* residual, int relu, float* y, void* cs) {
+  if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
+  bn_apply_kernel<<<apply_grid(M * (C >> 2)), BN_THREADS, 0, (cudaStream_t)cs>>>(x, M, C, stats, gamma, beta, residual,
+                                                                                  relu, y);
+  return (int)cudaGetLastError();
+}
+
+// sums[0:C] = dbeta, sums[C:2C] = dgamma.  y: saved forward output (needed only when a residual was added).
+int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
+                          const float* gamma, const float* beta, int relu, void* scratch, float* sums, void* cs) {
+  if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
+  int64_t rpb;
+  int grid = reduce_grid(M, C, &rpb);
+  size_t smem = 2 * BN_THREADS * sizeof(float4);
+  bn_bwd_reduce_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(dy, x, y, M, C, rpb, stats, gamma, beta, relu,
+                                                                       (float*)scratch);
+  bn_sums_finalize_kernel<<<(C + 31) / 32, dim3(32, 8, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, grid, C, sums);
+  return (int)cudaGetLastError();
+}
+
+int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
+                         const float* gamma, const float* beta, const float* sums, int relu, float* dx, float* dres,
+                         void* cs) {
+  if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
+  bn_bwd_apply_kernel<<<apply_grid(M * (C >> 2)), BN_THREADS, 0, (cudaStream_t)cs>>>(dy, x, y, M, C, stats, gamma, beta,
+                                                                                      sums, relu, dx, dres);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -6,13 +6,21 @@ from __future__ import annotations
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.bn import bn_act
 from .layers import bn, conv, linear
 
 
 def _projection(cin, cout, stride):
     if stride == 1 and cin == cout:
         return nn.Sequential()
-    return nn.Sequential(conv(cin, cout, 1, stride=stride), bn(cout))
+    return _Projection(conv(cin, cout, 1, stride=stride), bn(cout))
+
+
+class _Projection(nn.Sequential):
+    """1x1 convolution + batch norm of a shortcut; children are named "0" and "1" as in the reference."""
+
+    def forward(self, x):
+        return bn_act(self[1], self[0](x), relu=False)
 
 
 class BasicBlock(nn.Module):
@@ -25,9 +33,8 @@ class BasicBlock(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
-        y = self.bn2(self.conv2(y))
-        return F.relu(y + self.shortcut(x))
+        y = bn_act(self.bn1, self.conv1(x))
+        return bn_act(self.bn2, self.conv2(y), residual=self.shortcut(x))
 
 
 class Bottleneck(nn.Module):
@@ -41,10 +48,9 @@ class Bottleneck(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
-        y = F.relu(self.bn2(self.conv2(y)))
-        y = self.bn3(self.conv3(y))
-        return F.relu(y + self.shortcut(x))
+        y = bn_act(self.bn1, self.conv1(x))
+        y = bn_act(self.bn2, self.conv2(y))
+        return bn_act(self.bn3, self.conv3(y), residual=self.shortcut(x))
 
 
 class ResNet(nn.Module):
@@ -64,7 +70,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*blocks)
 
     def forward(self, x):
-        x = F.relu(self.bn1(self.conv1(x)))
+        x = bn_act(self.bn1, self.conv1(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = F.avg_pool2d(x, 4)
         return self.linear(x.flatten(1))

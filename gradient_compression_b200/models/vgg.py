@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
+from ..ops.bn import bn_act
 from .layers import bn, conv, linear
 
 CFG = {
@@ -30,7 +31,17 @@ class VGG(nn.Module):
         self.classifier = linear(512, 10)
 
     def forward(self, x):
-        return self.classifier(self.features(x).flatten(1))
+        mods = list(self.features)
+        i = 0
+        while i < len(mods):
+            m = mods[i]
+            if isinstance(m, nn.BatchNorm2d) and i + 1 < len(mods) and isinstance(mods[i + 1], nn.ReLU):
+                x = bn_act(m, x)            # BN + ReLU in one pass
+                i += 2
+            else:
+                x = m(x)
+                i += 1
+        return self.classifier(x.flatten(1))
 
 
 def VGG11():

@@ -102,6 +102,12 @@ def cuda():
         _declare(lib, "gc_cuda_randk_scatter", c_int, [P, c_i64, c_u64, c_u32, c_i64, c_i64, P, c_float, P])
         _declare(lib, "gc_cuda_scale", c_int, [P, c_i64, c_float, P])
         _declare(lib, "gc_cuda_sgd_step", c_int, [P, P, P, c_i64, P, c_int, P])
+        _declare(lib, "gc_cuda_bn_scratch_bytes", c_i64, [c_int])
+        _declare(lib, "gc_cuda_bn_supported", c_int, [c_i64, c_int])
+        _declare(lib, "gc_cuda_bn_stats", c_int, [P, c_i64, c_int, P, P, P, P, c_float, c_float, P])
+        _declare(lib, "gc_cuda_bn_apply", c_int, [P, c_i64, c_int, P, P, P, P, c_int, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])

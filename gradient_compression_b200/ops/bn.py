@@ -1,0 +1,104 @@
+"""Fused batch-norm (+ residual add) (+ ReLU) for channels-last fp32 activations.
+
+``bn_act(bn_module, x, residual=None, relu=True)`` computes ``relu(bn(x) + residual)`` -- the pattern
+of every block of the zoo (reference: models/resnet.py:71-75, models/vgg.py:105-106) -- with the
+kernels of ``csrc/gc_bn.cu`` on CUDA and with the equivalent torch ops on CPU.  The module stays a plain
+``torch.nn.BatchNorm2d`` (same parameters, buffers and ``state_dict`` keys); only the arithmetic moves.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as nat
+
+_scratch = {}
+
+
+def _scratch_for(device, channels):
+    key = (device.type, device.index)
+    cur = _scratch.get(key)
+    need = nat.cuda().gc_cuda_bn_scratch_bytes(int(channels))
+    if cur is None or cur.numel() < need:
+        cur = torch.empty(max(need, nat.cuda().gc_cuda_bn_scratch_bytes(2048)), dtype=torch.uint8, device=device)
+        _scratch[key] = cur
+    return cur
+
+
+def _cl(t):
+    return t if t.is_contiguous(memory_format=torch.channels_last) else t.contiguous(memory_format=torch.channels_last)
+
+
+def kernel_path_ok(x):
+    if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4):
+        return False
+    n, c, h, w = x.shape
+    return bool(nat.cuda().gc_cuda_bn_supported(n * h * w, c))
+
+
+class _FusedBNAct(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, running_mean, running_var, training, momentum, eps, relu):
+        x = _cl(x)
+        n, c, h, w = x.shape
+        m = n * h * w
+        lib, st = nat.cuda(), nat.stream_ptr()
+        stats = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            if training:
+                nat.check(lib.gc_cuda_bn_stats(x.data_ptr(), m, c, _scratch_for(x.device, c).data_ptr(), stats.data_ptr(),
+                                               nat.ptr(running_mean), nat.ptr(running_var), float(momentum), float(eps),
+                                               st), "bn_stats")
+                nat.count_launch()
+            else:
+                stats[:c] = running_mean
+                stats[c:] = torch.rsqrt(running_var + eps)
+            res = _cl(residual) if residual is not None else None
+            y = torch.empty_like(x)
+            nat.check(lib.gc_cuda_bn_apply(x.data_ptr(), m, c, stats.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                           nat.ptr(res), int(relu), y.data_ptr(), st), "bn_apply")
+        ctx.relu, ctx.has_res, ctx.training = bool(relu), residual is not None, bool(training)
+        ctx.save_for_backward(x, weight, bias, stats, y if (residual is not None and relu) else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, bias, stats, y = ctx.saved_tensors
+        dy = _cl(dy)
+        n, c, h, w = x.shape
+        m = n * h * w
+        lib, st = nat.cuda(), nat.stream_ptr()
+        if not ctx.training:
+            raise RuntimeError("bn_act: backward through eval-mode statistics is not supported by the fused kernel")
+        sums = torch.empty(2 * c, dtype=torch.float32, device=x.device)
+        dx = torch.empty_like(x)
+        dres = torch.empty_like(x) if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        with torch.cuda.device(x.device):
+            nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), x.data_ptr(), nat.ptr(y), m, c, stats.data_ptr(),
+                                                weight.data_ptr(), bias.data_ptr(), int(ctx.relu),
+                                                _scratch_for(x.device, c).data_ptr(), sums.data_ptr(), st),
+                      "bn_bwd_reduce")
+            nat.count_launch()
+            nat.check(lib.gc_cuda_bn_bwd_apply(dy.data_ptr(), x.data_ptr(), nat.ptr(y), m, c, stats.data_ptr(),
+                                               weight.data_ptr(), bias.data_ptr(), sums.data_ptr(), int(ctx.relu),
+                                               dx.data_ptr(), nat.ptr(dres), st), "bn_bwd_apply")
+        if ctx.has_res and dres is None and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, sums[c:], sums[:c], dres, None, None, None, None, None, None
+
+
+def bn_act(bn, x, residual=None, relu=True):
+    """``relu(bn(x) + residual)`` with ``bn`` a ``torch.nn.BatchNorm2d`` (affine, tracking running stats)."""
+    training = bn.training or bn.running_mean is None
+    use_kernel = kernel_path_ok(x) and bn.affine and not (not training and torch.is_grad_enabled() and x.requires_grad)
+    if not use_kernel:
+        y = bn(x)
+        if residual is not None:
+            y = y + residual
+        return F.relu(y) if relu else y
+    momentum = 0.1 if bn.momentum is None else bn.momentum
+    if training and bn.track_running_stats and bn.num_batches_tracked is not None:
+        bn.num_batches_tracked.add_(1)
+    rm = bn.running_mean if bn.track_running_stats else None
+    rv = bn.running_var if bn.track_running_stats else None
+    return _FusedBNAct.apply(x, bn.weight, bn.bias, residual, rm, rv, training, momentum, bn.eps, relu)
