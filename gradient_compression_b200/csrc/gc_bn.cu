@@ -18,7 +18,7 @@ using namespace gc;
 namespace {
 
 constexpr int BN_THREADS = 512;
-constexpr int BN_MAX_BLOCKS = 592;   // 148 SMs x 4
+constexpr int BN_MAX_BLOCKS = 296;   // 148 SMs x 2 resident blocks of 512 threads (about 50 registers per thread)
 
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
@@ -35,6 +35,7 @@ __device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_beg
   const int rofs = threadIdx.x / vec;
   const int rstep = BN_THREADS / vec;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+#pragma unroll 4
   for (int64_t r = row_begin + rofs; r < row_end; r += rstep) f(r, col, a, b);
   float4* sa = reinterpret_cast<float4*>(smem);
   float4* sb = sa + BN_THREADS;
@@ -58,18 +59,27 @@ __device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_beg
 }
 
 // Combine the per-block partials of 32 consecutive channels (both sums) in double precision.
-// block = (32, 8, 2): x = channel in the group, y strides over partial blocks, z = which of the two sums.
+// block = (32, FIN_Y, 2): x = channel in the group, y strides over partial blocks, z = which of the two sums.
+constexpr int FIN_Y = 16;
 __device__ __forceinline__ void combine_partials(const float* __restrict__ partials, int nparts, int C, double (&out)[2]) {
-  __shared__ double red[2][8][32];
+  __shared__ double red[2][FIN_Y][32];
   int c = blockIdx.x * 32 + threadIdx.x;
   double acc = 0.0;
-  if (c < C)
-    for (int b = threadIdx.y; b < nparts; b += 8) acc += (double)partials[(int64_t)b * 2 * C + threadIdx.z * C + c];
+  if (c < C) {
+    const float* base = partials + threadIdx.z * C + c;
+    int b = threadIdx.y;
+    for (; b + 3 * FIN_Y < nparts; b += 4 * FIN_Y) {   // four independent loads in flight per thread
+      float v0 = base[(int64_t)b * 2 * C], v1 = base[(int64_t)(b + FIN_Y) * 2 * C];
+      float v2 = base[(int64_t)(b + 2 * FIN_Y) * 2 * C], v3 = base[(int64_t)(b + 3 * FIN_Y) * 2 * C];
+      acc += ((double)v0 + (double)v1) + ((double)v2 + (double)v3);
+    }
+    for (; b < nparts; b += FIN_Y) acc += (double)base[(int64_t)b * 2 * C];
+  }
   red[threadIdx.z][threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   out[0] = out[1] = 0.0;
   if (threadIdx.y == 0 && threadIdx.z == 0) {
-    for (int k = 0; k < 8; ++k) { out[0] += red[0][k][threadIdx.x]; out[1] += red[1][k][threadIdx.x]; }
+    for (int k = 0; k < FIN_Y; ++k) { out[0] += red[0][k][threadIdx.x]; out[1] += red[1][k][threadIdx.x]; }
   }
 }
 
@@ -243,7 +253,7 @@ inline int reduce_grid(int64_t M, int C, int64_t* rows_per_block) {
   int rstep = BN_THREADS / vec;
   int64_t min_rows = (int64_t)rstep * 8;                  // at least 8 rows per thread
   int64_t blocks = (M + min_rows - 1) / min_rows;
-  int64_t cap = (int64_t)bn_sm_count() * 4;
+  int64_t cap = (int64_t)bn_sm_count() * 2;
   if (cap > BN_MAX_BLOCKS) cap = BN_MAX_BLOCKS;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
@@ -275,7 +285,7 @@ int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* sta
   int grid = reduce_grid(M, C, &rpb);
   size_t smem = 2 * BN_THREADS * sizeof(float4);
   bn_stats_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(x, M, C, rpb, (float*)scratch);
-  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, 8, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, x, grid, M, C, stats,
+  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, x, grid, M, C, stats,
                                                                                   running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }
@@ -297,7 +307,7 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
   size_t smem = 2 * BN_THREADS * sizeof(float4);
   bn_bwd_reduce_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(dy, x, y, M, C, rpb, stats, gamma, beta, relu,
                                                                        (float*)scratch);
-  bn_sums_finalize_kernel<<<(C + 31) / 32, dim3(32, 8, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, grid, C, sums);
+  bn_sums_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, grid, C, sums);
   return (int)cudaGetLastError();
 }
 

@@ -49,6 +49,28 @@ class FlatArena:
     def grads(self):
         return self.grad_views
 
+    def detach_grads(self):
+        """Let autograd allocate fresh gradients in the next backward (no accumulate-into-view kernels)."""
+        for p in self.params:
+            p.grad = None
+
+    def collect_grads(self):
+        """Copy the gradients autograd produced into the flat buffer with one multi-tensor kernel and
+        re-attach the views.  Together with ``detach_grads`` this replaces one memset plus one in-place
+        add per parameter tensor (161 launches for ResNet-50) by a single launch."""
+        src, dst = [], []
+        for p, gv in zip(self.params, self.grad_views):
+            if p.grad is None:
+                gv.zero_()
+            elif p.grad is not gv:
+                src.append(p.grad)
+                dst.append(gv)
+        if src:
+            torch._foreach_copy_(dst, src)
+        for p, gv in zip(self.params, self.grad_views):
+            p.grad = gv
+        return self.grad_views
+
     def sgd_step(self, hyper=None, lr=None, momentum=0.9, weight_decay=5e-4, nesterov=True):
         ops.sgd_step(self.flat_params, self.flat_grads, self.flat_momentum, lr=lr, momentum=momentum,
                      weight_decay=weight_decay, nesterov=nesterov, hyper=hyper)

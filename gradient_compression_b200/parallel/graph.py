@@ -28,10 +28,10 @@ class GraphedStep:
     # -- one eager step -------------------------------------------------------------------
     def _eager(self, x, y):
         task = self.task
-        task.zero_grad()
+        task.arena.detach_grads()
         loss = task._criterion(task._model(x), y)
         loss.backward()
-        grads = task.arena.grads()
+        grads = task.arena.collect_grads()
         self.bits_per_step = self.reducer.reduce(grads, grads)
         self.opt.step()
         return loss.detach()

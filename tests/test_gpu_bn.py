@@ -67,8 +67,9 @@ def test_unsupported_channel_counts_fall_back():
 
 
 def test_resnet50_step_matches_unfused_model():
-    """Whole-model check: loss and parameter gradients of the fused ResNet-50 vs the same weights pushed
-    through torch's own bn / add / relu."""
+    """Whole-model check.  A randomly initialised ResNet-50 at batch 16 is ill-conditioned: a 1e-6 relative
+    perturbation of the input already moves its gradients by ~1.5 % with fp32 convolutions.  The fused path
+    must stay within that natural sensitivity of the unfused (torch bn / add / relu) model."""
     from gradient_compression_b200 import models
     from gradient_compression_b200.ops import bn as bnmod
 
@@ -77,19 +78,32 @@ def test_resnet50_step_matches_unfused_model():
     x = torch.randn(16, 3, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last)
     y = torch.randint(0, 10, (16,), device="cuda")
     state = {k: v.clone() for k, v in net.state_dict().items()}
-    loss = F.cross_entropy(net(x), y)
-    loss.backward()
-    g1 = [p.grad.clone() for p in net.parameters()]
-    net.load_state_dict(state)
-    net.zero_grad()
-    orig = bnmod.kernel_path_ok
-    bnmod.kernel_path_ok = lambda t: False
+
+    def run(fused, xin):
+        net.load_state_dict(state)
+        net.zero_grad()
+        orig = bnmod.kernel_path_ok
+        if not fused:
+            bnmod.kernel_path_ok = lambda t: False
+        try:
+            loss = F.cross_entropy(net(xin), y)
+            loss.backward()
+        finally:
+            bnmod.kernel_path_ok = orig
+        return float(loss.detach()), [p.grad.clone() for p in net.parameters()]
+
+    def rel(g1, g2):
+        num = sum(float(((a - b) ** 2).sum()) for a, b in zip(g1, g2))
+        return (num / sum(float((b ** 2).sum()) for b in g2)) ** 0.5
+
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
     try:
-        loss2 = F.cross_entropy(net(x), y)
-        loss2.backward()
+        loss_f, g_f = run(True, x)
+        loss_u, g_u = run(False, x)
+        _, g_p = run(False, x * (1 + 1e-6))
     finally:
-        bnmod.kernel_path_ok = orig
-    assert abs(float(loss) - float(loss2)) < 1e-3
-    num = sum(float(((a - p.grad) ** 2).sum()) for a, p in zip(g1, net.parameters()))
-    den = sum(float((p.grad ** 2).sum()) for p in net.parameters())
-    assert (num / den) ** 0.5 < 2e-2       # TF32 convolutions amplify fp32-level differences through 50 layers
+        torch.backends.cudnn.allow_tf32 = old
+    assert abs(loss_f - loss_u) < 1e-4
+    assert rel(g_f, g_u) < 2.0 * rel(g_p, g_u) + 1e-3
+    assert float((g_f[-1] - g_u[-1]).norm() / g_u[-1].norm()) < 1e-4      # the head's bias gradient is well conditioned
