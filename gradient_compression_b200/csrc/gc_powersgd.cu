@@ -1,0 +1,278 @@
+// PowerSGD rank-r pipeline on the flat gradient (reference: reducer.py:1718-1858, there ~5 Python loops
+// over 54 layers of cuBLAS GEMV calls and ~5 tiny kernels per Gram-Schmidt column):
+//   psgd_p     P = (G + E) Q for every matrix in ONE launch (warp per matrix row); E <- G + E in place;
+//              1-D tensors are packed behind P so that one exchange carries both
+//   psgd_gs    classical Gram-Schmidt of every P in one launch (block per matrix)
+//   psgd_q     Q' = M^T P for every matrix in one launch (block per 128-column tile, no atomics)
+//   psgd_out   G <- P Q'^T, E <- M - P Q'^T; 1-D tensors get the plain mean
+// All products are bandwidth-bound at r <= 4 (each streams the 94 MB gradient once), so they run on the
+// CUDA cores with 16-byte loads; the two all-reduces in between use the one-shot peer-memory sum.
+// Matrix table: int64 rows of {off, n, m, r, p_off, q_off, row_start, tile_start}.
+// Vector table: int64 rows of {off, len, dst}.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gc_device.cuh"
+
+using namespace gc;
+
+namespace {
+
+constexpr int RMAX = 4;
+constexpr int MAT_FIELDS = 8;
+
+struct Mat { int64_t off; int n, m, r; int64_t p_off, q_off; };
+
+__device__ __forceinline__ Mat load_mat(const int64_t* __restrict__ tab, int i) {
+  const int64_t* t = tab + (int64_t)i * MAT_FIELDS;
+  Mat m;
+  m.off = t[0]; m.n = (int)t[1]; m.m = (int)t[2]; m.r = (int)t[3]; m.p_off = t[4]; m.q_off = t[5];
+  return m;
+}
+
+// Largest i with tab[i][field] <= key.
+__device__ __forceinline__ int find_mat(const int64_t* __restrict__ tab, int n_mats, int field, int64_t key) {
+  int lo = 0, hi = n_mats - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (tab[(int64_t)mid * MAT_FIELDS + field] <= key) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// ------------------------------------------------------------------------------------------ P = (G + E) Q
+__global__ void __launch_bounds__(256) psgd_p_kernel(const float* __restrict__ g, float* __restrict__ e,
+                                                     const int64_t* __restrict__ tab, int n_mats, int64_t total_rows,
+                                                     const float* __restrict__ q, float* __restrict__ p) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row_g = warp; row_g < total_rows; row_g += nwarps) {
+    int mi = find_mat(tab, n_mats, 6, row_g);
+    Mat mt = load_mat(tab, mi);
+    int row = (int)(row_g - tab[(int64_t)mi * MAT_FIELDS + 6]);
+    int64_t base = mt.off + (int64_t)row * mt.m;
+    const float* qm = q + mt.q_off;
+    float acc[RMAX] = {0.f, 0.f, 0.f, 0.f};
+    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0);
+    if (vec) {
+      for (int k = lane * 4; k < mt.m; k += 128) {
+        float4 a = *reinterpret_cast<const float4*>(g + base + k);
+        float4 b = *reinterpret_cast<const float4*>(e + base + k);
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        *reinterpret_cast<float4*>(e + base + k) = a;
+        float v[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+          for (int j = 0; j < mt.r; ++j) acc[j] = fmaf(v[t], qm[(int64_t)(k + t) * mt.r + j], acc[j]);
+      }
+    } else {
+      for (int k = lane; k < mt.m; k += 32) {
+        float a = g[base + k] + e[base + k];
+        e[base + k] = a;
+        for (int j = 0; j < mt.r; ++j) acc[j] = fmaf(a, qm[(int64_t)k * mt.r + j], acc[j]);
+      }
+    }
+    for (int j = 0; j < mt.r; ++j) {
+      float s = warp_sum(acc[j]);
+      if (lane == 0) p[mt.p_off + (int64_t)row * mt.r + j] = s;
+    }
+  }
+}
+
+// 1-D tensors: stage[dst + i] = g[off + i] (their error memory is identically zero).
+__global__ void psgd_pack_vec_kernel(const float* __restrict__ g, const int64_t* __restrict__ vtab, int n_vecs,
+                                     float* __restrict__ stage) {
+  for (int v = blockIdx.x; v < n_vecs; v += gridDim.x) {
+    int64_t off = vtab[v * 3], len = vtab[v * 3 + 1], dst = vtab[v * 3 + 2];
+    for (int64_t i = threadIdx.x; i < len; i += blockDim.x) stage[dst + i] = g[off + i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------ Gram-Schmidt
+__global__ void __launch_bounds__(256) psgd_gs_kernel(float* __restrict__ p, const int64_t* __restrict__ tab, float eps) {
+  __shared__ float smem[32];
+  Mat mt = load_mat(tab, blockIdx.x);
+  float* pm = p + mt.p_off;
+  for (int i = 0; i < mt.r; ++i) {
+    float ss = 0.f;
+    for (int row = threadIdx.x; row < mt.n; row += blockDim.x) { float v = pm[(int64_t)row * mt.r + i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, smem);
+    float inv = 1.0f / (sqrtf(ss) + eps);
+    __syncthreads();
+    for (int row = threadIdx.x; row < mt.n; row += blockDim.x) pm[(int64_t)row * mt.r + i] *= inv;
+    __syncthreads();
+    for (int j = i + 1; j < mt.r; ++j) {
+      float dot = 0.f;
+      for (int row = threadIdx.x; row < mt.n; row += blockDim.x)
+        dot = fmaf(pm[(int64_t)row * mt.r + i], pm[(int64_t)row * mt.r + j], dot);
+      dot = block_sum(dot, smem);
+      __syncthreads();
+      for (int row = threadIdx.x; row < mt.n; row += blockDim.x)
+        pm[(int64_t)row * mt.r + j] = fmaf(-dot, pm[(int64_t)row * mt.r + i], pm[(int64_t)row * mt.r + j]);
+      __syncthreads();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ Q' = M^T P
+// Block = one 128-column tile of one matrix; thread (c = tid % 32, rl = tid / 32) owns columns 4c..4c+3 of the
+// tile and rows rl, rl + 8, ...; the eight row lanes are combined through shared memory in a fixed order.
+__global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e /* holds M = G + E */,
+                                                     const int64_t* __restrict__ tab, int n_mats,
+                                                     const float* __restrict__ p, float* __restrict__ qout) {
+  __shared__ float red[8][32][4 * RMAX];
+  int mi = find_mat(tab, n_mats, 7, (int64_t)blockIdx.x);
+  Mat mt = load_mat(tab, mi);
+  int tile = (int)((int64_t)blockIdx.x - tab[(int64_t)mi * MAT_FIELDS + 7]);
+  int c = threadIdx.x & 31, rl = threadIdx.x >> 5;
+  int k0 = tile * 128 + c * 4;
+  float acc[4][RMAX];
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) acc[t][j] = 0.f;
+  const float* pm = p + mt.p_off;
+  bool vec = ((mt.off & 3) == 0) && ((mt.m & 3) == 0);
+  if (k0 < mt.m) {
+    for (int row = rl; row < mt.n; row += 8) {
+      float v[4];
+      int64_t base = mt.off + (int64_t)row * mt.m + k0;
+      if (vec) {
+        float4 a = *reinterpret_cast<const float4*>(e + base);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      } else {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) v[t] = (k0 + t < mt.m) ? e[base + t] : 0.f;
+      }
+      for (int j = 0; j < mt.r; ++j) {
+        float pv = pm[(int64_t)row * mt.r + j];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) acc[t][j] = fmaf(v[t], pv, acc[t][j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+#pragma unroll
+    for (int j = 0; j < RMAX; ++j) red[rl][c][t * RMAX + j] = acc[t][j];
+  __syncthreads();
+  if (rl == 0 && k0 < mt.m) {
+    for (int t = 0; t < 4 && k0 + t < mt.m; ++t)
+      for (int j = 0; j < mt.r; ++j) {
+        float s = 0.f;
+#pragma unroll
+        for (int l = 0; l < 8; ++l) s += red[l][c][t * RMAX + j];
+        qout[mt.q_off + (int64_t)(k0 + t) * mt.r + j] = s;
+      }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ G = P Q'^T ; E = M - G
+__global__ void __launch_bounds__(256) psgd_out_kernel(float* __restrict__ g, float* __restrict__ e,
+                                                       const int64_t* __restrict__ tab, int n_mats, int64_t total_rows,
+                                                       const float* __restrict__ p, const float* __restrict__ q) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row_g = warp; row_g < total_rows; row_g += nwarps) {
+    int mi = find_mat(tab, n_mats, 6, row_g);
+    Mat mt = load_mat(tab, mi);
+    int row = (int)(row_g - tab[(int64_t)mi * MAT_FIELDS + 6]);
+    int64_t base = mt.off + (int64_t)row * mt.m;
+    const float* qm = q + mt.q_off;
+    float pr[RMAX] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < mt.r; ++j) pr[j] = p[mt.p_off + (int64_t)row * mt.r + j];
+    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0);
+    if (vec) {
+      for (int k = lane * 4; k < mt.m; k += 128) {
+        float o[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float s = 0.f;
+          for (int j = 0; j < mt.r; ++j) s = fmaf(pr[j], qm[(int64_t)(k + t) * mt.r + j], s);
+          o[t] = s;
+        }
+        float4 mv = *reinterpret_cast<const float4*>(e + base + k);
+        *reinterpret_cast<float4*>(g + base + k) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(e + base + k) = make_float4(mv.x - o[0], mv.y - o[1], mv.z - o[2], mv.w - o[3]);
+      }
+    } else {
+      for (int k = lane; k < mt.m; k += 32) {
+        float s = 0.f;
+        for (int j = 0; j < mt.r; ++j) s = fmaf(pr[j], qm[(int64_t)k * mt.r + j], s);
+        g[base + k] = s;
+        e[base + k] -= s;
+      }
+    }
+  }
+}
+
+// 1-D tensors: g[off + i] = alpha * summed[dst + i]; their error memory stays zero.
+__global__ void psgd_unpack_vec_kernel(float* __restrict__ g, float* __restrict__ e, const int64_t* __restrict__ vtab,
+                                       int n_vecs, const float* __restrict__ summed, float alpha) {
+  for (int v = blockIdx.x; v < n_vecs; v += gridDim.x) {
+    int64_t off = vtab[v * 3], len = vtab[v * 3 + 1], dst = vtab[v * 3 + 2];
+    for (int64_t i = threadIdx.x; i < len; i += blockDim.x) {
+      g[off + i] = alpha * summed[dst + i];
+      e[off + i] = 0.f;
+    }
+  }
+}
+
+int psgd_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gc_cuda_psgd_max_rank() { return RMAX; }
+
+// stage = [P (p_total floats) | packed 1-D tensors]; e <- g + e for the matrices.
+int gc_cuda_psgd_p(const float* g, float* e, const int64_t* tab, int n_mats, int64_t total_rows, const float* q,
+                   float* stage, const int64_t* vtab, int n_vecs, int64_t vec_base, void* cs) {
+  cudaStream_t st = (cudaStream_t)cs;
+  if (n_mats > 0 && total_rows > 0) {
+    int64_t blocks = (total_rows + 7) / 8;
+    int64_t cap = (int64_t)psgd_sms() * 8;
+    psgd_p_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, st>>>(g, e, tab, n_mats, total_rows, q, stage);
+  }
+  if (n_vecs > 0) psgd_pack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 128, 0, st>>>(g, vtab, n_vecs, stage + vec_base);
+  return (int)cudaGetLastError();
+}
+
+int gc_cuda_psgd_gs(float* p, const int64_t* tab, int n_mats, float eps, void* cs) {
+  if (n_mats > 0) psgd_gs_kernel<<<n_mats, 256, 0, (cudaStream_t)cs>>>(p, tab, eps);
+  return (int)cudaGetLastError();
+}
+
+int gc_cuda_psgd_q(const float* e, const int64_t* tab, int n_mats, int64_t total_tiles, const float* p, float* qout,
+                   void* cs) {
+  if (n_mats > 0 && total_tiles > 0)
+    psgd_q_kernel<<<(unsigned)total_tiles, 256, 0, (cudaStream_t)cs>>>(e, tab, n_mats, p, qout);
+  return (int)cudaGetLastError();
+}
+
+int gc_cuda_psgd_out(float* g, float* e, const int64_t* tab, int n_mats, int64_t total_rows, const float* p,
+                     const float* q, const int64_t* vtab, int n_vecs, const float* summed_vecs, float alpha, void* cs) {
+  cudaStream_t st = (cudaStream_t)cs;
+  if (n_mats > 0 && total_rows > 0) {
+    int64_t blocks = (total_rows + 7) / 8;
+    int64_t cap = (int64_t)psgd_sms() * 8;
+    psgd_out_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, st>>>(g, e, tab, n_mats, total_rows, p, q);
+  }
+  if (n_vecs > 0)
+    psgd_unpack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 128, 0, st>>>(g, e, vtab, n_vecs, summed_vecs, alpha);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -108,6 +108,11 @@ def cuda():
         _declare(lib, "gc_cuda_bn_apply", c_int, [P, c_i64, c_int, P, P, P, P, c_int, P, P])
         _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P])
         _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_psgd_max_rank", c_int, [])
+        _declare(lib, "gc_cuda_psgd_p", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, c_i64, P])
+        _declare(lib, "gc_cuda_psgd_gs", c_int, [P, P, c_int, c_float, P])
+        _declare(lib, "gc_cuda_psgd_q", c_int, [P, P, c_int, c_i64, P, P, P])
+        _declare(lib, "gc_cuda_psgd_out", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, P, c_float, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])

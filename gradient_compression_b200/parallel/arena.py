@@ -4,8 +4,8 @@ All parameters of a model are re-pointed into one contiguous fp32 buffer, and so
 tensors and the optimiser's momentum.  Consequences: the reducer sees the gradient as one vector with
 no ``torch.cat`` (reference: reducer.py:62) and no per-tensor "accumulate" copy (trainer.py:188-190);
 the optimiser is ONE kernel over N elements (``ops.sgd_step``) instead of a per-tensor loop; zeroing
-gradients is one memset.  Each tensor starts on a 16-byte boundary (4 floats) so vector loads apply
-to per-tensor views as well.
+gradients is one memset.  Tensors are packed back to back (``align=1``) so that the parameter list
+aliases the flat buffer exactly; ``align=4`` starts every tensor on a 16-byte boundary instead.
 """
 from __future__ import annotations
 
@@ -15,7 +15,7 @@ from .. import ops
 
 
 class FlatArena:
-    def __init__(self, params, align=4, with_momentum=True):
+    def __init__(self, params, align=1, with_momentum=True):
         self.params = [p for p in params]
         dev = self.params[0].device
         self.offsets, off = [], 0

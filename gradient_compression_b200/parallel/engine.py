@@ -172,5 +172,73 @@ class FusedEngine:
         container = 8 if lo < 8 else 32
         return 32 + container * k + (8 * k if hi else 0)
 
+    def _psgd_tables(self, reducer, flat, plan):
+        cache = getattr(reducer, "_psgd_cache", None)
+        if cache is not None and cache["key"] == plan["key"]:
+            return cache
+        rows, tiles, mats = 0, 0, []
+        for (i, n, m, r, po, qo) in plan["hi"]:
+            mats.append([flat._start_idx[i], n, m, r, po, qo, rows, tiles])
+            rows += n
+            tiles += (m + 127) // 128
+        vecs, voff = [], 0
+        for i in plan["lo"]:
+            ln = flat._end_idx[i] - flat._start_idx[i]
+            vecs.append([flat._start_idx[i], ln, voff])
+            voff += ln
+        dev = flat.buffer.device
+        cache = {"key": plan["key"], "rows": rows, "tiles": tiles, "n_mats": len(mats), "n_vecs": len(vecs),
+                 "v_total": voff,
+                 "tab": torch.tensor(mats or [[0] * 8], dtype=torch.int64, device=dev),
+                 "vtab": torch.tensor(vecs or [[0] * 3], dtype=torch.int64, device=dev),
+                 "stage": torch.empty(plan["p_total"] + voff, device=dev),
+                 "reduced": torch.empty(plan["p_total"] + voff, device=dev),
+                 "q_local": torch.empty(max(plan["q_total"], 1), device=dev)}
+        reducer._psgd_cache = cache
+        return cache
+
     def powersgd(self, reducer, flat, grad_out, plan, fresh):
-        return None
+        """The whole PowerSGD step with the kernels of ``csrc/gc_powersgd.cu`` and two one-shot sums."""
+        from ..ops import philox
+
+        lib = nat.cuda()
+        if reducer.rank_r > lib.gc_cuda_psgd_max_rank():
+            return None
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        c = self._psgd_tables(reducer, flat, plan)
+        dest, tmp = self._out_flat(flat, grad_out)
+        g, e = flat.buffer, reducer._memory
+        p_total, q_total = plan["p_total"], plan["q_total"]
+        with reducer._timer("reduce.prepare.q", verbosity=2):
+            if not (reducer.reuse_query and not fresh):
+                philox.normal(q_total, reducer._seed, philox.stream_id(0, philox.PURPOSE_QINIT), reducer._step,
+                              device=g.device, out=reducer.q_memory)
+        st = nat.stream_ptr
+        with torch.cuda.device(g.device):
+            with reducer._timer("reduce.compute.p", verbosity=2):
+                nat.check(lib.gc_cuda_psgd_p(g.data_ptr(), e.data_ptr(), c["tab"].data_ptr(), c["n_mats"], c["rows"],
+                                             reducer.q_memory.data_ptr(), c["stage"].data_ptr(), c["vtab"].data_ptr(),
+                                             c["n_vecs"], p_total, st()), "psgd_p")
+            with reducer._timer("reduce.p", verbosity=2):
+                ops.small_sum(c["stage"], c["reduced"], alpha=1.0)
+            with reducer._timer("reduce.normalize.p", verbosity=2):
+                nat.check(lib.gc_cuda_psgd_gs(c["reduced"].data_ptr(), c["tab"].data_ptr(), c["n_mats"], 1e-8, st()),
+                          "psgd_gs")
+            with reducer._timer("reduce.compute.q", verbosity=2):
+                nat.check(lib.gc_cuda_psgd_q(e.data_ptr(), c["tab"].data_ptr(), c["n_mats"], c["tiles"],
+                                             c["reduced"].data_ptr(), c["q_local"].data_ptr(), st()), "psgd_q")
+            with reducer._timer("reduce.q", verbosity=2):
+                ops.small_sum(c["q_local"][:max(q_total, 1)], reducer.q_memory[:max(q_total, 1)] if q_total else c["q_local"],
+                              alpha=1.0 / reducer.n_workers)
+            with reducer._timer("reduce.outerprod", verbosity=2):
+                nat.check(lib.gc_cuda_psgd_out(dest.data_ptr(), e.data_ptr(), c["tab"].data_ptr(), c["n_mats"], c["rows"],
+                                               c["reduced"].data_ptr(), reducer.q_memory.data_ptr(),
+                                               c["vtab"].data_ptr(), c["n_vecs"],
+                                               c["reduced"][p_total:].data_ptr() if c["v_total"] else None,
+                                               1.0 / reducer.n_workers, st()), "psgd_out")
+        reducer.p_memory = c["reduced"][:p_total]
+        self._finish(flat, grad_out, dest, tmp)
+        bits = 32 * (p_total + q_total + c["v_total"])
+        reducer.last_wire_bits = bits
+        return bits

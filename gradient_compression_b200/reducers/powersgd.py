@@ -54,23 +54,22 @@ class RankKReducer(Reducer):
     def reduce(self, grad_in, grad_out):
         flat = TensorBuffer(grad_in)
         dev = flat.buffer.device
-        with self._timer("reduce.memory", verbosity=2):
-            if self._memory is None:
-                self._memory = torch.zeros_like(flat.buffer)
-            else:
-                flat.buffer.add_(self._memory)
         plan = self._plan(grad_in)
         with self._timer("reduce.allocate_memory", verbosity=2):
             fresh = self.p_memory is None
             if fresh:
                 self.p_memory = torch.empty(plan["p_total"], device=dev)
                 self.q_memory = torch.empty(plan["q_total"], device=dev)
+            if self._memory is None:
+                self._memory = torch.zeros_like(flat.buffer)
         if self._use_fused():
             from ..parallel import fused
-            bits = fused.powersgd(self, flat, grad_out, plan, fresh)
+            bits = fused.powersgd(self, flat, grad_out, plan, fresh)   # adds the error memory inside its first kernel
             if bits is not None:
                 self._step += 1
                 return bits
+        with self._timer("reduce.memory", verbosity=2):
+            flat.buffer.add_(self._memory)
         mats = [flat[i].view(n, m) for (i, n, m, r, _, _) in plan["hi"]]
         ps = [self.p_memory[po: po + n * r].view(n, r) for (_, n, m, r, po, qo) in plan["hi"]]
         qs = [self.q_memory[qo: qo + m * r].view(m, r) for (_, n, m, r, po, qo) in plan["hi"]]

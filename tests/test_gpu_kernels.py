@@ -108,3 +108,23 @@ def test_reducers_on_gpu_match_cpu_single_worker():
             outs[(dev, backend)] = torch.cat([o.reshape(-1).cpu() for o in out])
         assert torch.equal(outs[("cpu", "dist")], outs[("cuda", "dist")]), name
         assert torch.equal(outs[("cpu", "dist")], outs[("cuda", "fused")]), name
+
+
+@pytest.mark.parametrize("rank", [1, 2, 4])
+def test_powersgd_fused_matches_cpu_reference_path(rank):
+    from gradient_compression_b200 import reducers as R
+
+    shapes = [(64, 3, 3, 3), (64,), (64,), (128, 64, 3, 3), (128,), (256, 128, 1, 1), (10, 256), (10,), (7, 5, 3, 3)]
+    outs, mems = {}, {}
+    for dev, backend in (("cpu", "dist"), ("cuda", "fused")):
+        red = R.RankKReducer(dev, rank=rank, seed=3, backend=backend)
+        for step in range(3):           # error feedback carries over between steps
+            g = torch.Generator().manual_seed(step)
+            grads = [(torch.randn(s, generator=g) * 1e-2).to(dev) for s in shapes]
+            out = [torch.empty_like(t) for t in grads]
+            bits = red.reduce([t.clone() for t in grads], out)
+        outs[dev] = torch.cat([o.reshape(-1).cpu() for o in out])
+        mems[dev] = red._memory.cpu()
+        assert bits == 32 * (red._layout["p_total"] + red._layout["q_total"] + 64 + 64 + 128 + 10)
+    assert torch.allclose(outs["cpu"], outs["cuda"], rtol=1e-3, atol=1e-6)
+    assert torch.allclose(mems["cpu"], mems["cuda"], rtol=1e-3, atol=1e-6)

@@ -65,6 +65,18 @@ def _body(rank, world):
     expect = xs[rank] * (1.0 / world)
     expect[idx] = _oracle_qsgd([x[idx] for x in xs], 8, 5, 0)
     assert torch.equal(out[0].cpu(), expect), "randk"
+    # PowerSGD: the fused pipeline against the same reducer on the collective backend (NCCL)
+    shapes = [(64, 27), (64,), (128, 576), (128,), (10, 128), (10,)]
+    res = {}
+    for backend in ("fused", "dist"):
+        pr = R.RankKReducer(dev, rank=2, seed=11, backend=backend)
+        for step in range(2):
+            g = torch.Generator().manual_seed(100 * rank + step)
+            grads = [(torch.randn(s, generator=g) * 1e-2).to(dev) for s in shapes]
+            out = [torch.empty_like(t) for t in grads]
+            pr.reduce([t.clone() for t in grads], out)
+        res[backend] = torch.cat([o.reshape(-1) for o in out])
+    assert torch.allclose(res["fused"], res["dist"], rtol=1e-3, atol=1e-6), "powersgd"
     torch.cuda.synchronize()
 
 
