@@ -331,7 +331,14 @@ def main():
             return
         raise SystemExit("bench.py needs a CUDA device")
     world, rank, local_rank = setup_dist(args.gpus)
-    out = (run_ours if args.impl == "ours" else run_reference)(args, world, rank, local_rank)
+    try:
+        out = (run_ours if args.impl == "ours" else run_reference)(args, world, rank, local_rank)
+    except Exception as exc:
+        if args.impl != "reference":
+            raise
+        # a failure inside the reference's own code (e.g. its PowerSGD reducer with one worker) is reported,
+        # not hidden: the arm is unavailable for this configuration
+        out = {"impl": "reference", "unavailable": f"the reference's code raised {type(exc).__name__}: {str(exc)[:160]}"}
     if isinstance(out, dict):
         if rank == 0:
             emit(out)

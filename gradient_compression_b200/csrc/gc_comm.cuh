@@ -45,6 +45,7 @@ struct RankView {
   uint8_t* arena[MAXW];   // arena base of every rank as mapped into THIS rank's address space
   const float* in;        // this rank's input gradient
   float* out;             // this rank's output gradient
+  const void* aux;        // optional second input (index list of the sparse exchange)
   int rank;
   int pad;
 };

@@ -71,13 +71,47 @@ __device__ __forceinline__ float local_absmax(const Ctx& c, const float* __restr
   int64_t nq = (n + 3) / 4;
   int64_t stride = (int64_t)c.nblocks * THREADS;
   int64_t q = (int64_t)c.bid * THREADS + threadIdx.x;
-  for (; q + stride < nq; q += 2 * stride) {
+  // four independent 16-byte loads per thread and iteration keep ~64 KB in flight per SM
+  for (; q + 3 * stride < nq; q += 4 * stride) {
     float4 a = load_quad(x, q * 4, n, al);
     float4 b = load_quad(x, (q + stride) * 4, n, al);
-    m = fmaxf(m, fmaxf(quad_absmax(a), quad_absmax(b)));
+    float4 d = load_quad(x, (q + 2 * stride) * 4, n, al);
+    float4 e = load_quad(x, (q + 3 * stride) * 4, n, al);
+    m = fmaxf(m, fmaxf(fmaxf(quad_absmax(a), quad_absmax(b)), fmaxf(quad_absmax(d), quad_absmax(e))));
   }
-  if (q < nq) m = fmaxf(m, quad_absmax(load_quad(x, q * 4, n, al)));
+  for (; q < nq; q += stride) m = fmaxf(m, quad_absmax(load_quad(x, q * 4, n, al)));
   return m;
+}
+
+// Raw (still packed) magnitudes of this lane's quad, and their decoding.
+template <int MW>
+struct RawMags { uint32_t a, b; };
+template <int MW>
+__device__ __forceinline__ RawMags<MW> load_raw_mags(const uint8_t* __restrict__ mags, int64_t row, int lane) {
+  RawMags<MW> r;
+  r.b = 0;
+  if (MW == 16) { uint2 v = reinterpret_cast<const uint2*>(mags)[row * 32 + lane]; r.a = v.x; r.b = v.y; }
+  else if (MW == 8) r.a = reinterpret_cast<const uint32_t*>(mags)[row * 32 + lane];
+  else if (MW == 4) r.a = reinterpret_cast<const uint16_t*>(mags)[row * 32 + lane];
+  else if (MW == 2) r.a = mags[row * 32 + lane];
+  else r.a = mags[row * 16 + (lane >> 1)];
+  return r;
+}
+template <int MW>
+__device__ __forceinline__ void decode_mags(const RawMags<MW>& r, int lane, int (&m)[4]) {
+  if (MW == 16) { m[0] = r.a & 0xffff; m[1] = r.a >> 16; m[2] = r.b & 0xffff; m[3] = r.b >> 16; }
+  else if (MW == 8) { m[0] = r.a & 0xff; m[1] = (r.a >> 8) & 0xff; m[2] = (r.a >> 16) & 0xff; m[3] = r.a >> 24; }
+  else if (MW == 4) { m[0] = r.a & 0xf; m[1] = (r.a >> 4) & 0xf; m[2] = (r.a >> 8) & 0xf; m[3] = (r.a >> 12) & 0xf; }
+  else if (MW == 2) { m[0] = r.a & 3; m[1] = (r.a >> 2) & 3; m[2] = (r.a >> 4) & 3; m[3] = (r.a >> 6) & 3; }
+  else { uint32_t v = (lane & 1) ? (r.a >> 4) : r.a; m[0] = v & 1; m[1] = (v >> 1) & 1; m[2] = (v >> 2) & 1; m[3] = (v >> 3) & 1; }
+}
+
+// One 32-bit load per lane fetches the bit plane of a row from ALL ranks: lane l holds word (l & 3) of rank
+// (l >> 2).  plane_bit(word_of_rank(src, j)) then comes from a shuffle.
+__device__ __forceinline__ uint32_t load_plane_all_ranks(const RankView& v, int world, int64_t off_plane, int64_t row, int lane) {
+  int src = lane >> 2;
+  if (src >= world) return 0u;
+  return reinterpret_cast<const uint32_t*>(v.arena[src] + off_plane)[row * 4 + (lane & 3)];
 }
 
 template <int SUMB>
@@ -117,39 +151,55 @@ struct QsgdParams {
   int64_t chunk_rows;     // rows owned by each rank in the reduce-scatter
 };
 
-// Owner-pull reduce of the rows this rank owns, then push of the integer sums to every rank.
+// Owner-pull reduce of the rows this rank owns, then push of the integer sums to every rank.  Two rows per
+// warp and iteration: all peer loads of both rows are issued before the first one is consumed.
 template <int MW, int SUMB>
 __device__ __forceinline__ void reduce_scatter_rows(const Ctx& c, int world, int64_t rows, int64_t chunk_rows,
                                                     int64_t off_mags, int64_t off_signs, int64_t off_sums) {
   const RankView& v = *c.v;
   int64_t r0 = (int64_t)v.rank * chunk_rows;
   int64_t r1 = r0 + chunk_rows < rows ? r0 + chunk_rows : rows;
-  for (int64_t row = r0 + c.warp; row < r1; row += c.nwarps) {
-    int m[MAXW][4];
-    bool sg[MAXW][4];
+  for (int64_t rowa = r0 + c.warp; rowa < r1; rowa += 2 * c.nwarps) {
+    int64_t rowb = rowa + c.nwarps;
+    bool hasb = rowb < r1;
+    RawMags<MW> ma[MAXW], mb[MAXW];
 #pragma unroll
-    for (int src = 0; src < MAXW; ++src) {
+    for (int src = 0; src < MAXW; ++src)
       if (src < world) {
-        load_row_mags<MW>(v.arena[src] + off_mags, row, c.lane, m[src]);
-        load_row_plane(reinterpret_cast<const uint32_t*>(v.arena[src] + off_signs), row, c.lane, sg[src]);
+        ma[src] = load_raw_mags<MW>(v.arena[src] + off_mags, rowa, c.lane);
+        if (hasb) mb[src] = load_raw_mags<MW>(v.arena[src] + off_mags, rowb, c.lane);
       }
-    }
-    int acc[4] = {0, 0, 0, 0};
+    uint32_t sa = load_plane_all_ranks(v, world, off_signs, rowa, c.lane);
+    uint32_t sb = hasb ? load_plane_all_ranks(v, world, off_signs, rowb, c.lane) : 0u;
+    int acca[4] = {0, 0, 0, 0}, accb[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int src = 0; src < MAXW; ++src) {
+    for (int src = 0; src < MAXW; ++src)
       if (src < world) {
+        int m[4];
+        decode_mags<MW>(ma[src], c.lane, m);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] += sg[src][j] ? -m[src][j] : m[src][j];
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w = __shfl_sync(FULL, sa, src * 4 + j);
+          acca[j] += ((w >> c.lane) & 1u) ? -m[j] : m[j];
+        }
+        if (hasb) decode_mags<MW>(mb[src], c.lane, m);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w = __shfl_sync(FULL, sb, src * 4 + j);
+          if (hasb) accb[j] += ((w >> c.lane) & 1u) ? -m[j] : m[j];
+        }
       }
-    }
 #pragma unroll
     for (int dst = 0; dst < MAXW; ++dst)
-      if (dst < world) store_row_sums<SUMB>(v.arena[dst] + off_sums, row, c.lane, acc);
+      if (dst < world) {
+        store_row_sums<SUMB>(v.arena[dst] + off_sums, rowa, c.lane, acca);
+        if (hasb) store_row_sums<SUMB>(v.arena[dst] + off_sums, rowb, c.lane, accb);
+      }
   }
 }
 
 template <int MW, int SUMB>
-__global__ void __launch_bounds__(THREADS) qsgd_fused_kernel(LaunchViews lv, QsgdParams p) {
+__global__ void __launch_bounds__(THREADS, 2) qsgd_fused_kernel(LaunchViews lv, QsgdParams p) {
   __shared__ float smem[32];
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
@@ -171,33 +221,53 @@ __global__ void __launch_bounds__(THREADS) qsgd_fused_kernel(LaunchViews lv, Qsg
   RngKey key = rng_key(p.c, rng_step, v.rank, PURPOSE_ROUND);
 
   if (world == 1) {
-    // single worker: quantise and dequantise in registers, one pass
-    for (int64_t row = c.warp; row < rows; row += c.nwarps) {
-      int64_t e0 = row * 128 + c.lane * 4;
-      float4 x = load_quad(v.in, e0, n, al_in);
-      U4 r = philox_block(key, (uint64_t)(e0 >> 2));
-      float4 y;
-      y.x = mul_rn(dq, (float)quantize_level(x.x, scale, p.s, r.x));
-      y.y = mul_rn(dq, (float)quantize_level(x.y, scale, p.s, r.y));
-      y.z = mul_rn(dq, (float)quantize_level(x.z, scale, p.s, r.z));
-      y.w = mul_rn(dq, (float)quantize_level(x.w, scale, p.s, r.w));
-      store_quad(v.out, e0, n, al_out, y);
+    // single worker: quantise and dequantise in registers, one pass, four rows per warp in flight
+    for (int64_t row0 = c.warp; row0 < rows; row0 += 4 * c.nwarps) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int64_t row = row0 + u * c.nwarps;
+        x[u] = (row < rows) ? load_quad(v.in, row * 128 + c.lane * 4, n, al_in) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        int64_t row = row0 + u * c.nwarps;
+        if (row >= rows) break;
+        int64_t e0 = row * 128 + c.lane * 4;
+        U4 r = philox_block(key, (uint64_t)(e0 >> 2));
+        float4 y;
+        y.x = mul_rn(dq, (float)quantize_level(x[u].x, scale, p.s, r.x));
+        y.y = mul_rn(dq, (float)quantize_level(x[u].y, scale, p.s, r.y));
+        y.z = mul_rn(dq, (float)quantize_level(x[u].z, scale, p.s, r.z));
+        y.w = mul_rn(dq, (float)quantize_level(x[u].w, scale, p.s, r.w));
+        store_quad(v.out, e0, n, al_out, y);
+      }
     }
     return;
   }
 
-  // P1: quantise + pack into this rank's arena
+  // P1: quantise + pack into this rank's arena (four rows per warp in flight)
   uint8_t* my = v.arena[v.rank];
-  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
-    int64_t e0 = row * 128 + c.lane * 4;
-    float4 x = load_quad(v.in, e0, n, al_in);
-    U4 r = philox_block(key, (uint64_t)(e0 >> 2));
-    int q0 = quantize_level(x.x, scale, p.s, r.x), q1 = quantize_level(x.y, scale, p.s, r.y);
-    int q2 = quantize_level(x.z, scale, p.s, r.z), q3 = quantize_level(x.w, scale, p.s, r.w);
-    int mg[4] = {abs(q0), abs(q1), abs(q2), abs(q3)};
-    bool sg[4] = {q0 < 0, q1 < 0, q2 < 0, q3 < 0};
-    store_row_mags<MW>(my + p.off_mags, row, c.lane, mg);
-    store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_signs), row, c.lane, sg);
+  for (int64_t row0 = c.warp; row0 < rows; row0 += 4 * c.nwarps) {
+    float4 x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int64_t row = row0 + u * c.nwarps;
+      x[u] = (row < rows) ? load_quad(v.in, row * 128 + c.lane * 4, n, al_in) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int64_t row = row0 + u * c.nwarps;
+      if (row >= rows) break;
+      int64_t e0 = row * 128 + c.lane * 4;
+      U4 r = philox_block(key, (uint64_t)(e0 >> 2));
+      int q0 = quantize_level(x[u].x, scale, p.s, r.x), q1 = quantize_level(x[u].y, scale, p.s, r.y);
+      int q2 = quantize_level(x[u].z, scale, p.s, r.z), q3 = quantize_level(x[u].w, scale, p.s, r.w);
+      int mg[4] = {abs(q0), abs(q1), abs(q2), abs(q3)};
+      bool sg[4] = {q0 < 0, q1 < 0, q2 < 0, q3 < 0};
+      store_row_mags<MW>(my + p.off_mags, row, c.lane, mg);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_signs), row, c.lane, sg);
+    }
   }
   grid_barrier(w, c.nblocks, 0x21);
   if (c.bid == 0) signal_all(v, world, PH_READY, epoch);
@@ -210,12 +280,21 @@ __global__ void __launch_bounds__(THREADS) qsgd_fused_kernel(LaunchViews lv, Qsg
   wait_all(w, world, PH_DONE, epoch);
 
   // P3: dequantise the summed levels into the fp32 gradient (1/W folded into dq)
-  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
-    int a[4];
-    load_row_sums<SUMB>(my + p.off_sums, row, c.lane, a);
-    float4 y = make_float4(mul_rn(dq, (float)a[0]), mul_rn(dq, (float)a[1]), mul_rn(dq, (float)a[2]),
-                           mul_rn(dq, (float)a[3]));
-    store_quad(v.out, row * 128 + c.lane * 4, n, al_out, y);
+  for (int64_t row0 = c.warp; row0 < rows; row0 += 4 * c.nwarps) {
+    int a[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int64_t row = row0 + u * c.nwarps;
+      if (row < rows) load_row_sums<SUMB>(my + p.off_sums, row, c.lane, a[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      int64_t row = row0 + u * c.nwarps;
+      if (row >= rows) break;
+      float4 y = make_float4(mul_rn(dq, (float)a[u][0]), mul_rn(dq, (float)a[u][1]), mul_rn(dq, (float)a[u][2]),
+                             mul_rn(dq, (float)a[u][3]));
+      store_quad(v.out, row * 128 + c.lane * 4, n, al_out, y);
+    }
   }
 }
 
@@ -228,7 +307,7 @@ struct TwoScaleParams {
 };
 
 template <int MW, int SUMB>
-__global__ void __launch_bounds__(THREADS) twoscale_fused_kernel(LaunchViews lv, TwoScaleParams p) {
+__global__ void __launch_bounds__(THREADS, 2) twoscale_fused_kernel(LaunchViews lv, TwoScaleParams p) {
   __shared__ float smem[32];
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
@@ -279,16 +358,17 @@ __global__ void __launch_bounds__(THREADS) twoscale_fused_kernel(LaunchViews lv,
                  quantize_level(x.z, sc_lo, p.s_lo, rl.z), quantize_level(x.w, sc_lo, p.s_lo, rl.w)};
     bool use_hi[4];
     if (world > 1) {
-      uint4 andw = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+      uint32_t mine = load_plane_all_ranks(v, world, p.off_mask_local, row, c.lane);
+      uint32_t andw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
 #pragma unroll
-      for (int src = 0; src < MAXW; ++src) {
-        if (src < world) {
-          uint4 t = reinterpret_cast<const uint4*>(v.arena[src] + p.off_mask_local)[row];
-          andw.x &= t.x; andw.y &= t.y; andw.z &= t.z; andw.w &= t.w;
+      for (int src = 0; src < MAXW; ++src)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t t = __shfl_sync(FULL, mine, src * 4 + j);
+          if (src < world) andw[j] &= t;
         }
-      }
-      use_hi[0] = (andw.x >> c.lane) & 1u; use_hi[1] = (andw.y >> c.lane) & 1u;
-      use_hi[2] = (andw.z >> c.lane) & 1u; use_hi[3] = (andw.w >> c.lane) & 1u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) use_hi[j] = (andw[j] >> c.lane) & 1u;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) use_hi[j] = abs(qh[j]) <= p.s_lo;
@@ -340,7 +420,7 @@ struct AllreduceParams {
   float alpha;   // 1 / W
 };
 
-__global__ void __launch_bounds__(THREADS) allreduce_fused_kernel(LaunchViews lv, AllreduceParams p) {
+__global__ void __launch_bounds__(THREADS, 2) allreduce_fused_kernel(LaunchViews lv, AllreduceParams p) {
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
   Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
@@ -359,7 +439,15 @@ __global__ void __launch_bounds__(THREADS) allreduce_fused_kernel(LaunchViews lv
     return;
   }
   float4* stage = reinterpret_cast<float4*>(v.arena[v.rank] + p.off_stage);
-  for (int64_t q = tid; q < nq; q += stride) stage[q] = load_quad(v.in, q * 4, n, al_in);
+  {
+    int64_t q = tid;
+    for (; q + 3 * stride < nq; q += 4 * stride) {
+      float4 a = load_quad(v.in, q * 4, n, al_in), b = load_quad(v.in, (q + stride) * 4, n, al_in);
+      float4 d = load_quad(v.in, (q + 2 * stride) * 4, n, al_in), e = load_quad(v.in, (q + 3 * stride) * 4, n, al_in);
+      stage[q] = a; stage[q + stride] = b; stage[q + 2 * stride] = d; stage[q + 3 * stride] = e;
+    }
+    for (; q < nq; q += stride) stage[q] = load_quad(v.in, q * 4, n, al_in);
+  }
   grid_barrier(w, c.nblocks, 0x40);
   commit_epoch(c.hdr, epoch, c.bid);
   if (c.bid == 0) signal_all(v, world, PH_STAGE, epoch);
@@ -386,7 +474,15 @@ __global__ void __launch_bounds__(THREADS) allreduce_fused_kernel(LaunchViews lv
   wait_all(w, world, PH_DONE, epoch);
 
   const float4* res = reinterpret_cast<const float4*>(v.arena[v.rank] + p.off_result);
-  for (int64_t q = tid; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, res[q]);
+  {
+    int64_t q = tid;
+    for (; q + 3 * stride < nq; q += 4 * stride) {
+      float4 a = res[q], b = res[q + stride], d = res[q + 2 * stride], e = res[q + 3 * stride];
+      store_quad(v.out, q * 4, n, al_out, a); store_quad(v.out, (q + stride) * 4, n, al_out, b);
+      store_quad(v.out, (q + 2 * stride) * 4, n, al_out, d); store_quad(v.out, (q + 3 * stride) * 4, n, al_out, e);
+    }
+    for (; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, res[q]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------ small one-shot fp32 sum
@@ -471,7 +567,18 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
     float alpha = p.zero_unselected ? 0.0f : 1.0f / (float)world;
     if (!(alpha == 1.0f && v.in == v.out)) {
       int64_t nq = (n + 3) / 4;
-      for (int64_t q = tid; q < nq; q += stride) {
+      int64_t q = tid;
+      for (; q + 3 * stride < nq; q += 4 * stride) {
+        float4 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = load_quad(v.in, (q + u * stride) * 4, n, al_in);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          x[u].x *= alpha; x[u].y *= alpha; x[u].z *= alpha; x[u].w *= alpha;
+          store_quad(v.out, (q + u * stride) * 4, n, al_out, x[u]);
+        }
+      }
+      for (; q < nq; q += stride) {
         float4 x = load_quad(v.in, q * 4, n, al_in);
         x.x *= alpha; x.y *= alpha; x.z *= alpha; x.w *= alpha;
         store_quad(v.out, q * 4, n, al_out, x);
@@ -533,6 +640,57 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
   }
 }
 
+// ------------------------------------------------------------------------------------------ sparse exchange
+// Every rank contributes `count` (index, value) pairs; the result is out = alpha * sum over ranks of the
+// scattered pairs (zero elsewhere).  Lists are published in the arena, read by every rank (one-shot), and
+// applied rank by rank with a grid barrier in between, so the floating-point sum has a fixed order and no
+// atomics are needed (indices are unique within one rank's list).
+struct SparseParams {
+  Common c;
+  int64_t count;
+  int64_t off_idx, off_val, stride_bytes;   // list regions, double-buffered by epoch parity
+  float alpha;
+};
+
+__global__ void __launch_bounds__(THREADS, 2) sparse_fused_kernel(LaunchViews lv, SparseParams p) {
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t stride = (int64_t)c.nblocks * THREADS;
+  const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
+  const int par = epoch & 1;
+  const int32_t* my_idx = reinterpret_cast<const int32_t*>(v.aux);
+  {
+    int64_t nq = (n + 3) / 4;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t q = tid; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, z);
+  }
+  if (world > 1) {
+    int32_t* pub_idx = reinterpret_cast<int32_t*>(v.arena[v.rank] + p.off_idx + par * p.stride_bytes);
+    float* pub_val = reinterpret_cast<float*>(v.arena[v.rank] + p.off_val + par * p.stride_bytes);
+    for (int64_t i = tid; i < p.count; i += stride) { pub_idx[i] = my_idx[i]; pub_val[i] = v.in[i]; }
+  }
+  grid_barrier(w, c.nblocks, 0x70);
+  commit_epoch(c.hdr, epoch, c.bid);
+  if (world > 1) {
+    if (c.bid == 0) signal_all(v, world, PH_AUX, epoch);
+    wait_all(w, world, PH_AUX, epoch);
+  }
+  for (int src = 0; src < world; ++src) {
+    const int32_t* idx = world > 1 ? reinterpret_cast<const int32_t*>(v.arena[src] + p.off_idx + par * p.stride_bytes) : my_idx;
+    const float* val = world > 1 ? reinterpret_cast<const float*>(v.arena[src] + p.off_val + par * p.stride_bytes) : v.in;
+    for (int64_t i = tid; i < p.count; i += stride) {
+      int32_t at = idx[i];
+      if (at >= 0 && at < n) v.out[at] += p.alpha * val[i];
+    }
+    if (src + 1 < world) grid_barrier(w, c.nblocks, 0x71);
+  }
+}
+
 // ------------------------------------------------------------------------------------------ host side
 struct CommCtx {
   int world, rank, device;
@@ -552,7 +710,7 @@ int max_coresident(const void* kernel, int sm_count) {
 }
 
 int fill_views(CommCtx** ctxs, int n_virtual, const float* const* ins, float* const* outs, int coresident,
-               int max_blocks, LaunchViews* lv) {
+               int max_blocks, LaunchViews* lv, const void* const* auxs = nullptr) {
   if (n_virtual < 1 || n_virtual > MAXW) return -1;
   int world = ctxs[0]->world;
   int total = coresident;
@@ -567,6 +725,7 @@ int fill_views(CommCtx** ctxs, int n_virtual, const float* const* ins, float* co
     for (int p = 0; p < MAXW; ++p) r.arena[p] = p < world ? ctxs[i]->peers[p] : nullptr;
     r.in = ins[i];
     r.out = outs[i];
+    r.aux = auxs ? auxs[i] : nullptr;
     r.rank = ctxs[i]->rank;
     r.pad = 0;
     for (int p = 0; p < world; ++p)
@@ -811,6 +970,26 @@ int gc_fused_small_sum(void** ctxs_, int n_virtual, const float* const* ins, flo
   if (blocks < 1) blocks = 1;
   if (max_blocks <= 0 || blocks < max_blocks) max_blocks = blocks;
   if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+// Sparse all-gather + scatter-add: out (n floats) = alpha * sum over ranks of scatter(idx, val); `count` pairs
+// per rank (the same on every rank).  Needs 4 * align256(count * 4) bytes of arena after the header.
+int gc_fused_sparse(void** ctxs_, int n_virtual, const float* const* vals, float* const* outs, const void* const* idxs,
+                    int64_t n, int64_t count, float alpha, int timeout_ms, int max_blocks, void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  SparseParams p;
+  p.count = count;
+  p.alpha = alpha;
+  p.stride_bytes = align_up(count * 4, 256);
+  p.off_idx = ARENA_HEADER_BYTES;
+  p.off_val = p.off_idx + 2 * p.stride_bytes;
+  if (ctxs[0]->world > 1 && p.off_val + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  const void* kern = (const void*)sparse_fused_kernel;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, vals, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, idxs) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);

@@ -113,6 +113,9 @@ def cuda():
         _declare(lib, "gc_cuda_psgd_gs", c_int, [P, P, c_int, c_float, P])
         _declare(lib, "gc_cuda_psgd_q", c_int, [P, P, c_int, c_i64, P, P, P])
         _declare(lib, "gc_cuda_psgd_out", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, P, c_float, P])
+        _declare(lib, "gc_cuda_topk_state_bytes", c_i64, [c_int])
+        _declare(lib, "gc_cuda_topk_chunk", c_int, [])
+        _declare(lib, "gc_cuda_topk_select", c_int, [P, P, P, c_int, c_i64, P, P, P, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])
@@ -134,6 +137,7 @@ def cuda():
         _declare(lib, "gc_fused_small_sum", c_int, [PP, c_int, PP, PP, c_i64, c_float, c_int, c_int, P])
         _declare(lib, "gc_fused_randk", c_int, [PP, c_int, PP, PP, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int,
                                                 c_int, c_u32, c_int, c_int, P])
+        _declare(lib, "gc_fused_sparse", c_int, [PP, c_int, PP, PP, PP, c_i64, c_i64, c_float, c_int, c_int, P])
         _cuda = lib
     return _cuda
 

@@ -68,6 +68,16 @@ class FusedOps:
                                                               int(bool(zero_unselected)), int(step), self.timeout_ms,
                                                               self.max_blocks, nat.stream_ptr()))
 
+    def sparse(self, vals, outs, idxs, alpha):
+        vals, outs, (ctxs, nv, ia, oa) = self._prep(vals, outs)
+        idxs = [idxs] if torch.is_tensor(idxs) else list(idxs)
+        import ctypes
+        xa = (ctypes.c_void_p * nv)(*[t.data_ptr() for t in idxs])
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_sparse", nat.cuda().gc_fused_sparse(ctxs, nv, ia, oa, xa, outs[0].numel(), vals[0].numel(),
+                                                                float(alpha), self.timeout_ms, self.max_blocks,
+                                                                nat.stream_ptr()))
+
     def check(self):
         self.arena.check()
 
@@ -171,6 +181,15 @@ class FusedEngine:
         self._finish(flat, grad_out, dest, tmp)
         container = 8 if lo < 8 else 32
         return 32 + container * k + (8 * k if hi else 0)
+
+    def sparse(self, reducer, flat, grad_out, idx, vals):
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        with reducer._timer("reduce.fused", verbosity=2):
+            ops.sparse(vals, dest, idx, 1.0 / reducer.n_workers)
+        self._finish(flat, grad_out, dest, tmp)
+        return True
 
     def _psgd_tables(self, reducer, flat, plan):
         cache = getattr(reducer, "_psgd_cache", None)

@@ -42,3 +42,8 @@ def randk(reducer, flat, grad_out, start, k, npass):
 def powersgd(reducer, flat, grad_out, plan, fresh):
     eng = _engine(reducer)
     return eng.powersgd(reducer, flat, grad_out, plan, fresh) if eng else None
+
+
+def sparse(reducer, flat, grad_out, idx, vals):
+    eng = _engine(reducer)
+    return eng.sparse(reducer, flat, grad_out, idx, vals) if eng else False

@@ -143,6 +143,27 @@ def test_fused_randk_emulated(world, hi, zero):
         grp.close()
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_fused_sparse_exchange_emulated(world):
+    n, count = 100003, 777
+    grp, fo = _group(world, n)
+    try:
+        g = torch.Generator().manual_seed(world)
+        idxs = [torch.randperm(n, generator=g)[:count].to(torch.int32) for _ in range(world)]
+        vals = [torch.randn(count, generator=g) for _ in range(world)]
+        outs = [torch.full((n,), 7.0, device="cuda") for _ in range(world)]
+        for _ in range(2):
+            fo.sparse([v.cuda() for v in vals], outs, [i.cuda() for i in idxs], 1.0 / world)
+            fo.check()
+            expect = torch.zeros(n)
+            for i, v in zip(idxs, vals):       # rank order, as in the kernel
+                expect[i.long()] += (1.0 / world) * v
+            for o in outs:
+                assert torch.equal(o.cpu(), expect)
+    finally:
+        grp.close()
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     """A rank whose peers never launch: every wait runs out after the (short) limit, the kernel
     returns, the host reads STATUS_TIMEOUT, and the same context then completes a normal step."""

@@ -128,3 +128,55 @@ def test_powersgd_fused_matches_cpu_reference_path(rank):
         assert bits == 32 * (red._layout["p_total"] + red._layout["q_total"] + 64 + 64 + 128 + 10)
     assert torch.allclose(outs["cpu"], outs["cuda"], rtol=1e-3, atol=1e-6)
     assert torch.allclose(mems["cpu"], mems["cuda"], rtol=1e-3, atol=1e-6)
+
+
+def test_topk_select_many_segments():
+    from gradient_compression_b200.ops.topk import TopKSelector
+
+    g_ = torch.Generator().manual_seed(5)
+    lens = [10, 4096, 4097, 100000, 7, 1 << 20]
+    ks = [100, 1, 41, 1000, 7, 10485]
+    segs, off = [], 0
+    for l, k in zip(lens, ks):
+        segs.append((off, l, k))
+        off += l
+    g = torch.randn(off, generator=g_)
+    e = torch.randn(off, generator=g_) * 0.1
+    sel = TopKSelector(segs, "cuda")
+    for _ in range(2):                       # state and histograms re-arm themselves
+        ed = e.clone().cuda()
+        idx, val = sel.select(g.cuda(), ed)
+        a = g + e
+        idx, val, ed = idx.cpu().long(), val.cpu(), ed.cpu()
+        o = 0
+        for s, l, k in segs:
+            k = min(k, l)
+            mine = set(idx[o:o + k].tolist())
+            ref = set((torch.topk(a[s:s + l].abs(), k)[1] + s).tolist())
+            assert mine == ref, (s, l, k)
+            o += k
+        assert torch.equal(val, a[idx])
+        expect = a.clone()
+        expect[idx] = 0
+        assert torch.equal(ed, expect)
+    idx2, val2 = sel.select(g.cuda(), None)   # no error feedback: selection on g itself
+    assert torch.equal(val2.cpu(), g[idx2.cpu().long()])
+
+
+def test_topk_reducers_fused_match_cpu():
+    from gradient_compression_b200 import reducers as R
+
+    shapes = [(64, 3, 3, 3), (64,), (128, 64, 3, 3), (128,), (10, 128), (10,)]
+    for name, kw in [("TopKReducer", {"K": 50}), ("TopKReducerRatio", {"compression": 0.01}), ("GlobalTopKReducer", {"K": 500})]:
+        res = {}
+        for dev, backend in (("cpu", "dist"), ("cuda", "dist"), ("cuda", "fused")):
+            red = getattr(R, name)(dev, backend=backend, **kw)
+            for step in range(3):
+                g = torch.Generator().manual_seed(step)
+                grads = [torch.randn(s, generator=g).to(dev) for s in shapes]
+                out = [torch.empty_like(t) for t in grads]
+                red.reduce([t.clone() for t in grads], out)
+            res[(dev, backend)] = (torch.cat([o.reshape(-1).cpu() for o in out]), red._memory.cpu())
+        for key in (("cuda", "dist"), ("cuda", "fused")):
+            assert torch.equal(res[key][0], res[("cpu", "dist")][0]), (name, key)
+            assert torch.equal(res[key][1], res[("cpu", "dist")][1]), (name, key)

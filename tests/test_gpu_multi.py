@@ -65,6 +65,14 @@ def _body(rank, world):
     expect = xs[rank] * (1.0 / world)
     expect[idx] = _oracle_qsgd([x[idx] for x in xs], 8, 5, 0)
     assert torch.equal(out[0].cpu(), expect), "randk"
+    tk = {}
+    for backend in ("fused", "dist"):
+        red_tk = R.TopKReducerRatio(dev, compression=0.01, backend=backend)
+        out = [torch.empty(N, device=dev)]
+        red_tk.reduce([mine.clone()], out)
+        tk[backend] = out[0].clone()
+    assert torch.allclose(tk["fused"], tk["dist"], atol=1e-7), "topk"
+
     # PowerSGD: the fused pipeline against the same reducer on the collective backend (NCCL)
     shapes = [(64, 27), (64,), (128, 576), (128,), (10, 128), (10,)]
     res = {}
