@@ -709,11 +709,23 @@ int max_coresident(const void* kernel, int sm_count) {
   return per_sm * sm_count;
 }
 
+// Blocks that a problem of `n` elements can keep busy: small messages get a small grid, which keeps the
+// grid barriers (and hence the latency floor of the fused kernels) short.
+int blocks_for_elems(int64_t n) {
+  int64_t per_block = (int64_t)THREADS * 16;      // four 16-byte accesses per thread
+  int64_t b = (n + per_block - 1) / per_block;
+  return (int)(b < 1 ? 1 : (b > 4096 ? 4096 : b));
+}
+
 int fill_views(CommCtx** ctxs, int n_virtual, const float* const* ins, float* const* outs, int coresident,
-               int max_blocks, LaunchViews* lv, const void* const* auxs = nullptr) {
+               int max_blocks, LaunchViews* lv, const void* const* auxs = nullptr, int64_t work_elems = -1) {
   if (n_virtual < 1 || n_virtual > MAXW) return -1;
   int world = ctxs[0]->world;
   int total = coresident;
+  if (work_elems >= 0) {
+    int want = blocks_for_elems(work_elems);
+    if (max_blocks <= 0 || want < max_blocks) max_blocks = want;
+  }
   if (max_blocks > 0 && max_blocks * n_virtual < total) total = max_blocks * n_virtual;
   int per = total / n_virtual;
   if (per > MAX_PARTIALS / 2) per = MAX_PARTIALS / 2;
@@ -902,7 +914,7 @@ int gc_fused_qsgd(void** ctxs_, int n_virtual, const float* const* ins, float* c
   const void* kern = qsgd_kernel_for(mw, sumb);
   if (kern == nullptr) return (int)cudaErrorInvalidValue;
   LaunchViews lv;
-  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);
@@ -929,7 +941,7 @@ int gc_fused_twoscale(void** ctxs_, int n_virtual, const float* const* ins, floa
   const void* kern = twoscale_kernel_for(mw, sumb);
   if (kern == nullptr) return (int)cudaErrorInvalidValue;
   LaunchViews lv;
-  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);
@@ -949,7 +961,7 @@ int gc_fused_allreduce(void** ctxs_, int n_virtual, const float* const* ins, flo
   p.alpha = 1.0f / (float)world;
   const void* kern = (const void*)allreduce_fused_kernel;
   LaunchViews lv;
-  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);
@@ -989,7 +1001,7 @@ int gc_fused_sparse(void** ctxs_, int n_virtual, const float* const* vals, float
   if (ctxs[0]->world > 1 && p.off_val + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
   const void* kern = (const void*)sparse_fused_kernel;
   LaunchViews lv;
-  if (fill_views(ctxs, n_virtual, vals, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, idxs) != 0)
+  if (fill_views(ctxs, n_virtual, vals, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, idxs, n) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, 0, 0, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);
@@ -1015,7 +1027,7 @@ int gc_fused_randk(void** ctxs_, int n_virtual, const float* const* ins, float* 
   if (p.off_mask + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
   const void* kern = (const void*)randk_fused_kernel;
   LaunchViews lv;
-  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv) != 0)
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)
     return (int)cudaErrorInvalidValue;
   p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
   return coop_launch(kern, lv, p, (cudaStream_t)cs);

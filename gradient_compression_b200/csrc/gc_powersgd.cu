@@ -41,6 +41,55 @@ __device__ __forceinline__ int find_mat(const int64_t* __restrict__ tab, int n_m
 }
 
 // ------------------------------------------------------------------------------------------ P = (G + E) Q
+// acc[j] += sum_t v[t] * q[(k + t) * R + j] with the 4 * R query values fetched by 16-byte loads.
+template <int R>
+__device__ __forceinline__ void dot4(const float (&v)[4], const float* __restrict__ qk, float (&acc)[RMAX]) {
+  if (R == 1) {
+    float4 q = *reinterpret_cast<const float4*>(qk);
+    acc[0] = fmaf(v[0], q.x, fmaf(v[1], q.y, fmaf(v[2], q.z, fmaf(v[3], q.w, acc[0]))));
+  } else if (R == 2) {
+    float4 a = *reinterpret_cast<const float4*>(qk), b = *reinterpret_cast<const float4*>(qk + 4);
+    acc[0] = fmaf(v[0], a.x, fmaf(v[1], a.z, fmaf(v[2], b.x, fmaf(v[3], b.z, acc[0]))));
+    acc[1] = fmaf(v[0], a.y, fmaf(v[1], a.w, fmaf(v[2], b.y, fmaf(v[3], b.w, acc[1]))));
+  } else if (R == 4) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      float4 q = *reinterpret_cast<const float4*>(qk + 4 * t);
+      acc[0] = fmaf(v[t], q.x, acc[0]); acc[1] = fmaf(v[t], q.y, acc[1]);
+      acc[2] = fmaf(v[t], q.z, acc[2]); acc[3] = fmaf(v[t], q.w, acc[3]);
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+#pragma unroll
+      for (int j = 0; j < R; ++j) acc[j] = fmaf(v[t], qk[t * R + j], acc[j]);
+  }
+}
+
+template <int R>
+__device__ __forceinline__ void p_row_vec(const float* __restrict__ g, float* __restrict__ e, int64_t base, int m,
+                                          const float* __restrict__ qm, int lane, float (&acc)[RMAX]) {
+  int k = lane * 4;
+  for (; k + 128 < m; k += 256) {     // two independent 512-byte pieces of the row per iteration
+    float4 a0 = *reinterpret_cast<const float4*>(g + base + k), b0 = *reinterpret_cast<const float4*>(e + base + k);
+    float4 a1 = *reinterpret_cast<const float4*>(g + base + k + 128), b1 = *reinterpret_cast<const float4*>(e + base + k + 128);
+    a0.x += b0.x; a0.y += b0.y; a0.z += b0.z; a0.w += b0.w;
+    a1.x += b1.x; a1.y += b1.y; a1.z += b1.z; a1.w += b1.w;
+    *reinterpret_cast<float4*>(e + base + k) = a0;
+    *reinterpret_cast<float4*>(e + base + k + 128) = a1;
+    float v0[4] = {a0.x, a0.y, a0.z, a0.w}, v1[4] = {a1.x, a1.y, a1.z, a1.w};
+    dot4<R>(v0, qm + (int64_t)k * R, acc);
+    dot4<R>(v1, qm + (int64_t)(k + 128) * R, acc);
+  }
+  for (; k < m; k += 128) {
+    float4 a = *reinterpret_cast<const float4*>(g + base + k), b = *reinterpret_cast<const float4*>(e + base + k);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    *reinterpret_cast<float4*>(e + base + k) = a;
+    float v[4] = {a.x, a.y, a.z, a.w};
+    dot4<R>(v, qm + (int64_t)k * R, acc);
+  }
+}
+
 __global__ void __launch_bounds__(256) psgd_p_kernel(const float* __restrict__ g, float* __restrict__ e,
                                                      const int64_t* __restrict__ tab, int n_mats, int64_t total_rows,
                                                      const float* __restrict__ q, float* __restrict__ p) {
@@ -54,19 +103,12 @@ __global__ void __launch_bounds__(256) psgd_p_kernel(const float* __restrict__ g
     int64_t base = mt.off + (int64_t)row * mt.m;
     const float* qm = q + mt.q_off;
     float acc[RMAX] = {0.f, 0.f, 0.f, 0.f};
-    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0);
-    if (vec) {
-      for (int k = lane * 4; k < mt.m; k += 128) {
-        float4 a = *reinterpret_cast<const float4*>(g + base + k);
-        float4 b = *reinterpret_cast<const float4*>(e + base + k);
-        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-        *reinterpret_cast<float4*>(e + base + k) = a;
-        float v[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-        for (int t = 0; t < 4; ++t)
-          for (int j = 0; j < mt.r; ++j) acc[j] = fmaf(v[t], qm[(int64_t)(k + t) * mt.r + j], acc[j]);
-      }
-    } else {
+    // 16-byte path: row start, row length and the query block must all be 16-byte aligned
+    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0) && ((mt.q_off & 3) == 0);
+    if (vec && mt.r == 1) p_row_vec<1>(g, e, base, mt.m, qm, lane, acc);
+    else if (vec && mt.r == 2) p_row_vec<2>(g, e, base, mt.m, qm, lane, acc);
+    else if (vec && mt.r == 4) p_row_vec<4>(g, e, base, mt.m, qm, lane, acc);
+    else {
       for (int k = lane; k < mt.m; k += 32) {
         float a = g[base + k] + e[base + k];
         e[base + k] = a;
@@ -118,9 +160,12 @@ __global__ void __launch_bounds__(256) psgd_gs_kernel(float* __restrict__ p, con
 // ------------------------------------------------------------------------------------------ Q' = M^T P
 // Block = one 128-column tile of one matrix; thread (c = tid % 32, rl = tid / 32) owns columns 4c..4c+3 of the
 // tile and rows rl, rl + 8, ...; the eight row lanes are combined through shared memory in a fixed order.
+constexpr int Q_ROWCHUNK = 2048;   // rows per block along grid.y (one chunk covers every ResNet / VGG layer)
+
 __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e /* holds M = G + E */,
                                                      const int64_t* __restrict__ tab, int n_mats,
-                                                     const float* __restrict__ p, float* __restrict__ qout) {
+                                                     const float* __restrict__ p, float* __restrict__ qout,
+                                                     int64_t q_total) {
   __shared__ float red[8][32][4 * RMAX];
   int mi = find_mat(tab, n_mats, 7, (int64_t)blockIdx.x);
   Mat mt = load_mat(tab, mi);
@@ -134,8 +179,11 @@ __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e
     for (int j = 0; j < RMAX; ++j) acc[t][j] = 0.f;
   const float* pm = p + mt.p_off;
   bool vec = ((mt.off & 3) == 0) && ((mt.m & 3) == 0);
+  const int row_lo = blockIdx.y * Q_ROWCHUNK;
+  const int row_hi = row_lo + Q_ROWCHUNK < mt.n ? row_lo + Q_ROWCHUNK : mt.n;
+  float* qdst = qout + (int64_t)blockIdx.y * q_total;     // chunk y writes its own partial copy
   if (k0 < mt.m) {
-    for (int row = rl; row < mt.n; row += 8) {
+    for (int row = row_lo + rl; row < row_hi; row += 8) {
       float v[4];
       int64_t base = mt.off + (int64_t)row * mt.m + k0;
       if (vec) {
@@ -163,8 +211,18 @@ __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e
         float s = 0.f;
 #pragma unroll
         for (int l = 0; l < 8; ++l) s += red[l][c][t * RMAX + j];
-        qout[mt.q_off + (int64_t)(k0 + t) * mt.r + j] = s;
+        qdst[mt.q_off + (int64_t)(k0 + t) * mt.r + j] = s;
       }
+  }
+}
+
+// Sum of the row-chunk partials (only launched when some matrix has more than Q_ROWCHUNK rows).
+__global__ void psgd_q_sum_kernel(float* __restrict__ q, int64_t q_total, int chunks) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < q_total; i += stride) {
+    float s = q[i];
+    for (int c = 1; c < chunks; ++c) s += q[(int64_t)c * q_total + i];
+    q[i] = s;
   }
 }
 
@@ -183,15 +241,24 @@ __global__ void __launch_bounds__(256) psgd_out_kernel(float* __restrict__ g, fl
     const float* qm = q + mt.q_off;
     float pr[RMAX] = {0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < mt.r; ++j) pr[j] = p[mt.p_off + (int64_t)row * mt.r + j];
-    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0);
+    bool vec = ((base & 3) == 0) && ((mt.m & 3) == 0) && ((mt.q_off & 3) == 0) && (mt.r == 1 || mt.r == 2 || mt.r == 4);
     if (vec) {
       for (int k = lane * 4; k < mt.m; k += 128) {
         float o[4];
+        const float* qk = qm + (int64_t)k * mt.r;
+        if (mt.r == 1) {
+          float4 q0 = *reinterpret_cast<const float4*>(qk);
+          o[0] = pr[0] * q0.x; o[1] = pr[0] * q0.y; o[2] = pr[0] * q0.z; o[3] = pr[0] * q0.w;
+        } else if (mt.r == 2) {
+          float4 q0 = *reinterpret_cast<const float4*>(qk), q1 = *reinterpret_cast<const float4*>(qk + 4);
+          o[0] = fmaf(pr[1], q0.y, pr[0] * q0.x); o[1] = fmaf(pr[1], q0.w, pr[0] * q0.z);
+          o[2] = fmaf(pr[1], q1.y, pr[0] * q1.x); o[3] = fmaf(pr[1], q1.w, pr[0] * q1.z);
+        } else {
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          float s = 0.f;
-          for (int j = 0; j < mt.r; ++j) s = fmaf(pr[j], qm[(int64_t)(k + t) * mt.r + j], s);
-          o[t] = s;
+          for (int t = 0; t < 4; ++t) {
+            float4 qq = *reinterpret_cast<const float4*>(qk + 4 * t);
+            o[t] = fmaf(pr[3], qq.w, fmaf(pr[2], qq.z, fmaf(pr[1], qq.y, pr[0] * qq.x)));
+          }
         }
         float4 mv = *reinterpret_cast<const float4*>(e + base + k);
         *reinterpret_cast<float4*>(g + base + k) = make_float4(o[0], o[1], o[2], o[3]);
@@ -255,10 +322,19 @@ int gc_cuda_psgd_gs(float* p, const int64_t* tab, int n_mats, float eps, void* c
   return (int)cudaGetLastError();
 }
 
+int gc_cuda_psgd_q_chunks(int max_rows) { return (max_rows + Q_ROWCHUNK - 1) / Q_ROWCHUNK; }
+
+// qout must hold gc_cuda_psgd_q_chunks(max_rows) * q_total floats; the result ends up in its first q_total.
 int gc_cuda_psgd_q(const float* e, const int64_t* tab, int n_mats, int64_t total_tiles, const float* p, float* qout,
-                   void* cs) {
-  if (n_mats > 0 && total_tiles > 0)
-    psgd_q_kernel<<<(unsigned)total_tiles, 256, 0, (cudaStream_t)cs>>>(e, tab, n_mats, p, qout);
+                   int64_t q_total, int max_rows, void* cs) {
+  if (n_mats > 0 && total_tiles > 0) {
+    int chunks = gc_cuda_psgd_q_chunks(max_rows);
+    psgd_q_kernel<<<dim3((unsigned)total_tiles, (unsigned)chunks), 256, 0, (cudaStream_t)cs>>>(e, tab, n_mats, p, qout, q_total);
+    if (chunks > 1) {
+      int64_t blocks = (q_total + 255) / 256;
+      psgd_q_sum_kernel<<<(int)(blocks < 1024 ? blocks : 1024), 256, 0, (cudaStream_t)cs>>>(qout, q_total, chunks);
+    }
+  }
   return (int)cudaGetLastError();
 }
 

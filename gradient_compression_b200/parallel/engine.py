@@ -212,7 +212,9 @@ class FusedEngine:
                  "vtab": torch.tensor(vecs or [[0] * 3], dtype=torch.int64, device=dev),
                  "stage": torch.empty(plan["p_total"] + voff, device=dev),
                  "reduced": torch.empty(plan["p_total"] + voff, device=dev),
-                 "q_local": torch.empty(max(plan["q_total"], 1), device=dev)}
+                 "max_rows": max([n for (_, n, _, _, _, _) in plan["hi"]] or [1]),
+                 "q_local": torch.empty(max(plan["q_total"], 1) * nat.cuda().gc_cuda_psgd_q_chunks(
+                     max([n for (_, n, _, _, _, _) in plan["hi"]] or [1])), device=dev)}
         reducer._psgd_cache = cache
         return cache
 
@@ -246,7 +248,8 @@ class FusedEngine:
                           "psgd_gs")
             with reducer._timer("reduce.compute.q", verbosity=2):
                 nat.check(lib.gc_cuda_psgd_q(e.data_ptr(), c["tab"].data_ptr(), c["n_mats"], c["tiles"],
-                                             c["reduced"].data_ptr(), c["q_local"].data_ptr(), st()), "psgd_q")
+                                             c["reduced"].data_ptr(), c["q_local"].data_ptr(), q_total, c["max_rows"],
+                                             st()), "psgd_q")
             with reducer._timer("reduce.q", verbosity=2):
                 ops.small_sum(c["q_local"][:max(q_total, 1)], reducer.q_memory[:max(q_total, 1)] if q_total else c["q_local"],
                               alpha=1.0 / reducer.n_workers)
