@@ -1,0 +1,299 @@
+// TF32 GEMM on the 5th-generation tensor cores:  C[M, N] (fp32) = A[M, K] * B[N, K]^T (+ bias[N]),
+// A and B row-major with K contiguous ("K-major"), fp32 in memory, kind::tf32 in the MMA (the tensor core
+// reads the upper 19 bits of every fp32 word -- the same precision cuDNN uses for the reference's
+// convolutions).  Shapes this serves: 1x1 convolutions on channels-last activations (A = activations
+// [N*H*W, Cin], B = weight [Cout, Cin]), linear layers, and PowerSGD's P = M Q with Q stored transposed.
+//
+// One CTA per 128 x BN output tile, no clusters, no multicast:
+//   warp 0   TMA producer: cp.async.bulk.tensor.2d (128-byte swizzle) into a ring of shared-memory stages
+//   warp 1   allocates TMEM, issues tcgen05.mma (one elected thread), commits stages back to the producer
+//   warps 2-5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator from TMEM, bias add, global stores
+// Every mbarrier wait is bounded; when one runs out the CTA sets *error_flag, abandons its tile, frees
+// its TMEM and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // 32 fp32 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;                    // tf32
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t addr = smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 63u) == 63u) {
+      if (*abort_flag) return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand tile in the canonical 128-byte-swizzled layout (rows of 128 B, groups of 8 rows = 1024 B).
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);      // start address, bits [0, 14)
+  d |= (uint64_t)1 << 16;                                // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: 8 rows * 128 B
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                                // layout type: SWIZZLE_128B
+  return d;
+}
+
+// kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4)                 // C format: F32
+         | (2u << 7)               // A format: TF32
+         | (2u << 10)              // B format: TF32
+         | ((uint32_t)(n >> 3) << 17)
+         | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_c), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+struct Smem {
+  static constexpr int STAGES = (BN <= 64) ? 6 : 4;
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int B_STRIDE = (B_BYTES + 1023) / 1024 * 1024;     // every stage starts 1024-byte aligned
+  static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_STRIDE);
+  static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 float* __restrict__ C, const float* __restrict__ bias, int M, int N, int K, int64_t ldc,
+                 int* __restrict__ error_flag) {
+  using S = Smem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_tiles = tiles;
+  uint8_t* b_tiles = tiles + S::STAGES * S::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + S::TILE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_ready = empty + S::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int num_k = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int k = 0; k < num_k; ++k) {
+        int s = k % S::STAGES;
+        uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
+        if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) break;
+        mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
+        tma_load_2d(a_tiles + s * S::A_BYTES, &tma_a, k * BK, m0, &full[s]);
+        tma_load_2d(b_tiles + s * S::B_STRIDE, &tma_b, k * BK, n0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      bool ok = true;
+      for (int k = 0; k < num_k && ok; ++k) {
+        int s = k % S::STAGES;
+        uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
+        ok = mbar_wait(&full[s], phase, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        uint64_t adesc = make_smem_desc(a_tiles + s * S::A_BYTES);
+        uint64_t bdesc = make_smem_desc(b_tiles + s * S::B_STRIDE);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // advance both descriptors by 8 fp32 = 32 bytes inside the swizzled row (address field is in 16-byte units)
+          umma_tf32(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);        // the stage may be refilled once these MMAs have read it
+      }
+      umma_commit(acc_ready);          // fires when every MMA issued above has completed
+    }
+  } else {
+    // epilogue warps 2..5 -> TMEM lane groups 2, 3, 0, 1
+    const int lg = warp & 3;
+    bool ok = mbar_wait(acc_ready, 0u, &abort_flag);
+    ok = __all_sync(0xffffffffu, ok);      // the TMEM loads below are warp-collective: decide as a warp
+    tc_fence_after();
+    if (ok && num_k > 0) {
+      const int row = m0 + lg * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, v);   // warp-collective: every lane takes part
+        if (row < M) {
+          float* dst = C + (int64_t)row * ldc + n0 + c0;
+          if (n0 + c0 + 15 < N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (bias != nullptr) {
+                o.x += bias[n0 + c0 + j]; o.y += bias[n0 + c0 + j + 1]; o.z += bias[n0 + c0 + j + 2]; o.w += bias[n0 + c0 + j + 3];
+              }
+              *reinterpret_cast<float4*>(dst + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (n0 + c0 + j < N) dst[j] = v[j] + (bias != nullptr ? bias[n0 + c0 + j] : 0.0f);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_flag != nullptr) atomicExch(error_flag, 1);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D fp32 tensor [rows, cols] with row stride ld (elements); box = box_rows x 32 columns, 128-byte swizzle.
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BN>
+int launch(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda, int64_t ldb,
+           int64_t ldc, int* error_flag, cudaStream_t st) {
+  using S = Smem<BN>;
+  CUtensorMap ma, mb;
+  if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));
+  gemm_tf32_kernel<BN><<<grid, GEMM_THREADS, S::TOTAL, st>>>(ma, mb, C, bias, M, N, K, ldc, error_flag);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+// 1 when the shapes / pointers meet the TMA rules: 16-byte aligned bases, row strides multiples of 16 bytes.
+int gc_cuda_gemm_tf32_supported(const void* A, const void* B, int M, int N, int K, int64_t lda, int64_t ldb) {
+  if (M < 1 || N < 1 || K < 1) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u)) return 0;
+  if ((lda & 3) || (ldb & 3) || lda < K || ldb < K) return 0;
+  return encode_fn() != nullptr ? 1 : 0;
+}
+
+// C[M, N] = A[M, K] * B[N, K]^T (+ bias[N]); error_flag (device int, may be NULL) is set when a wait ran out.
+int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
+                      int64_t ldb, int64_t ldc, int* error_flag, void* cs) {
+  if (!gc_cuda_gemm_tf32_supported(A, B, M, N, K, lda, ldb)) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)cs;
+  if (N <= 16) return launch<16>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
+  if (N <= 64) return launch<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
+  return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,61 @@
+"""TF32 tensor-core GEMM (``csrc/gc_gemm_tc.cu``: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue).
+
+``gemm_tf32(a, b_nk, bias=None)`` returns ``a @ b_nk.T (+ bias)`` for row-major fp32 ``a [M, K]`` and
+``b_nk [N, K]``.  On CPU (and for shapes the TMA rules exclude) it is a plain fp32 matmul.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as nat
+
+_err = {}
+
+
+class TensorCoreTimeout(RuntimeError):
+    pass
+
+
+def _error_flag(device):
+    key = (device.type, device.index)
+    if key not in _err:
+        _err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err[key]
+
+
+def supported(a, b_nk):
+    if not (a.is_cuda and b_nk.is_cuda and a.dtype == torch.float32 and b_nk.dtype == torch.float32):
+        return False
+    if a.dim() != 2 or b_nk.dim() != 2 or a.shape[1] != b_nk.shape[1] or a.stride(1) != 1 or b_nk.stride(1) != 1:
+        return False
+    return bool(nat.cuda().gc_cuda_gemm_tf32_supported(a.data_ptr(), b_nk.data_ptr(), a.shape[0], b_nk.shape[0], a.shape[1],
+                                                       a.stride(0), b_nk.stride(0)))
+
+
+def gemm_tf32(a, b_nk, bias=None, out=None):
+    if not supported(a, b_nk):
+        y = a @ b_nk.t()
+        if bias is not None:
+            y = y + bias
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    m, k = a.shape
+    n = b_nk.shape[0]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float32, device=a.device)
+    assert out.stride(1) == 1
+    with torch.cuda.device(a.device):
+        nat.check(nat.cuda().gc_cuda_gemm_tf32(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nat.ptr(bias), m, n, k,
+                                               a.stride(0), b_nk.stride(0), out.stride(0), _error_flag(a.device).data_ptr(),
+                                               nat.stream_ptr()), "gemm_tf32")
+    return out
+
+
+def check(device="cuda"):
+    """Raise if any GEMM since the last check gave up on a wait (synchronises)."""
+    flag = _error_flag(torch.device(device) if not isinstance(device, torch.device) else device)
+    if int(flag.item()) != 0:
+        flag.zero_()
+        raise TensorCoreTimeout("a tcgen05 GEMM abandoned a tile after a bounded wait ran out")
