@@ -50,6 +50,7 @@ def parse_args():
     p.add_argument("--backend", default="auto", choices=["auto", "fused", "dist"])
     p.add_argument("--graph", type=int, default=1, help="capture the training step in a CUDA graph (ours)")
     p.add_argument("--channels-last", type=int, default=1)
+    p.add_argument("--cudnn-benchmark", type=int, default=1, help="let cuDNN autotune its convolution algorithms (ours)")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
 
@@ -151,6 +152,7 @@ def run_ours(args, world, rank, local_rank):
 
     device = torch.device("cuda", local_rank)
     set_seed(42)
+    torch.backends.cudnn.benchmark = bool(args.cudnn_benchmark)
     steps_needed = args.steps + args.warmup + 2
     task = CIFAR(device, None, args.model, seed=42, data="synthetic",
                  synthetic_train_size=args.batch * world * steps_needed, synthetic_test_size=args.batch,
@@ -204,7 +206,7 @@ def run_ours(args, world, rank, local_rank):
                "h2d_bytes_per_step": args.batch * 3 * 32 * 32 * 4 + args.batch * 8, "d2h_bytes_per_step": 4,
                "last_loss": loss_host}
     extra = {"graph": step_fn.graphed, "backend": getattr(reducer, "backend", "auto"),
-             "fused": bool(getattr(reducer, "_fused", None)), "channels_last": bool(args.channels_last),
+             "fused": bool(getattr(reducer, "_fused", None)), "channels_last": bool(args.channels_last), "cudnn_benchmark": bool(args.cudnn_benchmark),
              "conv_path": "cudnn (torch) -- scaffolding", "wire_bits_per_step": getattr(reducer, "last_wire_bits", None)}
     return dev_ms, launches, clocks, e2e, extra
 

@@ -97,21 +97,20 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int BN>
 struct Smem {
-  static constexpr int STAGES = (BN <= 64) ? 6 : 4;
+  // ring depth chosen so that two CTAs fit on one SM (<= ~100 KB each): while one CTA drains its accumulator
+  // through the epilogue, the other one's TMA loads and MMAs keep the SM busy
+  static constexpr int STAGES = (BN <= 16) ? 5 : ((BN <= 64) ? 4 : 3);
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int B_STRIDE = (B_BYTES + 1023) / 1024 * 1024;     // every stage starts 1024-byte aligned
@@ -121,7 +120,7 @@ struct Smem {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 2)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  float* __restrict__ C, const float* __restrict__ bias, int M, int N, int K, int64_t ldc,
                  int* __restrict__ error_flag) {
@@ -196,27 +195,40 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc_fence_after();
     if (ok && num_k > 0) {
       const int row = m0 + lg * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)c0, v);   // warp-collective: every lane takes part
-        if (row < M) {
-          float* dst = C + (int64_t)row * ldc + n0 + c0;
-          if (n0 + c0 + 15 < N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(lg * 32) << 16);
+      auto store16 = [&](const uint32_t (&r)[16], int c0) {
+        if (row >= M) return;
+        float* dst = C + (int64_t)row * ldc + n0 + c0;
+        if (n0 + c0 + 15 < N && ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0)) {
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (bias != nullptr) {
-                o.x += bias[n0 + c0 + j]; o.y += bias[n0 + c0 + j + 1]; o.z += bias[n0 + c0 + j + 2]; o.w += bias[n0 + c0 + j + 3];
-              }
-              *reinterpret_cast<float4*>(dst + j) = o;
+          for (int j = 0; j < 16; j += 4) {
+            float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            if (bias != nullptr) {
+              o.x += bias[n0 + c0 + j]; o.y += bias[n0 + c0 + j + 1]; o.z += bias[n0 + c0 + j + 2]; o.w += bias[n0 + c0 + j + 3];
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (n0 + c0 + j < N) dst[j] = v[j] + (bias != nullptr ? bias[n0 + c0 + j] : 0.0f);
+            *reinterpret_cast<float4*>(dst + j) = o;
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (n0 + c0 + j < N) dst[j] = __uint_as_float(r[j]) + (bias != nullptr ? bias[n0 + c0 + j] : 0.0f);
         }
+      };
+      if (BN >= 32) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {     // two TMEM loads in flight, then 128 bytes of stores per thread
+          uint32_t ra[16], rb[16];
+          tmem_ld16_nowait(lane_base + (uint32_t)c0, ra);
+          tmem_ld16_nowait(lane_base + (uint32_t)(c0 + 16), rb);
+          tmem_ld_wait();
+          store16(ra, c0);
+          store16(rb, c0 + 16);
+        }
+      } else {
+        uint32_t ra[16];
+        tmem_ld16_nowait(lane_base, ra);
+        tmem_ld_wait();
+        store16(ra, 0);
       }
     }
   }

@@ -114,10 +114,12 @@ class FusedEngine:
         return cls(reducer)
 
     def _ensure(self, n):
-        if self.ops is None or n > self._n:
-            arena = shared_arena(comm.required_bytes(n), self.device, self.group)
+        # the arena is shared by every reducer of this device / group and may have been regrown by another
+        # one since the last call: always go through the registry, never keep a stale handle
+        arena = shared_arena(comm.required_bytes(n), self.device, self.group)
+        if self.ops is None or self.ops.arena is not arena:
             self.ops = FusedOps(arena)
-            self._n = n
+        self._n = max(self._n, n)
         return self.ops
 
     @staticmethod
