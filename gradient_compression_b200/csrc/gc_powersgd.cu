@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(256) psgd_gs_kernel(float* __restrict__ p, con
 // ------------------------------------------------------------------------------------------ Q' = M^T P
 // Block = one 128-column tile of one matrix; thread (c = tid % 32, rl = tid / 32) owns columns 4c..4c+3 of the
 // tile and rows rl, rl + 8, ...; the eight row lanes are combined through shared memory in a fixed order.
-constexpr int Q_ROWCHUNK = 2048;   // rows per block along grid.y (one chunk covers every ResNet / VGG layer)
+constexpr int Q_ROWCHUNK = 1024;   // rows per block along grid.y
 
 __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e /* holds M = G + E */,
                                                      const int64_t* __restrict__ tab, int n_mats,
@@ -183,20 +183,38 @@ __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e
   const int row_hi = row_lo + Q_ROWCHUNK < mt.n ? row_lo + Q_ROWCHUNK : mt.n;
   float* qdst = qout + (int64_t)blockIdx.y * q_total;     // chunk y writes its own partial copy
   if (k0 < mt.m) {
-    for (int row = row_lo + rl; row < row_hi; row += 8) {
-      float v[4];
-      int64_t base = mt.off + (int64_t)row * mt.m + k0;
-      if (vec) {
-        float4 a = *reinterpret_cast<const float4*>(e + base);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-      } else {
+    if (vec) {
+      // four rows (8 apart) per iteration: four independent 16-byte loads in flight per thread
+      for (int row = row_lo + rl; row < row_hi; row += 32) {
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int rr = row + 8 * u;
+          a[u] = rr < row_hi ? *reinterpret_cast<const float4*>(e + mt.off + (int64_t)rr * mt.m + k0) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          int rr = row + 8 * u;
+          if (rr >= row_hi) break;
+          float v[4] = {a[u].x, a[u].y, a[u].z, a[u].w};
+          for (int j = 0; j < mt.r; ++j) {
+            float pv = pm[(int64_t)rr * mt.r + j];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) acc[t][j] = fmaf(v[t], pv, acc[t][j]);
+          }
+        }
+      }
+    } else {
+      for (int row = row_lo + rl; row < row_hi; row += 8) {
+        float v[4];
+        int64_t base = mt.off + (int64_t)row * mt.m + k0;
 #pragma unroll
         for (int t = 0; t < 4; ++t) v[t] = (k0 + t < mt.m) ? e[base + t] : 0.f;
-      }
-      for (int j = 0; j < mt.r; ++j) {
-        float pv = pm[(int64_t)row * mt.r + j];
+        for (int j = 0; j < mt.r; ++j) {
+          float pv = pm[(int64_t)row * mt.r + j];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) acc[t][j] = fmaf(v[t], pv, acc[t][j]);
+          for (int t = 0; t < 4; ++t) acc[t][j] = fmaf(v[t], pv, acc[t][j]);
+        }
       }
     }
   }

@@ -119,6 +119,13 @@ def cuda():
         _declare(lib, "gc_cuda_topk_select", c_int, [P, P, P, c_int, c_i64, P, P, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_supported", c_int, [P, P, c_int, c_int, c_int, c_i64, c_i64])
         _declare(lib, "gc_cuda_gemm_tf32", c_int, [P, P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, P, P])
+        _declare(lib, "gc_cuda_varpack_workspace_bytes", c_i64, [c_i64])
+        _declare(lib, "gc_cuda_varpack_plan", c_int, [P, c_i64, P, P, P, P])
+        _declare(lib, "gc_cuda_varpack_emit", c_int, [P, c_i64, P, P, P])
+        _declare(lib, "gc_cuda_bytepack", c_int, [P, c_i64, P, P])
+        _declare(lib, "gc_cuda_byteunpack", c_int, [P, c_i64, P, P])
+        _declare(lib, "gc_cuda_varunpack_counts", c_int, [P, c_i64, P, P])
+        _declare(lib, "gc_cuda_varunpack_emit", c_int, [P, c_i64, P, P, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])

@@ -180,3 +180,36 @@ def test_topk_reducers_fused_match_cpu():
         for key in (("cuda", "dist"), ("cuda", "fused")):
             assert torch.equal(res[key][0], res[("cpu", "dist")][0]), (name, key)
             assert torch.equal(res[key][1], res[("cpu", "dist")][1]), (name, key)
+
+
+@pytest.mark.parametrize("n", [1, 14, 15, 16, 255, 256, 257, 4099, (1 << 20) + 5])
+@pytest.mark.parametrize("scale", [1, 3, 15, 100, 255])
+def test_varpack_gpu_matches_host_packer(n, scale):
+    from gradient_compression_b200.ops import packing
+
+    g = torch.Generator().manual_seed(n * 7 + scale)
+    src = torch.randint(0, scale + 1, (n,), generator=g, dtype=torch.int32)
+    if n > 300:
+        src[100:140] = 0            # long runs of small values next to large ones: every mode shows up
+        src[200] = 255
+    host_words = packing.varpack(src)
+    dev_words = packing.varpack(src.cuda())
+    assert torch.equal(dev_words.cpu(), host_words)
+    assert torch.equal(packing.varunpack(dev_words, n).cpu(), src)
+    assert torch.equal(packing.varunpack(dev_words).cpu(), packing.varunpack(host_words))
+
+
+def test_varpack_gpu_rejects_out_of_range():
+    from gradient_compression_b200.ops import packing
+
+    with pytest.raises(ValueError):
+        packing.varpack(torch.tensor([1, 2, 300], dtype=torch.int32, device="cuda"))
+
+
+def test_bytepack_gpu_matches_host():
+    from gradient_compression_b200.ops import packing
+
+    src = torch.randint(-128, 128, (100003,), dtype=torch.int32)
+    w_host, w_dev = packing.bytepack(src), packing.bytepack(src.cuda())
+    assert torch.equal(w_dev.cpu(), w_host)
+    assert torch.equal(packing.byteunpack(w_dev, src.numel()).cpu(), src)
