@@ -112,7 +112,7 @@ __global__ void bn_stats_finalize_kernel(const float* __restrict__ partials, con
   double dmean = sums[0] / (double)M;              // mean of the shifted values
   double var = sums[1] / (double)M - dmean * dmean;
   if (var < 0.0) var = 0.0;
-  double mean = (double)x[c] + dmean;
+  double mean = (x != nullptr ? (double)x[c] : 0.0) + dmean;     // x == NULL: the partials are unshifted sums
   stats[c] = (float)mean;
   stats[C + c] = (float)(1.0 / sqrt(var + (double)eps));
   if (running_mean != nullptr) {
@@ -286,6 +286,14 @@ int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* sta
   size_t smem = 2 * BN_THREADS * sizeof(float4);
   bn_stats_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(x, M, C, rpb, (float*)scratch);
   bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, x, grid, M, C, stats,
+                                                                                  running_mean, running_var, momentum, eps);
+  return (int)cudaGetLastError();
+}
+
+// Statistics from partial column sums produced elsewhere (the GEMM epilogue): partials[nparts][2][C], unshifted.
+int gc_cuda_bn_finalize_partials(const float* partials, int nparts, int64_t M, int C, float* stats, float* running_mean,
+                                 float* running_var, float momentum, float eps, void* cs) {
+  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>(partials, nullptr, nparts, M, C, stats,
                                                                                   running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }

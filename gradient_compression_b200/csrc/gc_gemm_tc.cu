@@ -7,7 +7,9 @@
 // One CTA per 128 x BN output tile, no clusters, no multicast:
 //   warp 0   TMA producer: cp.async.bulk.tensor.2d (128-byte swizzle) into a ring of shared-memory stages
 //   warp 1   allocates TMEM, issues tcgen05.mma (one elected thread), commits stages back to the producer
-//   warps 2-5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator from TMEM, bias add, global stores
+//   warps 2-5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator from TMEM, bias add, then either a TMA
+//              store of 32-column slabs staged (128-byte swizzled, bank-conflict free) in the drained pipeline
+//              buffers, or plain stores when C does not meet the TMA alignment rules
 // Every mbarrier wait is bounded; when one runs out the CTA sets *error_flag, abandons its tile, frees
 // its TMEM and returns.
 #include <cuda.h>
@@ -110,20 +112,21 @@ template <int BN>
 struct Smem {
   // ring depth chosen so that two CTAs fit on one SM (<= ~100 KB each): while one CTA drains its accumulator
   // through the epilogue, the other one's TMA loads and MMAs keep the SM busy
-  static constexpr int STAGES = (BN <= 16) ? 5 : ((BN <= 64) ? 4 : 3);
+  static constexpr int STAGES = (BN <= 16) ? 5 : ((BN <= 64) ? 4 : ((BN <= 128) ? 3 : 2));
   static constexpr int A_BYTES = BM * BK * 4;
   static constexpr int B_BYTES = BN * BK * 4;
   static constexpr int B_STRIDE = (B_BYTES + 1023) / 1024 * 1024;     // every stage starts 1024-byte aligned
   static constexpr int TILE_BYTES = STAGES * (A_BYTES + B_STRIDE);
-  static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int TOTAL = TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + 1024 /* column sums */;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, int use_tma_store,
                  float* __restrict__ C, const float* __restrict__ bias, int M, int N, int K, int64_t ldc,
-                 int* __restrict__ error_flag) {
+                 float* __restrict__ col_partials, int* __restrict__ error_flag) {
   using S = Smem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -133,6 +136,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint64_t* empty = full + S::STAGES;
   uint64_t* acc_ready = empty + S::STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  float* colsum = reinterpret_cast<float*>(tiles + S::TILE_BYTES + 256);      // [4 row quarters][32 columns][2]
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,12 +194,90 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else {
     // epilogue warps 2..5 -> TMEM lane groups 2, 3, 0, 1
     const int lg = warp & 3;
-    bool ok = mbar_wait(acc_ready, 0u, &abort_flag);
-    ok = __all_sync(0xffffffffu, ok);      // the TMEM loads below are warp-collective: decide as a warp
+    mbar_wait(acc_ready, 0u, &abort_flag);
+    // decide as a group: the TMEM loads are warp-collective and the staged store below synchronises all four
+    // epilogue warps, so either every one of them runs the epilogue or none does
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = abort_flag == 0;
     tc_fence_after();
     if (ok && num_k > 0) {
       const int row = m0 + lg * 32 + lane;
       const uint32_t lane_base = tmem_base + ((uint32_t)(lg * 32) << 16);
+      if (use_tma_store) {
+        // Stage the tile as 32-column slabs of 128 rows x 128 bytes in the (now idle) pipeline buffers, in the
+        // 128-byte swizzle the store descriptor expects: 16-byte chunk c of row r lives at chunk c ^ (r & 7).
+        const int r = lg * 32 + lane;
+        constexpr int SLABS = (BN + 31) / 32;
+        constexpr int CAP = S::TILE_BYTES / (BM * 128);                 // slabs the drained buffers can hold at once
+        constexpr int PER_ROUND = SLABS < CAP ? SLABS : CAP;
+#pragma unroll 1
+        for (int s0 = 0; s0 < SLABS; s0 += PER_ROUND) {
+#pragma unroll 1
+          for (int sl = s0; sl < s0 + PER_ROUND && sl < SLABS; ++sl) {
+            uint8_t* slab = tiles + (sl - s0) * (BM * 128);
+            uint32_t ra[16], rb[16];
+            tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32), ra);
+            if (BN >= 32) tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32 + 16), rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              if (BN < 32 && c >= 4) break;
+              const uint32_t* src = c < 4 ? &ra[c * 4] : &rb[(c - 4) * 4];
+              float4 o = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]), __uint_as_float(src[3]));
+              if (bias != nullptr) {
+                int col = n0 + sl * 32 + c * 4;
+                o.x += col < N ? bias[col] : 0.f; o.y += col + 1 < N ? bias[col + 1] : 0.f;
+                o.z += col + 2 < N ? bias[col + 2] : 0.f; o.w += col + 3 < N ? bias[col + 3] : 0.f;
+              }
+              *reinterpret_cast<float4*>(slab + r * 128 + ((c ^ (r & 7)) << 4)) = o;
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");                     // the four epilogue warps only
+          if (col_partials != nullptr) {
+            // per-column sum and sum of squares over this CTA's 128 rows, read back from the staged slabs:
+            // thread (quarter, col) adds 32 rows of one column; a row of a slab is one conflict-free 128-byte line
+            const int te = (warp - 2) * 32 + lane, col = te & 31, quarter = te >> 5;
+#pragma unroll 1
+            for (int sl = s0; sl < s0 + PER_ROUND && sl < SLABS; ++sl) {
+              const uint8_t* slab = tiles + (sl - s0) * (BM * 128);
+              float sum = 0.f, sq = 0.f;
+#pragma unroll 8
+              for (int rr = quarter * 32; rr < quarter * 32 + 32; ++rr) {
+                float v = *reinterpret_cast<const float*>(slab + rr * 128 + (((col >> 2) ^ (rr & 7)) << 4) + ((col & 3) << 2));
+                v = (m0 + rr < M) ? v : 0.f;
+                sum += v;
+                sq = fmaf(v, v, sq);
+              }
+              colsum[(quarter * 32 + col) * 2] = sum;
+              colsum[(quarter * 32 + col) * 2 + 1] = sq;
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (quarter == 0) {
+                int gc = n0 + sl * 32 + col;
+                if (gc < N) {
+                  float a = colsum[col * 2] + colsum[(32 + col) * 2] + colsum[(64 + col) * 2] + colsum[(96 + col) * 2];
+                  float b = colsum[col * 2 + 1] + colsum[(32 + col) * 2 + 1] + colsum[(64 + col) * 2 + 1] + colsum[(96 + col) * 2 + 1];
+                  col_partials[((int64_t)blockIdx.x * 2) * N + gc] = a;
+                  col_partials[((int64_t)blockIdx.x * 2 + 1) * N + gc] = b;
+                }
+              }
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+          }
+          if (warp == 2 && lane == 0) {
+#pragma unroll 1
+            for (int sl = s0; sl < s0 + PER_ROUND && sl < SLABS; ++sl) {
+              if (n0 + sl * 32 >= N) break;
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&tma_c), "r"(smem_u32(tiles + (sl - s0) * (BM * 128))), "r"(n0 + sl * 32), "r"(m0)
+                           : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging buffers are free again
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+      } else {
       auto store16 = [&](const uint32_t (&r)[16], int c0) {
         if (row >= M) return;
         float* dst = C + (int64_t)row * ldc + n0 + c0;
@@ -230,6 +312,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_wait();
         store16(ra, 0);
       }
+      }
     }
   }
   tc_fence_before();
@@ -257,6 +340,10 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D fp32 tensor [rows, cols] with row stride ld (elements); box = box_rows x 32 columns, 128-byte swizzle.
+int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows);
+
+bool tma_store_ok(const float* C, int64_t ldc) { return (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && (ldc & 3) == 0; }
+
 int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -1;
@@ -271,10 +358,15 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, in
 
 template <int BN>
 int launch(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda, int64_t ldb,
-           int64_t ldc, int* error_flag, cudaStream_t st) {
+           int64_t ldc, float* col_partials, int* error_flag, cudaStream_t st) {
   using S = Smem<BN>;
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc;
   if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0) return (int)cudaErrorInvalidValue;
+  int use_tma_store = tma_store_ok(C, ldc) && make_map(&mc, C, M, N, ldc, BM) == 0 ? 1 : 0;
+  if (!use_tma_store) {
+    if (col_partials != nullptr) return (int)cudaErrorInvalidValue;     // the column sums ride the staged epilogue
+    mc = ma;
+  }
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -282,7 +374,7 @@ int launch(const float* A, const float* B, float* C, const float* bias, int M, i
     configured = true;
   }
   dim3 grid((unsigned)((M + BM - 1) / BM), (unsigned)((N + BN - 1) / BN));
-  gemm_tf32_kernel<BN><<<grid, GEMM_THREADS, S::TOTAL, st>>>(ma, mb, C, bias, M, N, K, ldc, error_flag);
+  gemm_tf32_kernel<BN><<<grid, GEMM_THREADS, S::TOTAL, st>>>(ma, mb, mc, use_tma_store, C, bias, M, N, K, ldc, col_partials, error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -298,14 +390,39 @@ int gc_cuda_gemm_tf32_supported(const void* A, const void* B, int M, int N, int 
   return encode_fn() != nullptr ? 1 : 0;
 }
 
+// Tile width: the widest of 256 / 128 / 64 columns that still yields at least ~2 CTAs per SM, so that wide N
+// reads A once while small problems keep all SMs busy.
+static int pick_bn(int M, int N) {
+  if (N <= 16) return 16;
+  if (N <= 64) return 64;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  int64_t mt = (M + BM - 1) / BM;
+  const int cand[3] = {256, 128, 64};
+  for (int i = 0; i < 3; ++i) {
+    int bn = cand[i];
+    if (bn == 256 && N <= 128) continue;
+    if (bn == 128 && N <= 64) continue;
+    if (mt * ((N + bn - 1) / bn) >= 2 * sms) return bn;
+  }
+  return 64;
+}
+
+int gc_cuda_gemm_tf32_m_tiles(int M) { return (M + BM - 1) / BM; }
+
 // C[M, N] = A[M, K] * B[N, K]^T (+ bias[N]); error_flag (device int, may be NULL) is set when a wait ran out.
+// col_partials (may be NULL): [m_tiles][2][N] floats receiving, per 128-row tile, the column sums and sums of
+// squares of C -- the batch-norm statistics of a 1x1 convolution's output without another pass over it.
 int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, int* error_flag, void* cs) {
+                      int64_t ldb, int64_t ldc, float* col_partials, int* error_flag, void* cs) {
   if (!gc_cuda_gemm_tf32_supported(A, B, M, N, K, lda, ldb)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)cs;
-  if (N <= 16) return launch<16>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
-  if (N <= 64) return launch<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
-  return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, error_flag, st);
+  switch (pick_bn(M, N)) {
+    case 16: return launch<16>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+    case 64: return launch<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+    case 128: return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+    default: return launch<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+  }
 }
 
 }  // extern "C"

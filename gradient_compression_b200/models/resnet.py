@@ -7,6 +7,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act
+from ..ops.conv import conv_bn_act
 from .layers import bn, conv, linear
 
 
@@ -20,7 +21,7 @@ class _Projection(nn.Sequential):
     """1x1 convolution + batch norm of a shortcut; children are named "0" and "1" as in the reference."""
 
     def forward(self, x):
-        return bn_act(self[1], self[0](x), relu=False)
+        return conv_bn_act(self[0], self[1], x, relu=False)
 
 
 class BasicBlock(nn.Module):
@@ -48,9 +49,9 @@ class Bottleneck(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        y = bn_act(self.bn1, self.conv1(x))
+        y = conv_bn_act(self.conv1, self.bn1, x)                 # 1x1: tensor-core GEMM with BN statistics in its epilogue
         y = bn_act(self.bn2, self.conv2(y))
-        return bn_act(self.bn3, self.conv3(y), residual=self.shortcut(x))
+        return conv_bn_act(self.conv3, self.bn3, y, residual=self.shortcut(x))
 
 
 class ResNet(nn.Module):

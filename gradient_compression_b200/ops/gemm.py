@@ -32,8 +32,11 @@ def supported(a, b_nk):
                                                        a.stride(0), b_nk.stride(0)))
 
 
-def gemm_tf32(a, b_nk, bias=None, out=None):
+def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None):
+    """``col_partials`` (optional, fp32 [m_tiles, 2, N]): receives per 128-row tile the column sums and sums of
+    squares of the result -- batch-norm statistics of a 1x1 convolution's output for free."""
     if not supported(a, b_nk):
+        assert col_partials is None, "column statistics need the tensor-core path"
         y = a @ b_nk.t()
         if bias is not None:
             y = y + bias
@@ -48,9 +51,13 @@ def gemm_tf32(a, b_nk, bias=None, out=None):
     assert out.stride(1) == 1
     with torch.cuda.device(a.device):
         nat.check(nat.cuda().gc_cuda_gemm_tf32(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nat.ptr(bias), m, n, k,
-                                               a.stride(0), b_nk.stride(0), out.stride(0), _error_flag(a.device).data_ptr(),
-                                               nat.stream_ptr()), "gemm_tf32")
+                                               a.stride(0), b_nk.stride(0), out.stride(0), nat.ptr(col_partials),
+                                               _error_flag(a.device).data_ptr(), nat.stream_ptr()), "gemm_tf32")
     return out
+
+
+def m_tiles(m):
+    return int(nat.cuda().gc_cuda_gemm_tf32_m_tiles(int(m)))
 
 
 def check(device="cuda"):

@@ -94,5 +94,9 @@ def test_bucketed_overlap_on_gpu_matches_serial():
             br.finish()
         torch.cuda.synchronize()
         res[overlap] = arena.flat_grads.clone()
-    # the backward itself is not bit-reproducible run to run only if cuDNN picks atomics; compare loosely
-    assert torch.allclose(res[True], res[False], rtol=1e-3, atol=1e-5)
+    # cuDNN's weight gradients are not bit-reproducible run to run, and a last-bit change can flip a stochastic
+    # rounding: outputs may differ by one quantisation level (bucket max / 255) in a few places, never by more
+    diff = (res[True] - res[False]).abs()
+    level = float(res[False].abs().max()) / 255
+    assert float(diff.max()) <= 1.01 * level
+    assert float((diff > 1e-6).float().mean()) < 0.05

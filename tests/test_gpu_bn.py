@@ -107,3 +107,59 @@ def test_resnet50_step_matches_unfused_model():
     assert abs(loss_f - loss_u) < 1e-4
     assert rel(g_f, g_u) < 2.0 * rel(g_p, g_u) + 1e-3
     assert float((g_f[-1] - g_u[-1]).norm() / g_u[-1].norm()) < 1e-4      # the head's bias gradient is well conditioned
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 32, 32, 256), (16, 256, 8, 8, 64), (8, 512, 4, 4, 2048), (5, 16, 7, 9, 32)])
+@pytest.mark.parametrize("residual", [False, True])
+@pytest.mark.parametrize("relu", [False, True])
+def test_conv1x1_bn_act_matches_torch(shape, residual, relu):
+    """1x1 convolution on the tcgen05 GEMM with BN statistics from its epilogue vs cuDNN conv + torch bn."""
+    from gradient_compression_b200.ops import conv as convmod
+    from gradient_compression_b200.ops.conv import _fusable, conv_bn_act
+
+    convmod.ENABLED = True
+    n, cin, h, w, cout = shape
+    g = torch.Generator().manual_seed(cin + cout)
+    cl = torch.channels_last
+    x = torch.randn(n, cin, h, w, generator=g).cuda().contiguous(memory_format=cl)
+    r = torch.randn(n, cout, h, w, generator=g).cuda().contiguous(memory_format=cl) if residual else None
+    dy = torch.randn(n, cout, h, w, generator=g).cuda().contiguous(memory_format=cl)
+    conv_a = torch.nn.Conv2d(cin, cout, 1, bias=False).cuda().to(memory_format=cl)
+    conv_b = torch.nn.Conv2d(cin, cout, 1, bias=False).cuda().to(memory_format=cl)
+    conv_b.load_state_dict(conv_a.state_dict())
+    bn_a, bn_b = torch.nn.BatchNorm2d(cout).cuda(), torch.nn.BatchNorm2d(cout).cuda()
+    with torch.no_grad():
+        bn_a.weight.copy_(torch.rand(cout, generator=g) + 0.5)
+        bn_a.bias.copy_(torch.randn(cout, generator=g) * 0.1)
+    bn_b.load_state_dict(bn_a.state_dict())
+    assert _fusable(conv_a, bn_a, x)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    ra = r.clone().requires_grad_(True) if residual else None
+    rb = r.clone().requires_grad_(True) if residual else None
+    ya = conv_bn_act(conv_a, bn_a, xa, ra, relu)
+    yb = bn_b(conv_b(xb))
+    if residual:
+        yb = yb + rb
+    if relu:
+        yb = F.relu(yb)
+    ya.backward(dy)
+    yb.backward(dy)
+    from gradient_compression_b200.ops import gemm
+    gemm.check()
+    tol = dict(rtol=5e-3, atol=5e-3)       # both sides multiply in TF32; they round differently
+
+    def close(a, b):
+        """Agreement at TF32 level in the Frobenius norm.  Both sides round operands to 10 mantissa bits, in
+        different summation orders; with ReLU a few pre-activations within rounding distance of zero land on
+        different sides, which changes those elements' gradient by O(dy)."""
+        a, b = a.detach(), b.detach()
+        return float((a - b).norm() / b.norm()) < (6e-2 if relu else 5e-3)
+
+    assert close(ya, yb)
+    assert close(xa.grad, xb.grad)
+    assert close(conv_a.weight.grad, conv_b.weight.grad)
+    assert close(bn_a.weight.grad, bn_b.weight.grad) and close(bn_a.bias.grad, bn_b.bias.grad)
+    if residual:
+        assert close(ra.grad, rb.grad)
+    assert torch.allclose(bn_a.running_mean, bn_b.running_mean, atol=1e-3)
+    assert torch.allclose(bn_a.running_var, bn_b.running_var, rtol=5e-3, atol=1e-3)
