@@ -120,8 +120,31 @@ def case_psgd(n, rank=2):
     return (lambda: red.reduce(views, views)), 4 * tot * 7, "psgd_p (2 reads, 1 write) + psgd_q (1 read) + psgd_out (1 read, 2 writes)"
 
 
+def case_gemm(n):
+    """1x1 convolution of ResNet-50's first stage as a GEMM: [131072, 64] x [256, 64]^T with BN statistics."""
+    from ..ops import gemm
+    m, k, nn = 131072, 64, 256
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(nn, k, device="cuda")
+    out = torch.empty(m, nn, device="cuda")
+    part = torch.empty(gemm.m_tiles(m), 2, nn, device="cuda")
+    return (lambda: gemm.gemm_tf32(a, b, out=out, col_partials=part)), 4 * (m * k + nn * k + m * nn), \
+        "gemm_tf32_kernel<256>: TMA loads, tcgen05.mma kind::tf32, TMEM accumulator, TMA store + column statistics"
+
+
+def case_gemm_deep(n):
+    """Compute-heavier GEMM: [8192, 2048] x [2048, 2048]^T (69 GFLOP)."""
+    from ..ops import gemm
+    m, k, nn = 8192, 2048, 2048
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(nn, k, device="cuda")
+    out = torch.empty(m, nn, device="cuda")
+    return (lambda: gemm.gemm_tf32(a, b, out=out)), 4 * (m * k + nn * k + m * nn), \
+        f"gemm_tf32_kernel: {2 * m * nn * k / 1e9:.0f} GFLOP"
+
+
 CASES = {"qsgd": case_qsgd, "absmax": case_absmax, "sgd": case_sgd, "pack": case_pack, "bn_fwd": case_bn_fwd,
-         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd}
+         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_deep": case_gemm_deep}
 
 
 def main(argv=None):

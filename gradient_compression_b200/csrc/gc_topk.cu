@@ -130,16 +130,31 @@ __global__ void __launch_bounds__(TK_THREADS) topk_compact_kernel(const float* _
   uint32_t thr = state[seg].prefix;
   int32_t need_eq = state[seg].k_rem;
   int64_t n_gt = k - need_eq;
-  for (int64_t i = c0 + threadIdx.x; i < c1; i += TK_THREADS) {
-    float a = e != nullptr ? e[start + i] : g[start + i];
+  const int lane = threadIdx.x & 31;
+  for (int64_t ib = c0; ib < c1; ib += TK_THREADS) {       // uniform trip count: the ballots below need whole warps
+    int64_t i = ib + threadIdx.x;
+    bool valid = i < c1;
+    float a = 0.f;
+    if (valid) a = e != nullptr ? e[start + i] : g[start + i];
     int64_t slot = -1;
     if (all) {
-      slot = i;
+      if (valid) slot = i;
     } else {
       uint32_t key = key_of(a);
-      if (key > thr) slot = (int64_t)atomicAdd(&state[seg].gt_count, 1u);
-      else if (key == thr) {
-        uint32_t q = atomicAdd(&state[seg].eq_count, 1u);
+      bool gt = valid && key > thr, eq = valid && key == thr;
+      // warp-aggregated slot allocation: one atomic per warp and class instead of one per selected element
+      unsigned mgt = __ballot_sync(0xffffffffu, gt), meq = __ballot_sync(0xffffffffu, eq);
+      uint32_t base_gt = 0, base_eq = 0;
+      if (lane == 0) {
+        if (mgt) base_gt = atomicAdd(&state[seg].gt_count, (uint32_t)__popc(mgt));
+        if (meq) base_eq = atomicAdd(&state[seg].eq_count, (uint32_t)__popc(meq));
+      }
+      base_gt = __shfl_sync(0xffffffffu, base_gt, 0);
+      base_eq = __shfl_sync(0xffffffffu, base_eq, 0);
+      unsigned below = (1u << lane) - 1u;
+      if (gt) slot = (int64_t)base_gt + __popc(mgt & below);
+      else if (eq) {
+        uint32_t q = base_eq + (uint32_t)__popc(meq & below);
         if ((int32_t)q < need_eq) slot = n_gt + q;
       }
     }
