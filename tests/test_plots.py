@@ -7,7 +7,7 @@ import pytest
 
 from gradient_compression_b200.utils import plots
 
-REF_LOGS = "/root/reference/logs"
+REF_LOGS = os.path.join(os.environ.get("GRADCOMP_REFERENCE_DIR", "/root/reference"), "logs")
 
 
 def test_performance_model_formula():

@@ -10,6 +10,7 @@ import torch.distributed as dist
 from gradient_compression_b200 import ops, reducers as R
 from gradient_compression_b200.ops import philox
 
+REFERENCE_DIR = os.environ.get("GRADCOMP_REFERENCE_DIR", "/root/reference")
 SHAPES = [(16, 3, 3, 3), (16,), (32, 16, 3, 3), (32,), (10, 32), (10,)]
 CFG = dict(seed=42, K=50, quantization_level=4, higher_quantization_level=8, quantization_levels=[2, 6, 10],
            compression=0.1, rank=2)
@@ -295,7 +296,7 @@ def test_reducers_across_gloo_ranks(dist_runner, world):
 
 # ------------------------------------------------------------------------------- reference as oracle
 def _reference_body(rank, world):
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, REFERENCE_DIR)
     import reducer as ref   # the reference's module, imported unmodified
 
     class _T:               # the reference's Timer interface, doing nothing
@@ -325,6 +326,6 @@ def _reference_body(rank, world):
         assert ours.reduce([t.clone() for t in mine], o) == theirs.reduce([t.clone() for t in mine], o), name
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/reducer.py"), reason="reference sources not mounted")
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_DIR, "reducer.py")), reason="reference sources not mounted")
 def test_parity_with_reference_reducers(dist_runner):
     dist_runner(_reference_body, world=2)
