@@ -1,0 +1,56 @@
+"""Per-kernel device time of one training step under CUDA-graph replay (torch profiler / CUPTI timeline, real
+cache conditions -- unlike ncu, nothing is flushed or serialised).
+
+    python -m gradient_compression_b200.benchmarks.step_profile --model ResNet50
+"""
+import argparse
+import collections
+import re
+
+import torch
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="ResNet50")
+    ap.add_argument("--reducer", default="QSGDMaxNormReducer")
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=5)
+    args = ap.parse_args(argv)
+
+    from .. import make_reducer
+    from ..parallel import FlatSGD
+    from ..parallel.graph import GraphedStep
+    from ..train import CIFAR
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.backends.cudnn.benchmark = True
+    dev = torch.device("cuda:0")
+    task = CIFAR(dev, None, args.model, seed=0, data="synthetic", synthetic_train_size=2 * args.batch,
+                 synthetic_test_size=args.batch)
+    opt = FlatSGD(task.arena, lr=0.1)
+    red = make_reducer(args.reducer, dev, None, {"quantization_level": 8, "seed": 1})
+    step = GraphedStep(task, red, opt, enabled=True)
+    x = torch.randn(args.batch, 3, 32, 32, device=dev).contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (args.batch,), device=dev)
+    for _ in range(8):
+        step((x, y))
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(args.steps):
+            step((x, y))
+        torch.cuda.synchronize()
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if ev.device_type == torch.autograd.DeviceType.CUDA:
+            name = re.sub(r"<.*", "", ev.name)[:80]
+            agg[name][0] += 1
+            agg[name][1] += ev.device_time
+    total = sum(v[1] for v in agg.values())
+    print(f"graphed: {step.graphed}; device time per step: {total / args.steps:.1f} us")
+    for name, (cnt, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:40]:
+        print(f"{t / args.steps:9.1f} us {cnt // args.steps:4d}  {name}")
+
+
+if __name__ == "__main__":
+    main()
