@@ -412,6 +412,139 @@ __global__ void __launch_bounds__(THREADS, 2) twoscale_fused_kernel(LaunchViews 
   }
 }
 
+// ------------------------------------------------------------------------------------------ multi-scale (L <= 4)
+// Per element every rank finds the finest scale l whose stochastically rounded level still fits the coarsest
+// scale's range (|q_l| <= s_0); the ranks agree on the MINIMUM index (reference: all-reduce MIN of an int8 array,
+// reducer.py:1680) through two bit planes in peer memory; everyone then sends the level of the agreed scale.
+struct MultiScaleParams {
+  Common c;
+  int n_levels;
+  int s[4];
+  int64_t off_mags, off_signs, off_sums, off_idx_local[2], off_idx_final[2];
+  int64_t chunk_rows;
+};
+
+template <int MW, int SUMB>
+__global__ void __launch_bounds__(THREADS, 2) multiscale_fused_kernel(LaunchViews lv, MultiScaleParams p) {
+  __shared__ float smem[32];
+  Ctx c = make_ctx(lv);
+  const RankView& v = *c.v;
+  Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
+  const uint32_t epoch = next_epoch(c.hdr);
+  const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
+  const int64_t n = p.c.n;
+  const int world = p.c.world;
+  const int L = p.n_levels;
+  const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
+  const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
+  const int64_t rows = (n + 127) / 128;
+  uint8_t* my = v.arena[v.rank];
+
+  float m = rank_max(w, local_absmax(c, v.in, n, al_in), c.bid, c.nblocks, smem, 0x80);
+  commit_epoch(c.hdr, epoch, c.bid);
+  float norm = (world > 1) ? exchange_max(w, v, world, epoch, m, c.bid == 0, smem) : m;
+  float sc[4], dq[4];
+#pragma unroll
+  for (int l = 0; l < 4; ++l) {
+    sc[l] = (l < L && norm > 0.0f) ? (float)p.s[l] / norm : 0.0f;
+    dq[l] = l < L ? dequant_scale(norm, p.s[l], world) : 0.0f;
+  }
+  auto level_of = [&](float x, int l, uint64_t blk, int j) {
+    U4 r = philox_block(rng_key(p.c, rng_step, v.rank, PURPOSE_LEVEL0 + (uint32_t)l), blk);
+    uint32_t rnd = j == 0 ? r.x : (j == 1 ? r.y : (j == 2 ? r.z : r.w));
+    return quantize_level(x, sc[l], p.s[l], rnd);
+  };
+  // finest scale whose rounded level fits the coarsest range (scale 0 always fits)
+  auto local_index = [&](float x, uint64_t blk, int j) {
+    int idx = 0;
+    for (int l = 1; l < L; ++l)
+      if (abs(level_of(x, l, blk, j)) <= p.s[0]) idx = l;
+    return idx;
+  };
+
+  if (world > 1) {
+    for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+      int64_t e0 = row * 128 + c.lane * 4;
+      float4 x = load_quad(v.in, e0, n, al_in);
+      float xs[4] = {x.x, x.y, x.z, x.w};
+      bool b0[4], b1[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int idx = local_index(xs[j], (uint64_t)(e0 >> 2), j);
+        b0[j] = idx & 1;
+        b1[j] = (idx >> 1) & 1;
+      }
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_idx_local[0]), row, c.lane, b0);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_idx_local[1]), row, c.lane, b1);
+    }
+    grid_barrier(w, c.nblocks, 0x81);
+    if (c.bid == 0) signal_all(v, world, PH_MASK, epoch);
+    wait_all(w, world, PH_MASK, epoch);
+  }
+
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int64_t e0 = row * 128 + c.lane * 4;
+    float4 x = load_quad(v.in, e0, n, al_in);
+    float xs[4] = {x.x, x.y, x.z, x.w};
+    int idx[4];
+    if (world > 1) {
+      uint32_t p0 = load_plane_all_ranks(v, world, p.off_idx_local[0], row, c.lane);
+      uint32_t p1 = load_plane_all_ranks(v, world, p.off_idx_local[1], row, c.lane);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idx[j] = 3;
+#pragma unroll
+      for (int src = 0; src < MAXW; ++src)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t w0 = __shfl_sync(FULL, p0, src * 4 + j), w1 = __shfl_sync(FULL, p1, src * 4 + j);
+          int r = (int)((w0 >> c.lane) & 1u) | ((int)((w1 >> c.lane) & 1u) << 1);
+          if (src < world) idx[j] = r < idx[j] ? r : idx[j];
+        }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idx[j] = local_index(xs[j], (uint64_t)(e0 >> 2), j);
+    }
+    int q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = level_of(xs[j], idx[j], (uint64_t)(e0 >> 2), j);
+    if (world == 1) {
+      float4 y = make_float4(mul_rn(dq[idx[0]], (float)q[0]), mul_rn(dq[idx[1]], (float)q[1]),
+                             mul_rn(dq[idx[2]], (float)q[2]), mul_rn(dq[idx[3]], (float)q[3]));
+      store_quad(v.out, e0, n, al_out, y);
+    } else {
+      int mg[4] = {abs(q[0]), abs(q[1]), abs(q[2]), abs(q[3])};
+      bool sg[4] = {q[0] < 0, q[1] < 0, q[2] < 0, q[3] < 0};
+      bool b0[4] = {(idx[0] & 1) != 0, (idx[1] & 1) != 0, (idx[2] & 1) != 0, (idx[3] & 1) != 0};
+      bool b1[4] = {(idx[0] & 2) != 0, (idx[1] & 2) != 0, (idx[2] & 2) != 0, (idx[3] & 2) != 0};
+      store_row_mags<MW>(my + p.off_mags, row, c.lane, mg);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_signs), row, c.lane, sg);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_idx_final[0]), row, c.lane, b0);
+      store_row_plane(reinterpret_cast<uint32_t*>(my + p.off_idx_final[1]), row, c.lane, b1);
+    }
+  }
+  if (world == 1) return;
+  grid_barrier(w, c.nblocks, 0x82);
+  if (c.bid == 0) signal_all(v, world, PH_READY, epoch);
+  wait_all(w, world, PH_READY, epoch);
+
+  reduce_scatter_rows<MW, SUMB>(c, world, rows, p.chunk_rows, p.off_mags, p.off_signs, p.off_sums);
+  grid_barrier(w, c.nblocks, 0x83);
+  if (c.bid == 0) signal_all(v, world, PH_DONE, epoch);
+  wait_all(w, world, PH_DONE, epoch);
+
+  for (int64_t row = c.warp; row < rows; row += c.nwarps) {
+    int a[4];
+    bool b0[4], b1[4];
+    load_row_sums<SUMB>(my + p.off_sums, row, c.lane, a);
+    load_row_plane(reinterpret_cast<const uint32_t*>(my + p.off_idx_final[0]), row, c.lane, b0);
+    load_row_plane(reinterpret_cast<const uint32_t*>(my + p.off_idx_final[1]), row, c.lane, b1);
+    float y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) y[j] = mul_rn(dq[(b0[j] ? 1 : 0) | (b1[j] ? 2 : 0)], (float)a[j]);
+    store_quad(v.out, row * 128 + c.lane * 4, n, al_out, make_float4(y[0], y[1], y[2], y[3]));
+  }
+}
+
 // ------------------------------------------------------------------------------------------ fp32 all-reduce
 struct AllreduceParams {
   Common c;
@@ -779,7 +912,7 @@ int gc_comm_max_world() { return MAXW; }
 // Bytes of arena needed by the largest fused op on an n-element gradient.
 int64_t gc_comm_required_bytes(int64_t n) {
   int64_t npad = pad128(n);
-  int64_t qsgd = mag_bytes(npad, 16) + 3 * plane_bytes(npad) + npad * 4;   // mags(16b) + signs + 2 masks + int32 sums
+  int64_t qsgd = mag_bytes(npad, 16) + 5 * plane_bytes(npad) + npad * 4 + 8 * 256;   // mags(16b) + signs + 4 index planes + int32 sums
   int64_t ar = 2 * npad * 4;                                               // fp32 stage + result
   int64_t need = qsgd > ar ? qsgd : ar;
   return ARENA_HEADER_BYTES + need + 4096;
@@ -894,6 +1027,7 @@ int gc_comm_destroy(void* ctx) {
   }
 GC_KERNEL_TABLE(qsgd_kernel_for, qsgd_fused_kernel)
 GC_KERNEL_TABLE(twoscale_kernel_for, twoscale_fused_kernel)
+GC_KERNEL_TABLE(multiscale_kernel_for, multiscale_fused_kernel)
 
 // One QSGD-MaxNorm reduce step.  ctxs: n_virtual contexts (1 in multi-GPU runs; all ranks of an
 // emulated group otherwise); ins / outs: one gradient pointer per context.
@@ -939,6 +1073,38 @@ int gc_fused_twoscale(void** ctxs_, int n_virtual, const float* const* ins, floa
   int64_t rows = npad / 128;
   p.chunk_rows = (rows + world - 1) / world;
   const void* kern = twoscale_kernel_for(mw, sumb);
+  if (kern == nullptr) return (int)cudaErrorInvalidValue;
+  LaunchViews lv;
+  if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)
+    return (int)cudaErrorInvalidValue;
+  p.c = make_common(ctxs, n_virtual, n, seed, step, timeout_ms);
+  return coop_launch(kern, lv, p, (cudaStream_t)cs);
+}
+
+// levels: n_levels ascending bit widths (2 <= n_levels <= 4); values on the wire never exceed 2^levels[0] - 1.
+int gc_fused_multiscale(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n,
+                        const int* levels, int n_levels, uint64_t seed, uint32_t step, int timeout_ms, int max_blocks,
+                        void* cs) {
+  CommCtx** ctxs = (CommCtx**)ctxs_;
+  if (n_levels < 1 || n_levels > 4) return (int)cudaErrorInvalidValue;
+  int world = ctxs[0]->world;
+  MultiScaleParams p;
+  p.n_levels = n_levels;
+  for (int l = 0; l < 4; ++l) p.s[l] = l < n_levels ? (1 << levels[l]) - 1 : 0;
+  int mw = mag_width(levels[0]), sumb = sum_container_bytes(p.s[0], world);
+  int64_t npad = pad128(n), off = ARENA_HEADER_BYTES;
+  auto take = [&](int64_t bytes) { int64_t r = off; off = align_up(off + bytes, 256); return r; };
+  p.off_mags = take(mag_bytes(npad, mw));
+  p.off_signs = take(plane_bytes(npad));
+  p.off_idx_local[0] = take(plane_bytes(npad));
+  p.off_idx_local[1] = take(plane_bytes(npad));
+  p.off_idx_final[0] = take(plane_bytes(npad));
+  p.off_idx_final[1] = take(plane_bytes(npad));
+  p.off_sums = take(npad * sumb);
+  if (off > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  int64_t rows = npad / 128;
+  p.chunk_rows = (rows + world - 1) / world;
+  const void* kern = multiscale_kernel_for(mw, sumb);
   if (kern == nullptr) return (int)cudaErrorInvalidValue;
   LaunchViews lv;
   if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)

@@ -399,3 +399,28 @@ int64_t gc_host_elias_decode(const int64_t* src, int64_t n_words, float* norm_ov
 }
 
 }  // extern "C"
+
+#include "gc_augment.h"
+
+extern "C" {
+
+// out: [batch, 32, 32, 3] fp32 (NHWC); images: [n_images, 32, 32, 3] uint8; sample b of the batch is image
+// perm(first_slot + b) of the keyed permutation of [0, n_images) (identity when shuffle == 0).
+void gc_host_augment(const uint8_t* images, const int64_t* labels, int64_t n_images, uint64_t seed, uint32_t epoch,
+                     int64_t first_slot, int64_t slot_stride, int batch, int train, int shuffle, const float* mean,
+                     const float* inv_std, float* out, int64_t* out_labels) {
+  PermKey pk = make_perm_key((uint64_t)n_images, seed, epoch);
+  for (int b = 0; b < batch; ++b) {
+    uint64_t slot = (uint64_t)(first_slot + (int64_t)b * slot_stride);
+    uint64_t src = shuffle ? perm_eval(pk, slot % (uint64_t)n_images) : slot % (uint64_t)n_images;
+    AugmentDraw d = augment_draw(seed, epoch, slot);
+    const uint8_t* img = images + src * 3072;
+    for (int y = 0; y < 32; ++y)
+      for (int x = 0; x < 32; ++x)
+        for (int c = 0; c < 3; ++c)
+          out[(((int64_t)b * 32 + y) * 32 + x) * 3 + c] = augment_pixel(img, d, y, x, c, mean[c], inv_std[c], train != 0);
+    out_labels[b] = labels[src];
+  }
+}
+
+}  // extern "C"

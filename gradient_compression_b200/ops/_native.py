@@ -62,6 +62,7 @@ def host():
         _declare(lib, "gc_host_gram_schmidt", None, [P, c_i64, c_int, c_float])
         _declare(lib, "gc_host_topk_abs", None, [P, c_i64, c_i64, P])
         _declare(lib, "gc_host_sgd_step", None, [P, P, P, c_i64, c_float, c_float, c_float, c_int])
+        _declare(lib, "gc_host_augment", None, [P, P, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int, c_int, P, P, P, P])
         _declare(lib, "gc_host_elias_encode", c_i64, [P, c_i64, c_float, P, c_i64])
         _declare(lib, "gc_host_elias_decode", c_i64, [P, c_i64, P, P, c_i64])
         _host = lib
@@ -128,6 +129,7 @@ def cuda():
         _declare(lib, "gc_cuda_byteunpack", c_int, [P, c_i64, P, P])
         _declare(lib, "gc_cuda_varunpack_counts", c_int, [P, c_i64, P, P])
         _declare(lib, "gc_cuda_varunpack_emit", c_int, [P, c_i64, P, P, P])
+        _declare(lib, "gc_cuda_augment", c_int, [P, P, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int, c_int, P, P, P, P, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])
@@ -145,6 +147,7 @@ def cuda():
         _declare(lib, "gc_fused_qsgd", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_u64, c_u32, c_int, c_int, P])
         _declare(lib, "gc_fused_twoscale", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, c_u64, c_u32, c_int,
                                                    c_int, P])
+        _declare(lib, "gc_fused_multiscale", c_int, [PP, c_int, PP, PP, c_i64, P, c_int, c_u64, c_u32, c_int, c_int, P])
         _declare(lib, "gc_fused_allreduce", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, P])
         _declare(lib, "gc_fused_small_sum", c_int, [PP, c_int, PP, PP, c_i64, c_float, c_int, c_int, P])
         _declare(lib, "gc_fused_randk", c_int, [PP, c_int, PP, PP, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int,

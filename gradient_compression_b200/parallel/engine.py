@@ -46,6 +46,15 @@ class FusedOps:
                                                                     self.timeout_ms, self.max_blocks,
                                                                     nat.stream_ptr()))
 
+    def multiscale(self, ins, outs, levels, seed, step):
+        import ctypes
+        ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        lv = (ctypes.c_int * len(levels))(*[int(b) for b in levels])
+        with torch.cuda.device(self.arena.device):
+            self._run("fused_multiscale", nat.cuda().gc_fused_multiscale(ctxs, nv, ia, oa, ins[0].numel(), lv, len(levels),
+                                                                        int(seed), int(step), self.timeout_ms,
+                                                                        self.max_blocks, nat.stream_ptr()))
+
     def allreduce(self, ins, outs):
         ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
         with torch.cuda.device(self.arena.device):
@@ -161,6 +170,19 @@ class FusedEngine:
                          reducer._noise.seed, reducer._noise.next_step())
         self._finish(flat, grad_out, dest, tmp)
         container = 8 if reducer._lower_quantization_level < 8 else 32
+        return 32 + 8 * n + container * n
+
+    def qsgd_multiscale(self, reducer, flat, grad_out):
+        levels = reducer._quantization_levels
+        if not (2 <= len(levels) <= 4):
+            return None
+        n = flat.buffer.numel()
+        ops = self._ensure(n)
+        dest, tmp = self._out_flat(flat, grad_out)
+        with reducer._timer("reduce.fused", verbosity=2):
+            ops.multiscale(flat.buffer, dest, levels, reducer._noise.seed, reducer._noise.next_step())
+        self._finish(flat, grad_out, dest, tmp)
+        container = 8 if levels[0] < 8 else 32
         return 32 + 8 * n + container * n
 
     def allreduce_mean(self, reducer, flat, grad_out):

@@ -47,3 +47,8 @@ def powersgd(reducer, flat, grad_out, plan, fresh):
 def sparse(reducer, flat, grad_out, idx, vals):
     eng = _engine(reducer)
     return eng.sparse(reducer, flat, grad_out, idx, vals) if eng else False
+
+
+def qsgd_multiscale(reducer, flat, grad_out):
+    eng = _engine(reducer)
+    return eng.qsgd_multiscale(reducer, flat, grad_out) if eng else None

@@ -70,6 +70,8 @@ class QSGDMaxNormMultiScaleReducer(Reducer):
     """L scales: per element the finest scale index that fits on every worker (MIN all-reduce of the
     int8 index array), then the agreed scale's levels are summed (reducer.py:1636-1715)."""
 
+    fused_capable = True
+
     def __init__(self, device, timer=None, quantization_levels=None, **kw):
         super().__init__(device, timer, **kw)
         self._quantization_levels = sorted(quantization_levels or [6, 10])
@@ -80,6 +82,11 @@ class QSGDMaxNormMultiScaleReducer(Reducer):
     def reduce(self, grad_in, grad_out):
         with self._timer("reduce.flat_pack"):
             flat = TensorBuffer(grad_in)
+        if self._use_fused():
+            from ..parallel import fused
+            bits = fused.qsgd_multiscale(self, flat, grad_out)
+            if bits is not None:
+                return bits
         with self._timer("reduce.norm", verbosity=2):
             max_norm = self._global_max(ops.absmax(flat.buffer))
         with self._timer("reduce.compress", verbosity=2):

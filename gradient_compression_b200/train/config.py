@@ -35,7 +35,7 @@ class TrainConfig:
     backend: str = "auto"             # reducer backend: auto | fused | dist
     reference_compat: bool = False
     broadcast_parameters: bool = True  # the reference never synchronises replicas
-    data: str = "cifar10"             # cifar10 | synthetic
+    data: str = "cifar10"             # cifar10 | synthetic | cifar10_device | synthetic_device
     data_path: str = "./data"
     synthetic_train_size: int = 50000
     synthetic_test_size: int = 10000

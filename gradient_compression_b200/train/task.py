@@ -4,8 +4,8 @@ Same public interface as the reference's ``CIFAR`` (``parameters``, ``train_data
 ``test_dataloader``, ``batch_loss``, ``batch_loss_with_gradients``, ``evaluate_predictions``,
 ``state_dict``, ``test``, ``len_train_loader``).  Additions: parameters, gradients and momentum live
 in one ``FlatArena``; metrics are returned as device tensors (no ``.item()`` sync inside the step)
-unless ``sync_metrics=True``; data may be synthetic; host->device copies are non-blocking from
-pinned memory.
+unless ``sync_metrics=True``; data may be synthetic or fully device-resident (``data="cifar10_device"`` /
+``"synthetic_device"``: one augmentation kernel per batch); host->device copies are non-blocking from pinned memory.
 """
 from __future__ import annotations
 
@@ -58,6 +58,17 @@ class CIFAR:
     def _load_dataset(self, kind, data_path, n_train, n_test):
         if kind == "synthetic":
             return D.SyntheticCIFAR(n_train, self._seed * 2 + 1), D.SyntheticCIFAR(n_test, self._seed * 2 + 2)
+        if kind in ("synthetic_device", "cifar10_device"):
+            # whole dataset resident on the device; one augmentation kernel per batch, no loader workers
+            from .gpu_data import DeviceCIFAR
+            if kind == "synthetic_device":
+                return (DeviceCIFAR.synthetic(n_train, self._device, self._seed * 2 + 1, train=True),
+                        DeviceCIFAR.synthetic(n_test, self._device, self._seed * 2 + 2, train=False))
+            import torchvision
+            tr = torchvision.datasets.CIFAR10(root=data_path, train=True, download=False)
+            te = torchvision.datasets.CIFAR10(root=data_path, train=False, download=False)
+            return (DeviceCIFAR.from_torchvision(tr, self._device, self._seed, train=True),
+                    DeviceCIFAR.from_torchvision(te, self._device, self._seed, train=False))
         train, test = D.load_cifar10(data_path)
         return D.TorchvisionLoaders(train, shuffle=True), D.TorchvisionLoaders(test, shuffle=True)
 
@@ -81,8 +92,8 @@ class CIFAR:
         self._epoch += 1
 
     def test_dataloader(self, batch_size=32):
-        loader = (self._test_set.loader(batch_size, 0, shuffle=False, drop_last=False) if self._data_kind == "synthetic"
-                  else self._test_set.loader(batch_size, 0))
+        loader = (self._test_set.loader(batch_size, 0, shuffle=False, drop_last=False)
+                  if self._data_kind in ("synthetic", "synthetic_device", "cifar10_device") else self._test_set.loader(batch_size, 0))
         self.len_test_loader = len(loader)
         for imgs, labels in loader:
             yield self._to_device(imgs, labels)

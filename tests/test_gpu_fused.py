@@ -95,6 +95,45 @@ def test_fused_twoscale_emulated(world, n, lo, hi):
         grp.close()
 
 
+def _oracle_multiscale(xs, levels, seed, step):
+    world = len(xs)
+    s = [(1 << b) - 1 for b in levels]
+    norm = max(float(x.abs().max()) for x in xs)
+    q = [[ops.quantize_levels(x, norm, s[l], seed, philox.stream_id(r, philox.PURPOSE_LEVEL0 + l), step) for l in range(len(s))]
+         for r, x in enumerate(xs)]
+    idx = None
+    for r in range(world):
+        mine = torch.zeros_like(q[r][0])
+        for l in range(1, len(s)):
+            mine[q[r][l].abs() <= s[0]] = l
+        idx = mine if idx is None else torch.minimum(idx, mine)
+    tot = torch.zeros_like(q[0][0])
+    for r in range(world):
+        for l in range(len(s)):
+            tot += torch.where(idx == l, q[r][l], torch.zeros_like(tot))
+    out = torch.zeros(xs[0].numel())
+    for l in range(len(s)):
+        out = torch.where(idx == l, ops.dequantize_levels(tot.to(torch.int32), norm, s[l], world), out)
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("n,levels", [(4099, [2, 6]), (100003, [2, 6, 10]), (100003, [4, 8, 12, 16]), (50001, [8, 12])])
+def test_fused_multiscale_emulated(world, n, levels):
+    grp, fo = _group(world, n)
+    try:
+        xs = _inputs(world, n, n + len(levels))
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        for step in range(2):
+            fo.multiscale([x.cuda() for x in xs], outs, levels, 5, step)
+            fo.check()
+            expect = _oracle_multiscale(xs, levels, 5, step)
+            for o in outs:
+                assert torch.equal(o.cpu(), expect)
+    finally:
+        grp.close()
+
+
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 @pytest.mark.parametrize("n", [5, 4099, (1 << 20) + 3])
 def test_fused_allreduce_emulated(world, n):

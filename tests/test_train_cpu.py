@@ -171,3 +171,12 @@ def test_resume_continues_where_it_stopped(tmp_path):
     for k in a["model"]:
         assert torch.allclose(a["model"][k].float(), c["model"][k].float(), atol=1e-6), k
     assert torch.allclose(a["optimizer"]["momentum_buf"], c["optimizer"]["momentum_buf"], atol=1e-6)
+
+
+def test_trainer_with_device_resident_pipeline(tmp_path):
+    cfg = TrainConfig(runs=1, num_epochs=1, batch_size=8, architecture="LeNet", reducer="NoneAllReducer",
+                      data="synthetic_device", synthetic_train_size=32, synthetic_test_size=16, log_verbosity=0,
+                      timer_mode="sync", lr=0.01, log_root=str(tmp_path))
+    lg = train(0, cfg, logger=Logger(cfg.as_dict(), 0, log_path=str(tmp_path / "run")))
+    log = np.load(os.path.join(lg.log_path, "log_dict.npy"), allow_pickle=True).item()
+    assert np.isfinite(log["train_loss"]).all() and np.isfinite(log["test_loss"]).all()
