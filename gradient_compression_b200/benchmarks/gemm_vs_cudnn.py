@@ -1,9 +1,10 @@
 """tcgen05 TF32 GEMM (``ops.gemm_tf32``) against cuDNN's 1x1 convolution on the ResNet-50 (CIFAR, batch 128) shapes.
 
-    python -m gradient_compression_b200.benchmarks.gemm_vs_cudnn
+    python -m gradient_compression_b200.benchmarks.gemm_vs_cudnn [--sweep]
 
 One JSON line per shape: CUDA-event medians, L2 flushed between launches.
 """
+import argparse
 import json
 
 import torch
@@ -33,6 +34,9 @@ def _median_us(fn, flush, iters=10, warmup=3):
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sweep", action="store_true", help="also time both kernels at every tile width")
+    args = ap.parse_args()
     torch.backends.cudnn.benchmark = True
     flush = torch.zeros(64 << 20, device="cuda")
     for (m, k, n) in SHAPES:
@@ -42,14 +46,27 @@ def main():
         a = x.permute(0, 2, 3, 1).reshape(m, k)
         b = w.view(n, k)
         out = torch.empty(m, n, device="cuda")
+        sweep = {}
+        if args.sweep:                        # every kernel / tile width, to calibrate the choice
+            for kernel in ("tile", "persistent"):
+                for tile_n in (64, 128, 256):
+                    if tile_n // 2 >= n:
+                        continue
+                    gemm.configure(kernel, tile_n)
+                    sweep[f"{kernel}{tile_n}"] = round(_median_us(lambda: gemm.gemm_tf32(a, b, out=out), flush, iters=6), 1)
+            gemm.configure("tile", 0)
+            sweep["tile_auto"] = round(_median_us(lambda: gemm.gemm_tf32(a, b, out=out), flush, iters=6), 1)
+        gemm.configure("auto", 0)
         t_ours = _median_us(lambda: gemm.gemm_tf32(a, b, out=out), flush)
+        parts = torch.empty(gemm.m_tiles(m), 2, n, device="cuda")
+        t_stats = _median_us(lambda: gemm.gemm_tf32(a, b, out=out, col_partials=parts), flush)
         t_cudnn = _median_us(lambda: torch.nn.functional.conv2d(x, w), flush)
         ref = torch.nn.functional.conv2d(x, w).permute(0, 2, 3, 1).reshape(m, n)
         err = float((out - ref).abs().max() / ref.abs().max())
         nbytes = 4 * (m * k + n * k + m * n)
-        print(json.dumps({"M": m, "K": k, "N": n, "ours_us": round(t_ours, 1), "cudnn_us": round(t_cudnn, 1),
+        print(json.dumps({"M": m, "K": k, "N": n, "ours_us": round(t_ours, 1), "ours_with_bn_stats_us": round(t_stats, 1), "cudnn_us": round(t_cudnn, 1),
                           "ours_GBs": round(nbytes / t_ours / 1e3), "ours_TFLOPs": round(2 * m * n * k / t_ours / 1e6, 1),
-                          "relerr_vs_cudnn": err}))
+                          "relerr_vs_cudnn": err, **({"sweep_us": sweep} if sweep else {})}))
     gemm.check()
 
 

@@ -129,7 +129,17 @@ def case_gemm(n):
     out = torch.empty(m, nn, device="cuda")
     part = torch.empty(gemm.m_tiles(m), 2, nn, device="cuda")
     return (lambda: gemm.gemm_tf32(a, b, out=out, col_partials=part)), 4 * (m * k + nn * k + m * nn), \
-        "gemm_tf32_kernel<256>: TMA loads, tcgen05.mma kind::tf32, TMEM accumulator, TMA store + column statistics"
+        "gemm_tf32_persistent_kernel<256>: TMA loads, tcgen05.mma kind::tf32, double-buffered TMEM accumulator, TMA store + column statistics"
+
+
+def case_gemm_narrow(n):
+    """[131072, 64] x [64, 64]^T: the narrowest 1x1 convolution of the first stage (67 MB of traffic, 1 GFLOP)."""
+    from ..ops import gemm
+    m, k, nn = 131072, 64, 64
+    a = torch.randn(m, k, device="cuda")
+    b = torch.randn(nn, k, device="cuda")
+    out = torch.empty(m, nn, device="cuda")
+    return (lambda: gemm.gemm_tf32(a, b, out=out)), 4 * (m * k + nn * k + m * nn), "gemm_tf32_persistent_kernel<64>"
 
 
 def case_gemm_deep(n):
@@ -144,7 +154,8 @@ def case_gemm_deep(n):
 
 
 CASES = {"qsgd": case_qsgd, "absmax": case_absmax, "sgd": case_sgd, "pack": case_pack, "bn_fwd": case_bn_fwd,
-         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_deep": case_gemm_deep}
+         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_narrow": case_gemm_narrow,
+         "gemm_deep": case_gemm_deep}
 
 
 def main(argv=None):

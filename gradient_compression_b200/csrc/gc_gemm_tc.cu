@@ -324,6 +324,242 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (threadIdx.x == 0 && abort_flag && error_flag != nullptr) atomicExch(error_flag, 1);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Persistent variant: one CTA per SM walks a strided list of output tiles.  The accumulator is double
+// buffered in TMEM (2 x BN columns), so the MMA warp works on tile i + 1 while the epilogue warps drain
+// tile i; the TMA loads run ahead across tile boundaries through the same ring of stages; two groups of
+// four epilogue warps take alternate 32-column slabs, each group staging them in its own ring of dedicated
+// buffers and waiting for a TMA store only when it needs that store's buffer back.  Tiles are ordered
+// with the column tile fastest: CTAs that run at the same time share the rows of A in L2.
+template <int BN>
+struct PSmem {
+  static constexpr int STAGES = (BN <= 64) ? 5 : ((BN <= 128) ? 4 : 3);
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;               // a multiple of 1024 for BN >= 8
+  static constexpr int NSLAB = 4;
+  static constexpr int SLAB_BYTES = BM * 128;
+  static constexpr int RING_BYTES = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int STAGING_OFF = RING_BYTES;
+  static constexpr int BAR_OFF = STAGING_OFF + NSLAB * SLAB_BYTES;
+  static constexpr int COLSUM_OFF = BAR_OFF + 256;
+  static constexpr int TOTAL = 1024 /* alignment slack */ + COLSUM_OFF + 4 * BN * 2 * 4;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static_assert(BN == 64 || BN == 128 || BN == 256, "tile widths of the persistent kernel");
+  static_assert(TOTAL <= 232448, "shared memory of one CTA");
+};
+
+// Named barrier of one epilogue group (ids 1 and 2; 0 is __syncthreads).
+__device__ __forceinline__ void group_bar(int grp) {
+  if (grp == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+  else asm volatile("bar.sync 2, 128;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+constexpr int EPI_GROUPS = 2;
+constexpr int PERSISTENT_THREADS = 64 + 128 * EPI_GROUPS;
+
+template <int BN>
+__global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
+gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                            const __grid_constant__ CUtensorMap tma_c, const float* __restrict__ bias, int M, int N, int K,
+                            int tiles_m, int tiles_n, float* __restrict__ col_partials, int* __restrict__ error_flag) {
+  using S = PSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_tiles = base;
+  uint8_t* b_tiles = base + S::STAGES * S::A_BYTES;
+  uint8_t* staging = base + S::STAGING_OFF;
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + S::BAR_OFF);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_full = empty + S::STAGES;      // [2] MMA -> epilogue: accumulator complete
+  uint64_t* acc_empty = acc_full + 2;          // [2] epilogue -> MMA: accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* colsum = reinterpret_cast<float*>(base + S::COLSUM_OFF);      // [4 row quarters][BN columns][2]
+  __shared__ int abort_flag;
+  __shared__ int epi_go[EPI_GROUPS];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_k = (K + BK - 1) / BK;
+  const int total_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int g = 0; g < EPI_GROUPS; ++g) epi_go[g] = 1;
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128 * EPI_GROUPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;                                        // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const int s = (int)(it % S::STAGES);
+          const uint32_t phase = (it / S::STAGES) & 1u;
+          if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
+          tma_load_2d(a_tiles + s * S::A_BYTES, &tma_a, k * BK, m0, &full[s]);
+          tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, k * BK, n0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      uint32_t it = 0, lt = 0;                                // k-blocks consumed, tiles started
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+        const uint32_t buf = lt & 1u, aphase = (lt >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], aphase ^ 1u, &abort_flag)) break;      // first use of a buffer passes at once
+        tc_fence_after();
+        const uint32_t tmem_c = tmem_base + buf * (uint32_t)BN;
+        for (int k = 0; k < num_k; ++k, ++it) {
+          const int s = (int)(it % S::STAGES);
+          const uint32_t phase = (it / S::STAGES) & 1u;
+          if (!mbar_wait(&full[s], phase, &abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(a_tiles + s * S::A_BYTES);
+          const uint64_t bdesc = make_smem_desc(b_tiles + s * S::B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_tf32(tmem_c, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // Two epilogue groups of four warps (TMEM lane quarters warp & 3); group g drains the 32-column slabs
+    // g, g + 2, ... of every tile through its own half of the staging ring, with its own named barrier and its
+    // own store-issuing thread, so the groups never wait for each other.
+    const int ew = warp - 2;
+    const int grp = ew >> 2;
+    const int lg = warp & 3;
+    const int r = lg * 32 + lane;                              // row of the tile this thread owns
+    const int te = (ew & 3) * 32 + lane;                       // 0..127 inside the group
+    const bool issuer = te == 0;                               // owns the group's bulk store groups
+    constexpr int SLABS = BN / 32;
+    constexpr int RING = S::NSLAB / EPI_GROUPS;                // staging buffers per group
+    uint8_t* my_staging = staging + grp * (RING * S::SLAB_BYTES);
+    float* my_colsum = colsum;                                 // [4 row quarters][BN][2]; a group only touches its slabs' columns
+    uint32_t lt = 0, sc = 0;                                   // tiles drained, slabs staged by this group
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
+      const int mi = t / tiles_n;
+      const int m0 = mi * BM, n0 = (t % tiles_n) * BN;
+      const uint32_t buf = lt & 1u, aphase = (lt >> 1) & 1u;
+      const bool got = mbar_wait(&acc_full[buf], aphase, &abort_flag);
+      // one thread decides for the group: the TMEM loads are warp-collective and the named barriers below
+      // involve all four warps, so either every one of them drains this tile or none does
+      if (issuer) epi_go[grp] = (got && abort_flag == 0) ? 1 : 0;
+      group_bar(grp);
+      if (!epi_go[grp]) break;
+      tc_fence_after();
+      const uint32_t lane_base = tmem_base + ((uint32_t)(lg * 32) << 16) + buf * (uint32_t)BN;
+      const bool full_rows = m0 + BM <= M;
+#pragma unroll 1
+      for (int sl = grp; sl < SLABS; sl += EPI_GROUPS, ++sc) {
+        uint8_t* slab = my_staging + (sc % RING) * S::SLAB_BYTES;
+        // the store that last read this buffer was committed RING groups ago
+        if (issuer) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(RING - 1) : "memory");
+        group_bar(grp);
+        uint32_t ra[16], rb[16];
+        tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32), ra);
+        tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32 + 16), rb);
+        tmem_ld_wait();
+        if (sl + EPI_GROUPS >= SLABS) {                        // this thread has read its share of the accumulator
+          tc_fence_before();
+          mbar_arrive(&acc_empty[buf]);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t* src = c < 4 ? &ra[c * 4] : &rb[(c - 4) * 4];
+          float4 o = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]), __uint_as_float(src[3]));
+          if (bias != nullptr) {
+            int col = n0 + sl * 32 + c * 4;
+            o.x += col < N ? bias[col] : 0.f; o.y += col + 1 < N ? bias[col + 1] : 0.f;
+            o.z += col + 2 < N ? bias[col + 2] : 0.f; o.w += col + 3 < N ? bias[col + 3] : 0.f;
+          }
+          *reinterpret_cast<float4*>(slab + r * 128 + ((c ^ (r & 7)) << 4)) = o;     // 128-byte swizzle of the store map
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        group_bar(grp);
+        if (issuer) {
+          if (n0 + sl * 32 < N)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                         ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
+                         : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");              // one group per slab, empty ones included
+        }
+        if (col_partials != nullptr) {
+          // sum and sum of squares of 32 rows of one column, read back from the staged slab (a row of a slab is
+          // one 128-byte line: conflict free); four independent chains each
+          const int col = te & 31, quarter = te >> 5;
+          const uint8_t* colbase = slab + (quarter * 32) * 128 + ((col & 3) << 2);
+          const int chunk = col >> 2;
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+          if (full_rows) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float v0 = *reinterpret_cast<const float*>(colbase + (j + 0) * 128 + ((chunk ^ ((j + 0) & 7)) << 4));
+              float v1 = *reinterpret_cast<const float*>(colbase + (j + 1) * 128 + ((chunk ^ ((j + 1) & 7)) << 4));
+              float v2 = *reinterpret_cast<const float*>(colbase + (j + 2) * 128 + ((chunk ^ ((j + 2) & 7)) << 4));
+              float v3 = *reinterpret_cast<const float*>(colbase + (j + 3) * 128 + ((chunk ^ ((j + 3) & 7)) << 4));
+              s0 += v0; s1 += v1; s2 += v2; s3 += v3;
+              q0 = fmaf(v0, v0, q0); q1 = fmaf(v1, v1, q1); q2 = fmaf(v2, v2, q2); q3 = fmaf(v3, v3, q3);
+            }
+          } else {
+#pragma unroll 4
+            for (int j = 0; j < 32; ++j) {
+              float v = *reinterpret_cast<const float*>(colbase + j * 128 + ((chunk ^ (j & 7)) << 4));
+              v = (m0 + quarter * 32 + j < M) ? v : 0.f;
+              s0 += v;
+              q0 = fmaf(v, v, q0);
+            }
+          }
+          my_colsum[(quarter * BN + sl * 32 + col) * 2] = (s0 + s1) + (s2 + s3);
+          my_colsum[(quarter * BN + sl * 32 + col) * 2 + 1] = (q0 + q1) + (q2 + q3);
+        }
+      }
+      if (col_partials != nullptr) {
+        group_bar(grp);
+        for (int idx = te; idx < (SLABS / EPI_GROUPS) * 32; idx += 128) {       // the columns of this group's slabs
+          const int c = (grp + EPI_GROUPS * (idx >> 5)) * 32 + (idx & 31);
+          const int gc = n0 + c;
+          if (gc < N) {
+            float a = (my_colsum[c * 2] + my_colsum[(BN + c) * 2]) + (my_colsum[(2 * BN + c) * 2] + my_colsum[(3 * BN + c) * 2]);
+            float b = (my_colsum[c * 2 + 1] + my_colsum[(BN + c) * 2 + 1]) + (my_colsum[(2 * BN + c) * 2 + 1] + my_colsum[(3 * BN + c) * 2 + 1]);
+            col_partials[((int64_t)mi * 2) * N + gc] = a;
+            col_partials[((int64_t)mi * 2 + 1) * N + gc] = b;
+          }
+        }
+      }
+    }
+    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory outlives the stores
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_flag != nullptr) atomicExch(error_flag, 1);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -356,6 +592,16 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, in
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
 template <int BN>
 int launch(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda, int64_t ldb,
            int64_t ldc, float* col_partials, int* error_flag, cudaStream_t st) {
@@ -378,6 +624,30 @@ int launch(const float* A, const float* B, float* C, const float* bias, int M, i
   return (int)cudaGetLastError();
 }
 
+template <int BN>
+int launch_persistent(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
+                      int64_t ldb, int64_t ldc, float* col_partials, int* error_flag, cudaStream_t st) {
+  using S = PSmem<BN>;
+  CUtensorMap ma, mb, mc;
+  if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0 || make_map(&mc, C, M, N, ldc, BM) != 0)
+    return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tf32_persistent_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  int64_t total = (int64_t)tiles_m * tiles_n;
+  int64_t grid = total < sm_count() ? total : sm_count();
+  gemm_tf32_persistent_kernel<BN><<<(unsigned)grid, PERSISTENT_THREADS, S::TOTAL, st>>>(ma, mb, mc, bias, M, N, K, tiles_m, tiles_n,
+                                                                                 col_partials, error_flag);
+  return (int)cudaGetLastError();
+}
+
+// 0 = choose, 1 = one tile per CTA, 2 = persistent;  tile width 0 = choose
+int g_kernel_choice = 0, g_tile_choice = 0;
+
 }  // namespace
 
 extern "C" {
@@ -390,13 +660,12 @@ int gc_cuda_gemm_tf32_supported(const void* A, const void* B, int M, int N, int 
   return encode_fn() != nullptr ? 1 : 0;
 }
 
-// Tile width: the widest of 256 / 128 / 64 columns that still yields at least ~2 CTAs per SM, so that wide N
-// reads A once while small problems keep all SMs busy.
+// Tile width of the one-tile-per-CTA kernel: the widest of 256 / 128 / 64 columns that still yields at least
+// ~2 CTAs per SM, so that wide N reads A once while small problems keep all SMs busy.
 static int pick_bn(int M, int N) {
   if (N <= 16) return 16;
   if (N <= 64) return 64;
-  int sms = 148;
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  int sms = sm_count();
   int64_t mt = (M + BM - 1) / BM;
   const int cand[3] = {256, 128, 64};
   for (int i = 0; i < 3; ++i) {
@@ -408,7 +677,38 @@ static int pick_bn(int M, int N) {
   return 64;
 }
 
+// Tile width of the persistent kernel: the candidate with the lowest modelled time.  A tile costs the larger of
+// its DRAM share (C written once, A read once per row of tiles) and its shared-memory fill (A and B per
+// k-block), plus a fixed start-up; CTAs work through ceil(tiles / SMs) tiles one after the other.
+static int pick_bn_persistent(int M, int N, int K) {
+  int sms = sm_count();
+  int64_t mt = (M + BM - 1) / BM;
+  const int cand[3] = {256, 128, 64};
+  int best = 64;
+  double best_t = 1e30;
+  for (int i = 0; i < 3; ++i) {
+    int bn = cand[i];
+    if (bn == 256 && N <= 128) continue;
+    if (bn == 128 && N <= 64) continue;
+    int64_t nt = (N + bn - 1) / bn;
+    int64_t waves = (mt * nt + sms - 1) / sms;
+    double dram = (double)BM * bn * 4.0 + (double)BM * K * 4.0 / (double)nt;      // bytes per tile
+    double fill = (double)(BM + bn) * K * 4.0;
+    double t_tile = dram / 40.0;                                                    // ~40 B/ns of DRAM per SM
+    if (fill / 110.0 > t_tile) t_tile = fill / 110.0;                               // ~110 B/ns from L2 into one SM
+    double t = (double)waves * (t_tile + 300.0);
+    if (t < best_t) { best_t = t; best = bn; }
+  }
+  return best;
+}
+
 int gc_cuda_gemm_tf32_m_tiles(int M) { return (M + BM - 1) / BM; }
+
+// For measurements: kernel 0 = choose, 1 = one tile per CTA, 2 = persistent; tile width 0 = choose, else 64 / 128 / 256.
+void gc_cuda_gemm_tf32_config(int kernel, int tile_n) {
+  g_kernel_choice = kernel;
+  g_tile_choice = tile_n;
+}
 
 // C[M, N] = A[M, K] * B[N, K]^T (+ bias[N]); error_flag (device int, may be NULL) is set when a wait ran out.
 // col_partials (may be NULL): [m_tiles][2][N] floats receiving, per 128-row tile, the column sums and sums of
@@ -417,7 +717,17 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
                       int64_t ldb, int64_t ldc, float* col_partials, int* error_flag, void* cs) {
   if (!gc_cuda_gemm_tf32_supported(A, B, M, N, K, lda, ldb)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)cs;
-  switch (pick_bn(M, N)) {
+  bool persistent = g_kernel_choice != 1 && N > 16 && tma_store_ok(C, ldc);
+  if (persistent) {
+    int bn = g_tile_choice ? g_tile_choice : pick_bn_persistent(M, N, K);
+    switch (bn) {
+      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+      default: return (int)cudaErrorInvalidValue;
+    }
+  }
+  switch (g_tile_choice && N > 16 ? g_tile_choice : pick_bn(M, N)) {
     case 16: return launch<16>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
     case 64: return launch<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
     case 128: return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);

@@ -56,6 +56,15 @@ def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None):
     return out
 
 
+KERNELS = {"auto": 0, "tile": 1, "persistent": 2}
+
+
+def configure(kernel="auto", tile_n=0):
+    """Pin the kernel ("tile": one output tile per CTA; "persistent": one CTA per SM with a double-buffered TMEM
+    accumulator) and the tile width (64 / 128 / 256; 0 = choose) -- for measurements and tests."""
+    nat.cuda().gc_cuda_gemm_tf32_config(KERNELS[kernel], int(tile_n))
+
+
 def m_tiles(m):
     return int(nat.cuda().gc_cuda_gemm_tf32_m_tiles(int(m)))
 

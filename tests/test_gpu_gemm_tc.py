@@ -67,3 +67,55 @@ def test_gemm_into_strided_and_unaligned_outputs():
     gemm.gemm_tf32(a, b, out=odd[:, :72])
     gemm.check()
     assert torch.equal(odd[:, :72], ref) and float(odd[:, 72:].abs().max()) == 0.0
+
+
+@pytest.fixture
+def gemm_choice():
+    from gradient_compression_b200.ops import gemm
+
+    yield gemm.configure
+    gemm.configure("auto", 0)
+
+
+@pytest.mark.parametrize("kernel,tile_n", [("tile", 64), ("tile", 128), ("tile", 256), ("persistent", 64), ("persistent", 128),
+                                           ("persistent", 256)])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 32), (1000, 256, 576), (4096, 512, 64), (300, 200, 100), (20000, 320, 96),
+                                   (131, 40, 2048), (38000, 64, 64)])
+def test_both_kernels_every_tile_width(gemm_choice, kernel, tile_n, m, n, k):
+    """Exact on small-integer inputs (TF32 represents them, fp32 sums are exact): any mix-up of tiles, accumulator
+    buffers, staging slabs or pipeline phases shows as a wrong entry.  The larger cases give every CTA of the
+    persistent kernel several tiles, so both TMEM buffers and the whole staging ring are reused."""
+    from gradient_compression_b200.ops import gemm
+
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float().cuda()
+    b = torch.randint(-4, 5, (n, k), generator=g).float().cuda()
+    bias = torch.randint(-9, 10, (n,), generator=g).float().cuda()
+    ref = a.double() @ b.double().t() + bias.double()
+    gemm_choice(kernel, tile_n)
+    out = torch.full((m, n), float("nan"), device="cuda")
+    gemm.gemm_tf32(a, b, bias, out=out)
+    gemm.check()
+    assert torch.equal(out.double(), ref)
+    # column statistics of the same product
+    parts = torch.full((gemm.m_tiles(m), 2, n), float("nan"), device="cuda")
+    out2 = torch.empty(m, n, device="cuda")
+    gemm.gemm_tf32(a, b, bias, out=out2, col_partials=parts)
+    gemm.check()
+    assert torch.equal(out2.double(), ref)
+    assert torch.equal(parts[:, 0].double().sum(0), ref.sum(0))
+    assert torch.allclose(parts[:, 1].double().sum(0), (ref * ref).sum(0), rtol=1e-5)
+
+
+@pytest.mark.parametrize("kernel", ["tile", "persistent"])
+def test_chosen_tile_width_random_inputs(gemm_choice, kernel):
+    from gradient_compression_b200.ops import gemm
+
+    gemm_choice(kernel, 0)
+    for (m, n, k) in [(131072, 64, 64), (32768, 512, 128), (8192, 256, 1024), (2048, 2048, 512)]:
+        a = torch.randn(m, k, device="cuda")
+        b = torch.randn(n, k, device="cuda")
+        ref = (a.double() @ b.double().t()).float()
+        out = gemm.gemm_tf32(a, b)
+        gemm.check()
+        assert float((out - ref).abs().max() / ref.abs().max()) < 3e-3
