@@ -209,9 +209,13 @@ def run_ours(args, world, rank, local_rank):
         e2e = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": args.batch * 3 * 32 * 32 * 4 + args.batch * 8, "d2h_bytes_per_step": 4,
                "last_loss": loss_host}
+    from gradient_compression_b200.ops import conv as conv_ops
+    conv_path = ("1x1 (stride 1, >= %d positions): own tcgen05 TF32 GEMM with BN statistics in the epilogue, forward and "
+                 "input gradient; other convolutions and weight gradients: cuDNN" % conv_ops.MIN_ROWS) if conv_ops.ENABLED \
+        else "cuDNN (torch); own tcgen05 GEMM path off (GCB200_TC_CONV=0)"
     extra = {"graph": step_fn.graphed, "backend": getattr(reducer, "backend", "auto"),
              "fused": bool(getattr(reducer, "_fused", None)), "channels_last": bool(args.channels_last), "cudnn_benchmark": bool(args.cudnn_benchmark),
-             "conv_path": "cudnn (torch) -- scaffolding", "wire_bits_per_step": getattr(reducer, "last_wire_bits", None)}
+             "conv_path": conv_path, "wire_bits_per_step": getattr(reducer, "last_wire_bits", None)}
     return dev_ms, launches, clocks, e2e, extra
 
 

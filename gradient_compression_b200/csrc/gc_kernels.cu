@@ -324,6 +324,36 @@ __global__ void __launch_bounds__(512) sgd_kernel(float* __restrict__ p, const f
 
 #define GC_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+// Transposes of many small row-major matrices in one launch (the [Cout, Cin] weights of 1x1 convolutions
+// -> [Cin, Cout], the K-major operand of the input-gradient GEMM).  Table rows: {src pointer, dst pointer,
+// rows, cols, first tile}; a block moves one 32 x 32 tile through shared memory.
+namespace {
+constexpr int TR_FIELDS = 5;
+__global__ void __launch_bounds__(256) batched_transpose_kernel(const int64_t* __restrict__ tab, int n_seg) {
+  __shared__ float tile[32][33];
+  int lo = 0, hi = n_seg - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (tab[(int64_t)mid * TR_FIELDS + 4] <= (int64_t)blockIdx.x) lo = mid; else hi = mid - 1;
+  }
+  const int64_t* t = tab + (int64_t)lo * TR_FIELDS;
+  const float* __restrict__ src = reinterpret_cast<const float*>(t[0]);
+  float* __restrict__ dst = reinterpret_cast<float*>(t[1]);
+  const int rows = (int)t[2], cols = (int)t[3];
+  const int tiles_c = (cols + 31) / 32;
+  const int local = (int)((int64_t)blockIdx.x - t[4]);
+  const int r0 = (local / tiles_c) * 32, c0 = (local % tiles_c) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8)
+    if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(int64_t)(r0 + j) * cols + c0 + tx];
+  __syncthreads();
+#pragma unroll
+  for (int j = ty; j < 32; j += 8)
+    if (c0 + j < cols && r0 + tx < rows) dst[(int64_t)(c0 + j) * rows + r0 + tx] = tile[tx][j];
+}
+}  // namespace
+
 extern "C" {
 
 int gc_cuda_abi_version() { return 3; }
@@ -458,6 +488,13 @@ int gc_cuda_sgd_step(float* p, const float* g, float* m, int64_t n, const float*
   int threads = 512, grid = grid_for((n + 3) / 4, threads, 4);
   bool al = aligned16(p) && aligned16(g) && aligned16(m);
   sgd_kernel<<<grid, threads, 0, (cudaStream_t)cs>>>(p, g, m, n, al, hyper, nesterov);
+  return GC_LAUNCH_CHECK();
+}
+
+// tab: device table of n_seg rows {src, dst, rows, cols, first tile}; total_tiles = sum of ceil(rows/32) * ceil(cols/32).
+int gc_cuda_batched_transpose(const int64_t* tab, int n_seg, int64_t total_tiles, void* cs) {
+  if (n_seg <= 0 || total_tiles <= 0) return 0;
+  batched_transpose_kernel<<<(unsigned)total_tiles, 256, 0, (cudaStream_t)cs>>>(tab, n_seg);
   return GC_LAUNCH_CHECK();
 }
 

@@ -11,6 +11,7 @@ statistics and read again.  Backward: fused BN backward kernels, input gradient 
 from __future__ import annotations
 
 import os
+import weakref
 
 import torch
 
@@ -18,9 +19,83 @@ from . import _native as nat
 from . import gemm
 from .bn import _cl, _scratch_for, bn_act, kernel_path_ok
 
-# Off by default: on the CIFAR ResNet-50 step the GEMM is still 15-25 % behind cuDNN's own sm_100 kernels on these
-# shapes, which costs more than the saved statistics pass returns.  GCB200_TC_CONV=1 (or ``ENABLED = True``) turns it on.
-ENABLED = os.environ.get("GCB200_TC_CONV", "0") == "1"
+# On by default.  Measured on the CIFAR ResNet-50 step (batch 128, one B200, three back-to-back pairs of runs): 8.04 /
+# 8.28 / 8.26 ms with this path against 8.34 / 8.37 / 8.40 ms with cuDNN convolutions everywhere.  GCB200_TC_CONV=0 (or
+# ``ENABLED = False``) keeps every convolution on cuDNN.
+ENABLED = os.environ.get("GCB200_TC_CONV", "1") == "1"
+
+
+# Below this many output positions (N*H*W) cuDNN's kernels win by more than the fused statistics return.
+MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "4096"))
+
+
+class _TransposedWeights:
+    """[Cin, Cout] copies of the 1x1 convolution weights: the K-major operand of the input-gradient GEMM.
+
+    A copy is valid while the weight's version counter and storage are the ones it was made from; the backward of
+    a layer redoes a stale copy on the spot.  Kernels that write parameters through raw pointers do not move
+    version counters, so ``ops.sgd_step`` marks every copy stale, and ``FlatArena.sgd_step`` -- which knows the
+    parameter list -- then re-transposes all of its registered weights in ONE launch (``refresh``), which is also
+    what a captured step graph replays."""
+
+    def __init__(self):
+        self.entries = {}          # id(weight) -> [weakref, wt, version, data_ptr]
+
+    def get(self, w):
+        e = self.entries.get(id(w))
+        if e is None or e[0]() is not w or e[3] != w.data_ptr() or e[1].device != w.device:
+            e = [weakref.ref(w), torch.empty(w.shape[1], w.shape[0], dtype=torch.float32, device=w.device), -1, w.data_ptr()]
+            self.entries[id(w)] = e
+            if len(self.entries) % 64 == 0:
+                self.entries = {k: v for k, v in self.entries.items() if v[0]() is not None}
+        if e[2] != w._version:
+            e[1].copy_(w.detach().reshape(w.shape[0], w.shape[1]).t())
+            e[2] = w._version
+        return e[1]
+
+    def invalidate(self):
+        for e in self.entries.values():
+            e[2] = -1
+
+    def refresh(self, owner, params):
+        """One launch for every registered weight among ``params``; the pointer table and the buffers it names are
+        kept on ``owner`` so that they live as long as a graph that replays the launch."""
+        mine = [e for e in (self.entries.get(id(p)) for p in params) if e is not None and e[0]() is not None and e[0]().is_cuda]
+        if not mine:
+            return
+        key = tuple((e[0]().data_ptr(), e[1].data_ptr()) for e in mine)
+        state = getattr(owner, "_transposed_weight_table", None)
+        if state is None or state[0] != key:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("the table of transposed 1x1 weights changed inside a CUDA graph capture: run one "
+                                   "eager step (forward, backward, optimiser) before capturing")
+            rows, tiles = [], 0
+            for e in mine:
+                w = e[0]()
+                rows.append([w.data_ptr(), e[1].data_ptr(), w.shape[0], w.shape[1], tiles])
+                tiles += ((w.shape[0] + 31) // 32) * ((w.shape[1] + 31) // 32)
+            state = (key, torch.tensor(rows, dtype=torch.int64).to(mine[0][1].device), tiles, [e[1] for e in mine])
+            owner._transposed_weight_table = state
+        _, table, tiles, _ = state
+        with torch.cuda.device(table.device):
+            nat.check(nat.cuda().gc_cuda_batched_transpose(table.data_ptr(), table.shape[0], tiles, nat.stream_ptr()),
+                      "batched_transpose")
+        nat.count_launch()
+        for e in mine:
+            e[2] = e[0]()._version
+
+
+_transposed = _TransposedWeights()
+
+
+def weights_written_raw():
+    """Called by kernels that rewrite parameters through raw pointers (version counters do not move)."""
+    _transposed.invalidate()
+
+
+def refresh_transposed(owner, params):
+    """Called by the owner of a parameter list after it rewrote them: one batched re-transpose."""
+    _transposed.refresh(owner, params)
 
 
 def _as_2d(t):
@@ -81,7 +156,7 @@ class _Conv1x1BNAct(torch.autograd.Function):
             dx = None
             if ctx.needs_input_grad[0]:
                 dx = torch.empty_like(x)
-                wt = w.reshape(cout, cin).t().contiguous()                  # [Cin, Cout]: K-major for dX = dY x W
+                wt = _transposed.get(w)                                     # [Cin, Cout]: K-major for dX = dY x W
                 gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx))
             dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
                                                      [False, True, False])[1]
@@ -100,7 +175,7 @@ def _fusable(conv, bn, x):
                          (x.requires_grad or conv.weight.requires_grad)):
         return False
     n, cin, h, w = x.shape
-    if cin % 4 or conv.out_channels % 4:
+    if cin % 4 or conv.out_channels % 4 or n * h * w < MIN_ROWS:
         return False
     return bool(nat.cuda().gc_cuda_bn_supported(n * h * w, conv.out_channels))
 

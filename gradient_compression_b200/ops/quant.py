@@ -256,6 +256,9 @@ def sgd_step(p, g, m, lr=None, momentum=0.9, weight_decay=0.0, nesterov=True, hy
         with torch.cuda.device(p.device):
             nat.check(nat.cuda().gc_cuda_sgd_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), n, hyper.data_ptr(),
                                                   int(bool(nesterov)), nat.stream_ptr()), "sgd_step")
+        from . import conv                     # raw-pointer write: cached transposes of these weights are stale
+
+        conv.weights_written_raw()
     else:
         if hyper is not None:
             lr, momentum, weight_decay = (float(v) for v in hyper.tolist())

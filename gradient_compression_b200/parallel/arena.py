@@ -74,6 +74,10 @@ class FlatArena:
     def sgd_step(self, hyper=None, lr=None, momentum=0.9, weight_decay=5e-4, nesterov=True):
         ops.sgd_step(self.flat_params, self.flat_grads, self.flat_momentum, lr=lr, momentum=momentum,
                      weight_decay=weight_decay, nesterov=nesterov, hyper=hyper)
+        if self.flat_params.is_cuda:
+            from ..ops import conv
+
+            conv.refresh_transposed(self, self.params)        # transposed 1x1 weights for the input-gradient GEMMs
 
     def state_dict(self):
         return {"momentum": self.flat_momentum.clone() if self.flat_momentum is not None else None}

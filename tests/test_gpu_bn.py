@@ -109,15 +109,24 @@ def test_resnet50_step_matches_unfused_model():
     assert float((g_f[-1] - g_u[-1]).norm() / g_u[-1].norm()) < 1e-4      # the head's bias gradient is well conditioned
 
 
+@pytest.fixture
+def tc_conv():
+    """Tensor-core 1x1 convolutions on for every size, restored afterwards."""
+    from gradient_compression_b200.ops import conv as convmod
+
+    old = (convmod.ENABLED, convmod.MIN_ROWS)
+    convmod.ENABLED, convmod.MIN_ROWS = True, 0
+    yield convmod
+    convmod.ENABLED, convmod.MIN_ROWS = old
+
+
 @pytest.mark.parametrize("shape", [(128, 64, 32, 32, 256), (16, 256, 8, 8, 64), (8, 512, 4, 4, 2048), (5, 16, 7, 9, 32)])
 @pytest.mark.parametrize("residual", [False, True])
 @pytest.mark.parametrize("relu", [False, True])
-def test_conv1x1_bn_act_matches_torch(shape, residual, relu):
+def test_conv1x1_bn_act_matches_torch(tc_conv, shape, residual, relu):
     """1x1 convolution on the tcgen05 GEMM with BN statistics from its epilogue vs cuDNN conv + torch bn."""
-    from gradient_compression_b200.ops import conv as convmod
     from gradient_compression_b200.ops.conv import _fusable, conv_bn_act
 
-    convmod.ENABLED = True
     n, cin, h, w, cout = shape
     g = torch.Generator().manual_seed(cin + cout)
     cl = torch.channels_last
@@ -163,3 +172,40 @@ def test_conv1x1_bn_act_matches_torch(shape, residual, relu):
         assert close(ra.grad, rb.grad)
     assert torch.allclose(bn_a.running_mean, bn_b.running_mean, atol=1e-3)
     assert torch.allclose(bn_a.running_var, bn_b.running_var, rtol=5e-3, atol=1e-3)
+
+
+def test_input_gradient_follows_weight_updates(tc_conv):
+    """The input-gradient GEMM reads cached transposed weights.  They must follow (a) the fused SGD kernel, which
+    writes parameters through raw pointers and re-transposes all of them in one launch, and (b) in-place torch
+    updates, which the version counter reveals."""
+    from gradient_compression_b200.ops.conv import conv_bn_act
+    from gradient_compression_b200.parallel.arena import FlatArena, FlatSGD
+
+    cl = torch.channels_last
+    torch.manual_seed(5)
+    convs = torch.nn.ModuleList([torch.nn.Conv2d(32, 64, 1, bias=False), torch.nn.Conv2d(64, 32, 1, bias=False)]).cuda().to(memory_format=cl)
+    bns = torch.nn.ModuleList([torch.nn.BatchNorm2d(64), torch.nn.BatchNorm2d(32)]).cuda()
+    arena = FlatArena(list(convs.parameters()) + list(bns.parameters()))
+    opt = FlatSGD(arena, lr=0.5, momentum=0.0, weight_decay=0.0, nesterov=False)
+    x = torch.randn(8, 32, 16, 16, device="cuda").contiguous(memory_format=cl)
+    dy = torch.randn(8, 32, 16, 16, device="cuda").contiguous(memory_format=cl)
+
+    def input_grads():
+        xa = x.clone().requires_grad_(True)
+        conv_bn_act(convs[1], bns[1], conv_bn_act(convs[0], bns[0], xa, None, True), None, False).backward(dy)
+        xb = x.clone().requires_grad_(True)
+        h = F.relu(F.batch_norm(F.conv2d(xb, convs[0].weight), None, None, bns[0].weight, bns[0].bias, True))
+        F.batch_norm(F.conv2d(h, convs[1].weight), None, None, bns[1].weight, bns[1].bias, True).backward(dy)
+        return xa.grad, xb.grad
+
+    for step in range(4):
+        arena.zero_grad()
+        ga, gb = input_grads()
+        assert float((ga - gb).norm() / gb.norm()) < 6e-2, step
+        if step < 2:
+            opt.step()                                   # raw-pointer update + batched re-transpose
+        else:
+            with torch.no_grad():                        # in-place torch update: the version counter moves
+                for c in convs:
+                    c.weight.add_(torch.randn_like(c.weight) * 0.3)
+    assert getattr(arena, "_transposed_weight_table", None) is not None and arena._transposed_weight_table[1].shape[0] == 2
