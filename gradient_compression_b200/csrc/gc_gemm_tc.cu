@@ -365,7 +365,8 @@ template <int BN>
 __global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                             const __grid_constant__ CUtensorMap tma_c, const float* __restrict__ bias, int M, int N, int K,
-                            int tiles_m, int tiles_n, float* __restrict__ col_partials, int* __restrict__ error_flag) {
+                            int tiles_m, int tiles_n, int accumulate, float* __restrict__ col_partials,
+                            int* __restrict__ error_flag) {
   using S = PSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -499,10 +500,16 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         group_bar(grp);
         if (issuer) {
-          if (n0 + sl * 32 < N)
-            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                         ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
-                         : "memory");
+          if (n0 + sl * 32 < N) {
+            if (accumulate)                      // C += tile: the add happens in L2, C is never read by the SM
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
+                           : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
+                           : "memory");
+          }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");              // one group per slab, empty ones included
         }
         if (col_partials != nullptr) {
@@ -626,7 +633,7 @@ int launch(const float* A, const float* B, float* C, const float* bias, int M, i
 
 template <int BN>
 int launch_persistent(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, float* col_partials, int* error_flag, cudaStream_t st) {
+                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, cudaStream_t st) {
   using S = PSmem<BN>;
   CUtensorMap ma, mb, mc;
   if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0 || make_map(&mc, C, M, N, ldc, BM) != 0)
@@ -641,7 +648,7 @@ int launch_persistent(const float* A, const float* B, float* C, const float* bia
   int64_t total = (int64_t)tiles_m * tiles_n;
   int64_t grid = total < sm_count() ? total : sm_count();
   gemm_tf32_persistent_kernel<BN><<<(unsigned)grid, PERSISTENT_THREADS, S::TOTAL, st>>>(ma, mb, mc, bias, M, N, K, tiles_m, tiles_n,
-                                                                                 col_partials, error_flag);
+                                                                                 accumulate, col_partials, error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -710,20 +717,23 @@ void gc_cuda_gemm_tf32_config(int kernel, int tile_n) {
   g_tile_choice = tile_n;
 }
 
-// C[M, N] = A[M, K] * B[N, K]^T (+ bias[N]); error_flag (device int, may be NULL) is set when a wait ran out.
+// C[M, N] = A[M, K] * B[N, K]^T (+ bias[N]), or C += ... when accumulate != 0 (persistent kernel only: needs N > 16 and
+// a C that meets the TMA rules; the additions are done by TMA reduce stores, i.e. in L2);
+// error_flag (device int, may be NULL) is set when a wait ran out.
 // col_partials (may be NULL): [m_tiles][2][N] floats receiving, per 128-row tile, the column sums and sums of
 // squares of C -- the batch-norm statistics of a 1x1 convolution's output without another pass over it.
 int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, float* col_partials, int* error_flag, void* cs) {
+                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, void* cs) {
   if (!gc_cuda_gemm_tf32_supported(A, B, M, N, K, lda, ldb)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)cs;
-  bool persistent = g_kernel_choice != 1 && N > 16 && tma_store_ok(C, ldc);
+  bool persistent = (g_kernel_choice != 1 || accumulate) && N > 16 && tma_store_ok(C, ldc);
+  if (accumulate && !persistent) return (int)cudaErrorInvalidValue;
   if (persistent) {
     int bn = g_tile_choice ? g_tile_choice : pick_bn_persistent(M, N, K);
     switch (bn) {
-      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
-      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
-      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
+      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
+      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
       default: return (int)cudaErrorInvalidValue;
     }
   }

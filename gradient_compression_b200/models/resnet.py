@@ -7,7 +7,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act
-from ..ops.conv import conv_bn_act
+from ..ops.conv import GradLink, conv_bn_act
 from .layers import bn, conv, linear
 
 
@@ -49,9 +49,13 @@ class Bottleneck(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        y = conv_bn_act(self.conv1, self.bn1, x)                 # 1x1: tensor-core GEMM with BN statistics in its epilogue
+        # 1x1 convolutions: tensor-core GEMM with BN statistics in its epilogue.  In an identity block the gradient of
+        # the skip connection and conv1's input gradient meet at x: the link lets conv1's GEMM add onto the former.
+        identity = len(self.shortcut) == 0
+        link = GradLink() if identity else None
+        y = conv_bn_act(self.conv1, self.bn1, x, link=link)
         y = bn_act(self.bn2, self.conv2(y))
-        return conv_bn_act(self.conv3, self.bn3, y, residual=self.shortcut(x))
+        return conv_bn_act(self.conv3, self.bn3, y, residual=link.residual(x) if identity else self.shortcut(x))
 
 
 class ResNet(nn.Module):

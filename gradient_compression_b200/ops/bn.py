@@ -7,10 +7,33 @@ kernels of ``csrc/gc_bn.cu`` on CUDA and with the equivalent torch ops on CPU.  
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 import torch.nn.functional as F
 
 from . import _native as nat
+
+# Gradient tensors this library allocated itself and handed to autograd for a residual input: nobody else holds
+# them, so a later kernel may accumulate into them in place (``ops.conv.GradLink``).  Keyed by address, checked by
+# object identity through a weak reference, so a freed and re-used address never matches.
+_owned_grads = {}
+
+
+def own_grad(t):
+    if len(_owned_grads) >= 256:
+        for k in [k for k, r in _owned_grads.items() if r() is None]:
+            del _owned_grads[k]
+        if len(_owned_grads) >= 256:
+            _owned_grads.clear()
+    _owned_grads[t.data_ptr()] = weakref.ref(t)
+    return t
+
+
+def take_owned_grad(t):
+    """True exactly once for a tensor registered with ``own_grad``."""
+    r = _owned_grads.pop(t.data_ptr(), None)
+    return r is not None and r() is t
 
 _scratch = {}
 
@@ -72,7 +95,7 @@ class _FusedBNAct(torch.autograd.Function):
             raise RuntimeError("bn_act: backward through eval-mode statistics is not supported by the fused kernel")
         sums = torch.empty(2 * c, dtype=torch.float32, device=x.device)
         dx = torch.empty_like(x)
-        dres = torch.empty_like(x) if (ctx.has_res and ctx.needs_input_grad[3]) else None
+        dres = own_grad(torch.empty_like(x)) if (ctx.has_res and ctx.needs_input_grad[3]) else None
         with torch.cuda.device(x.device):
             nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), x.data_ptr(), nat.ptr(y), m, c, stats.data_ptr(),
                                                 weight.data_ptr(), bias.data_ptr(), int(ctx.relu),

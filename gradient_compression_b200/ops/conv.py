@@ -17,13 +17,16 @@ import torch
 
 from . import _native as nat
 from . import gemm
-from .bn import _cl, _scratch_for, bn_act, kernel_path_ok
+from .bn import _cl, _scratch_for, bn_act, kernel_path_ok, own_grad, take_owned_grad
 
 # On by default.  Measured on the CIFAR ResNet-50 step (batch 128, one B200, three back-to-back pairs of runs): 8.04 /
 # 8.28 / 8.26 ms with this path against 8.34 / 8.37 / 8.40 ms with cuDNN convolutions everywhere.  GCB200_TC_CONV=0 (or
 # ``ENABLED = False``) keeps every convolution on cuDNN.
 ENABLED = os.environ.get("GCB200_TC_CONV", "1") == "1"
 
+
+# GradLink (accumulating input-gradient GEMMs of identity blocks) on / off, for measurements.
+LINK_ENABLED = os.environ.get("GCB200_GRAD_LINK", "1") == "1"
 
 # Below this many output positions (N*H*W) cuDNN's kernels win by more than the fused statistics return.
 MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "4096"))
@@ -103,10 +106,52 @@ def _as_2d(t):
     return t.permute(0, 2, 3, 1).reshape(n * h * w, c)
 
 
+class GradLink:
+    """Joins the two gradients that reach the input of a residual block: the identity branch's and the first
+    convolution's.  When that convolution runs on the GEMM, its input-gradient GEMM adds its product straight onto the
+    identity branch's gradient (``accumulate=True``: TMA reduce stores), instead of autograd writing both and summing
+    them in a third pass.  Usage, inside a block's ``forward``::
+
+        link = GradLink()
+        y = conv_bn_act(conv1, bn1, x, link=link)
+        ...
+        out = conv_bn_act(conv3, bn3, y, residual=link.residual(x))
+
+    ``link.residual(x)`` must be called after the convolution (autograd runs later-created nodes first, and the
+    identity gradient has to be there when the convolution's backward runs); either order stays correct, only the
+    saving is lost."""
+
+    def __init__(self):
+        self.armed = False          # the convolution took the GEMM path and will look for a stashed gradient
+        self.conv_done = False      # its backward already ran (without finding one)
+        self.stash, self.stash_owned = None, False
+
+    def residual(self, x):
+        if not (self.armed and torch.is_grad_enabled() and x.requires_grad):
+            return x
+        return _StashGrad.apply(x, self)
+
+
+class _StashGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, link):
+        ctx.link = link
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        link = ctx.link
+        if link.conv_done:              # the convolution's backward came first: ordinary accumulation by autograd
+            return g, None
+        link.stash, link.stash_owned = g, take_owned_grad(g)
+        return None, None
+
+
 class _Conv1x1BNAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu):
+    def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu, link):
         x = _cl(x)
+        ctx.link = link
         n, cin, h, wd = x.shape
         cout = w.shape[0]
         m = n * h * wd
@@ -144,7 +189,7 @@ class _Conv1x1BNAct(torch.autograd.Function):
         lib, st = nat.cuda(), nat.stream_ptr
         sums = torch.empty(2 * cout, dtype=torch.float32, device=x.device)
         dconv = torch.empty_like(yconv)
-        dres = torch.empty_like(yconv) if (ctx.has_res and ctx.needs_input_grad[5]) else None
+        dres = own_grad(torch.empty_like(yconv)) if (ctx.has_res and ctx.needs_input_grad[5]) else None
         with torch.cuda.device(x.device):
             nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
                                                 gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),
@@ -154,14 +199,29 @@ class _Conv1x1BNAct(torch.autograd.Function):
                                                gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),
                                                dconv.data_ptr(), nat.ptr(dres), st()), "bn_bwd_apply")
             dx = None
+            link = ctx.link
             if ctx.needs_input_grad[0]:
-                dx = torch.empty_like(x)
                 wt = _transposed.get(w)                                     # [Cin, Cout]: K-major for dX = dY x W
-                gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx))
+                acc = None
+                if link is not None and link.stash is not None:
+                    acc, link.stash = link.stash, None
+                    if not (link.stash_owned and acc.shape == x.shape and acc.dtype == torch.float32
+                            and acc.is_contiguous(memory_format=torch.channels_last)):
+                        acc = acc.contiguous(memory_format=torch.channels_last).clone()     # not ours to write into
+                if acc is not None and gemm.can_accumulate(_as_2d(acc)):
+                    dx = acc                                                # dX = identity-branch gradient + dY x W, added in L2
+                    gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx), accumulate=True)
+                else:
+                    dx = torch.empty_like(x)
+                    gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx))
+                    if acc is not None:
+                        dx += acc
+            if link is not None:
+                link.conv_done = True
             dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
                                                      [False, True, False])[1]
             dcb = dconv.sum((0, 2, 3)) if ctx.has_cbias else None
-        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None
+        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None
 
 
 def _fusable(conv, bn, x):
@@ -180,9 +240,11 @@ def _fusable(conv, bn, x):
     return bool(nat.cuda().gc_cuda_bn_supported(n * h * w, conv.out_channels))
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
     if not _fusable(conv, bn, x):
         return bn_act(bn, conv(x), residual=residual, relu=relu)
+    if link is not None:
+        link.armed = LINK_ENABLED and torch.is_grad_enabled() and x.requires_grad
     training = bn.training or bn.running_mean is None
     momentum = 0.1 if bn.momentum is None else bn.momentum
     if training and bn.track_running_stats and bn.num_batches_tracked is not None:
@@ -190,4 +252,4 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True):
     rm = bn.running_mean if bn.track_running_stats else None
     rv = bn.running_var if bn.track_running_stats else None
     return _Conv1x1BNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,
-                               bn.eps, relu)
+                               bn.eps, relu, link if (link is not None and link.armed) else None)

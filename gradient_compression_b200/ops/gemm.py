@@ -32,16 +32,28 @@ def supported(a, b_nk):
                                                        a.stride(0), b_nk.stride(0)))
 
 
-def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None):
+def can_accumulate(out):
+    """``accumulate=True`` needs an output the TMA store rules accept and more than 16 columns."""
+    return (out.is_cuda and out.dtype == torch.float32 and out.dim() == 2 and out.stride(1) == 1 and out.shape[1] > 16
+            and out.data_ptr() % 16 == 0 and out.stride(0) % 4 == 0)
+
+
+def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None, accumulate=False):
     """``col_partials`` (optional, fp32 [m_tiles, 2, N]): receives per 128-row tile the column sums and sums of
-    squares of the result -- batch-norm statistics of a 1x1 convolution's output for free."""
-    if not supported(a, b_nk):
+    squares of the product -- batch-norm statistics of a 1x1 convolution's output for free.
+    ``accumulate=True``: ``out += a @ b_nk.T`` with the additions done by TMA reduce stores (in L2), so the old
+    contents of ``out`` never travel to an SM."""
+    assert not accumulate or out is not None, "accumulate needs the tensor to add to"
+    if not supported(a, b_nk) or (accumulate and not can_accumulate(out)):
         assert col_partials is None, "column statistics need the tensor-core path"
         y = a @ b_nk.t()
         if bias is not None:
             y = y + bias
         if out is not None:
-            out.copy_(y)
+            if accumulate:
+                out.add_(y)
+            else:
+                out.copy_(y)
             return out
         return y
     m, k = a.shape
@@ -51,7 +63,8 @@ def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None):
     assert out.stride(1) == 1
     with torch.cuda.device(a.device):
         nat.check(nat.cuda().gc_cuda_gemm_tf32(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nat.ptr(bias), m, n, k,
-                                               a.stride(0), b_nk.stride(0), out.stride(0), nat.ptr(col_partials),
+                                               a.stride(0), b_nk.stride(0), out.stride(0), int(bool(accumulate)),
+                                               nat.ptr(col_partials),
                                                _error_flag(a.device).data_ptr(), nat.stream_ptr()), "gemm_tf32")
     return out
 

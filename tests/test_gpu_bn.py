@@ -209,3 +209,40 @@ def test_input_gradient_follows_weight_updates(tc_conv):
                 for c in convs:
                     c.weight.add_(torch.randn_like(c.weight) * 0.3)
     assert getattr(arena, "_transposed_weight_table", None) is not None and arena._transposed_weight_table[1].shape[0] == 2
+
+
+@pytest.mark.parametrize("owned", [True, False])
+def test_identity_block_gradient_link(tc_conv, owned):
+    """x feeds conv1 and the skip connection.  With a GradLink the input-gradient GEMM of conv1 accumulates onto the
+    skip connection's gradient; the result must equal autograd's own sum.  ``owned=False`` routes the skip through a
+    plain torch add, whose gradient tensor is shared with the other branch and must not be written in place."""
+    from gradient_compression_b200.ops.conv import GradLink, conv_bn_act
+
+    cl = torch.channels_last
+    torch.manual_seed(11)
+    conv1, conv3 = torch.nn.Conv2d(64, 32, 1, bias=False).cuda().to(memory_format=cl), torch.nn.Conv2d(32, 64, 1, bias=False).cuda().to(memory_format=cl)
+    bn1, bn3 = torch.nn.BatchNorm2d(32).cuda(), torch.nn.BatchNorm2d(64).cuda()
+    x0 = torch.randn(16, 64, 16, 16, device="cuda").contiguous(memory_format=cl)
+    dy = torch.randn(16, 64, 16, 16, device="cuda").contiguous(memory_format=cl)
+
+    def block(x, use_link):
+        link = GradLink() if use_link else None
+        y = conv_bn_act(conv1, bn1, x, link=link)
+        res = link.residual(x) if use_link else x
+        if owned:
+            return conv_bn_act(conv3, bn3, y, residual=res)
+        return torch.relu(conv_bn_act(conv3, bn3, y, relu=False) + res)
+
+    grads = []
+    for use_link in (True, False):
+        for p in (conv1.weight, conv3.weight):
+            p.grad = None
+        x = (x0 * 1.0).requires_grad_(True)           # non-leaf input, as inside a network
+        x.retain_grad()
+        out = block(x, use_link)
+        out.backward(dy)
+        grads.append((x.grad.clone(), conv1.weight.grad.clone(), dy.clone()))
+    (gx_l, gw_l, dy_l), (gx_p, gw_p, _) = grads
+    assert torch.equal(dy_l, dy)                       # the incoming gradient was not written to
+    assert float((gx_l - gx_p).norm() / gx_p.norm()) < 1e-6
+    assert float((gw_l - gw_p).norm() / gw_p.norm()) < 1e-6

@@ -119,3 +119,24 @@ def test_chosen_tile_width_random_inputs(gemm_choice, kernel):
         out = gemm.gemm_tf32(a, b)
         gemm.check()
         assert float((out - ref).abs().max() / ref.abs().max()) < 3e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(1000, 256, 96), (20000, 64, 64), (4096, 40, 200)])
+def test_accumulate_adds_onto_the_output(m, n, k):
+    """``accumulate=True``: C += A B^T through TMA reduce stores; exact on small integers, rows and columns outside the
+    product untouched."""
+    from gradient_compression_b200.ops import gemm
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randint(-4, 5, (m, k), generator=g).float().cuda()
+    b = torch.randint(-4, 5, (n, k), generator=g).float().cuda()
+    c0 = torch.randint(-100, 101, (m + 3, n + 8), generator=g).float().cuda()
+    c = c0.clone()
+    gemm.gemm_tf32(a, b, out=c[:m, :n], accumulate=True)
+    gemm.check()
+    ref = c0.clone()
+    ref[:m, :n] += a @ b.t()
+    assert torch.equal(c, ref)
+    gemm.gemm_tf32(a, b, out=c[:m, :n], accumulate=True)          # twice: the reduce really reads what is there
+    ref[:m, :n] += a @ b.t()
+    assert torch.equal(c, ref)
