@@ -51,6 +51,7 @@ def parse_args():
     p.add_argument("--graph", type=int, default=1, help="capture the training step in a CUDA graph (ours)")
     p.add_argument("--channels-last", type=int, default=1)
     p.add_argument("--cudnn-benchmark", type=int, default=1, help="let cuDNN autotune its convolution algorithms (ours)")
+    p.add_argument("--cudnn-benchmark-limit", type=int, default=-1, help="algorithms cuDNN's autotuner tries (0 = all; -1 = torch default)")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
 
@@ -153,6 +154,8 @@ def run_ours(args, world, rank, local_rank):
     device = torch.device("cuda", local_rank)
     set_seed(42)
     torch.backends.cudnn.benchmark = bool(args.cudnn_benchmark)
+    if args.cudnn_benchmark_limit >= 0:
+        torch.backends.cudnn.benchmark_limit = args.cudnn_benchmark_limit
     steps_needed = args.steps + args.warmup + 10
     task = CIFAR(device, None, args.model, seed=42, data="synthetic",
                  synthetic_train_size=args.batch * world * steps_needed, synthetic_test_size=args.batch,

@@ -87,6 +87,8 @@ __device__ __forceinline__ void combine_partials(const float* __restrict__ parti
 // out stats[0:C] = mean, stats[C:2C] = rstd; running stats updated in place when given.
 __global__ void __launch_bounds__(BN_THREADS) bn_stats_kernel(const float* __restrict__ x, int64_t M, int C,
                                                               int64_t rows_per_block, float* __restrict__ partials) {
+  pdl_wait();
+  pdl_launch_dependents();
   int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
   int64_t r1 = r0 + rows_per_block < M ? r0 + rows_per_block : M;
   // shifted sums: k = the channel's value in row 0, so that sum (x-k)^2 does not cancel against
@@ -105,6 +107,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_stats_kernel(const float* __res
 __global__ void bn_stats_finalize_kernel(const float* __restrict__ partials, const float* __restrict__ x, int nparts,
                                          int64_t M, int C, float* __restrict__ stats, float* __restrict__ running_mean,
                                          float* __restrict__ running_var, float momentum, float eps) {
+  pdl_wait();
+  pdl_launch_dependents();
   double sums[2];
   combine_partials(partials, nparts, C, sums);
   int c = blockIdx.x * 32 + threadIdx.x;
@@ -129,6 +133,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_apply_kernel(const float* __res
                                                               const float* __restrict__ gamma, const float* __restrict__ beta,
                                                               const float* __restrict__ residual, int relu,
                                                               float* __restrict__ y) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int vec = C >> 2;
   const int64_t nq = M * vec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -159,6 +165,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* 
                                                                    int64_t rows_per_block, const float* __restrict__ stats,
                                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                    int relu, float* __restrict__ partials) {
+  pdl_wait();
+  pdl_launch_dependents();
   int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
   int64_t r1 = r0 + rows_per_block < M ? r0 + rows_per_block : M;
   const int col = threadIdx.x % (C >> 2);
@@ -185,6 +193,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* 
 }
 
 __global__ void bn_sums_finalize_kernel(const float* __restrict__ partials, int nparts, int C, float* __restrict__ sums) {
+  pdl_wait();
+  pdl_launch_dependents();
   double out[2];
   combine_partials(partials, nparts, C, out);
   int c = blockIdx.x * 32 + threadIdx.x;
@@ -200,6 +210,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(const float* _
                                                                   const float* __restrict__ stats, const float* __restrict__ gamma,
                                                                   const float* __restrict__ beta, const float* __restrict__ sums,
                                                                   int relu, float* __restrict__ dx, float* __restrict__ dres) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int vec = C >> 2;
   const int64_t nq = M * vec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -284,25 +296,25 @@ int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* sta
   int64_t rpb;
   int grid = reduce_grid(M, C, &rpb);
   size_t smem = 2 * BN_THREADS * sizeof(float4);
-  bn_stats_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(x, M, C, rpb, (float*)scratch);
-  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, x, grid, M, C, stats,
-                                                                                  running_mean, running_var, momentum, eps);
+  launch_pdl(bn_stats_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, x, M, C, rpb, (float*)scratch);
+  launch_pdl(bn_stats_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, x, grid, M,
+             C, stats, running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }
 
 // Statistics from partial column sums produced elsewhere (the GEMM epilogue): partials[nparts][2][C], unshifted.
 int gc_cuda_bn_finalize_partials(const float* partials, int nparts, int64_t M, int C, float* stats, float* running_mean,
                                  float* running_var, float momentum, float eps, void* cs) {
-  bn_stats_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>(partials, nullptr, nparts, M, C, stats,
-                                                                                  running_mean, running_var, momentum, eps);
+  launch_pdl(bn_stats_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, partials, (const float*)nullptr,
+             nparts, M, C, stats, running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }
 
 int gc_cuda_bn_apply(const float* x, int64_t M, int C, const float* stats, const float* gamma, const float* beta,
                      const float* residual, int relu, float* y, void* cs) {
   if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
-  bn_apply_kernel<<<apply_grid(M * (C >> 2)), BN_THREADS, 0, (cudaStream_t)cs>>>(x, M, C, stats, gamma, beta, residual,
-                                                                                  relu, y);
+  launch_pdl(bn_apply_kernel, dim3(apply_grid(M * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, x, M, C, stats, gamma, beta,
+             residual, relu, y);
   return (int)cudaGetLastError();
 }
 
@@ -313,9 +325,9 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
   int64_t rpb;
   int grid = reduce_grid(M, C, &rpb);
   size_t smem = 2 * BN_THREADS * sizeof(float4);
-  bn_bwd_reduce_kernel<<<grid, BN_THREADS, smem, (cudaStream_t)cs>>>(dy, x, y, M, C, rpb, stats, gamma, beta, relu,
-                                                                       (float*)scratch);
-  bn_sums_finalize_kernel<<<(C + 31) / 32, dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs>>>((const float*)scratch, grid, C, sums);
+  launch_pdl(bn_bwd_reduce_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dy, x, y, M, C, rpb, stats, gamma, beta,
+             relu, (float*)scratch);
+  launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
   return (int)cudaGetLastError();
 }
 
@@ -323,8 +335,8 @@ int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_
                          const float* gamma, const float* beta, const float* sums, int relu, float* dx, float* dres,
                          void* cs) {
   if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
-  bn_bwd_apply_kernel<<<apply_grid(M * (C >> 2)), BN_THREADS, 0, (cudaStream_t)cs>>>(dy, x, y, M, C, stats, gamma, beta,
-                                                                                      sums, relu, dx, dres);
+  launch_pdl(bn_bwd_apply_kernel, dim3(apply_grid(M * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, dy, x, y, M, C, stats, gamma,
+             beta, sums, relu, dx, dres);
   return (int)cudaGetLastError();
 }
 

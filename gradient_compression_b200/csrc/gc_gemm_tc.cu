@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "gc_device.cuh"
+
 namespace {
 
 constexpr int BM = 128;
@@ -402,6 +404,10 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above (barriers, TMEM) overlapped the tail of the previous kernel of the stream; its results are
+  // needed from here on
+  gc::pdl_wait();
+  gc::pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -567,6 +573,175 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
   if (threadIdx.x == 0 && abort_flag && error_flag != nullptr) atomicExch(error_flag, 1);
 }
 
+// ------------------------------------------------------------------------------------------------
+// "TN" GEMM for weight gradients:  C[Mo, No] += A[P, Mo]^T * B[P, No], contraction over the rows P (the
+// N*H*W positions of a 1x1 convolution: A = dY, B = X, C = dW).  Both operands are MN-major for the tensor
+// core (the contraction index is the slow one in memory).  For 32-bit elements that takes the shared-memory
+// layout "128-byte swizzle with 32-byte atoms": 32 consecutive output-dimension floats (128 B) of one
+// position form a row, 32 positions a 4 KB chunk (one TMA box), and the chunks of a k-block lie one after the
+// other.  In descriptor terms: leading byte offset = 4096
+// (next 32 floats of the output dimension), stride byte offset = 512 (next group of 4 positions), one MMA
+// (K = 8 positions) advances the start address by 1024 bytes.
+// Split-K: CTA (tile, split) contracts its slice of positions and adds its 128 x BN partial result onto C
+// with TMA reduce stores, so C must hold the value to add to (zeros for a plain product).
+template <int BN>
+struct TnSmem {
+  static constexpr int STAGES = (BN <= 64) ? 6 : ((BN <= 128) ? 5 : 3);
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int RING_BYTES = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int NSLAB = 2;
+  static constexpr int SLAB_BYTES = BM * 128;
+  static constexpr int STAGING_OFF = RING_BYTES;
+  static constexpr int BAR_OFF = STAGING_OFF + NSLAB * SLAB_BYTES;
+  static constexpr int TOTAL = 1024 + BAR_OFF + 256;
+  static constexpr int TMEM_COLS = BN;
+  static_assert(TOTAL <= 232448, "shared memory of one CTA");
+};
+
+__device__ __forceinline__ uint64_t make_smem_desc_mn(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);      // start address
+  d |= (uint64_t)(4096 >> 4) << 16;                      // leading byte offset: next 32-float chunk of the M / N dimension
+  d |= (uint64_t)(512 >> 4) << 32;                       // stride byte offset: next group of 4 K rows
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)1 << 61;                                // layout type: SWIZZLE_128B_BASE32B
+  return d;
+}
+
+__host__ __device__ constexpr uint32_t make_idesc_mn(int n) {
+  return make_idesc(n) | (1u << 15) | (1u << 16);        // A and B are MN-major
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_c, int P, int Mo, int No, int tiles_n, int splits,
+                    int kblocks_per_split, int* __restrict__ error_flag) {
+  using S = TnSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_tiles = base;
+  uint8_t* b_tiles = base + S::STAGES * S::A_BYTES;
+  uint8_t* staging = base + S::STAGING_OFF;
+  uint64_t* full = reinterpret_cast<uint64_t*>(base + S::BAR_OFF);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_ready = empty + S::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  __shared__ int abort_flag;
+  __shared__ int epi_go;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x % splits;
+  const int tile = blockIdx.x / splits;
+  const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+  const int total_k = (P + BK - 1) / BK;
+  const int k_begin = split * kblocks_per_split;
+  const int k_end = k_begin + kblocks_per_split < total_k ? k_begin + kblocks_per_split : total_k;
+  const int num_k = k_end > k_begin ? k_end - k_begin : 0;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    epi_go = 1;
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_ready, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (num_k > 0) {
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int k = 0; k < num_k; ++k) {
+          const int s = k % S::STAGES;
+          const uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
+          if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) break;
+          mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
+          // one 4 KB box (32 floats x 32 positions) per 32-float chunk of the output dimensions
+#pragma unroll
+          for (int c = 0; c < BM / 32; ++c)
+            tma_load_2d(a_tiles + s * S::A_BYTES + c * 4096, &tma_a, m0 + c * 32, (k_begin + k) * BK, &full[s]);
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c)
+            tma_load_2d(b_tiles + s * S::B_BYTES + c * 4096, &tma_b, n0 + c * 32, (k_begin + k) * BK, &full[s]);
+        }
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        constexpr uint32_t idesc = make_idesc_mn(BN);
+        bool ok = true;
+        for (int k = 0; k < num_k; ++k) {
+          const int s = k % S::STAGES;
+          const uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
+          if (!mbar_wait(&full[s], phase, &abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc_mn(a_tiles + s * S::A_BYTES);
+          const uint64_t bdesc = make_smem_desc_mn(b_tiles + s * S::B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)     // 8 positions = 8 rows of 128 bytes = 1024 bytes = 64 address units
+            umma_tf32(tmem_base, adesc + (uint64_t)(kk * 64), bdesc + (uint64_t)(kk * 64), idesc, (k | kk) != 0 ? 1u : 0u);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(acc_ready);
+      }
+    } else {
+      const int lg = warp & 3;
+      const int r = lg * 32 + lane;
+      const int te = (warp - 2) * 32 + lane;
+      const bool issuer = te == 0;
+      const bool got = mbar_wait(acc_ready, 0u, &abort_flag);
+      if (issuer) epi_go = (got && abort_flag == 0) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (epi_go) {
+        tc_fence_after();
+        const uint32_t lane_base = tmem_base + ((uint32_t)(lg * 32) << 16);
+        constexpr int SLABS = BN / 32;
+#pragma unroll 1
+        for (int sl = 0; sl < SLABS; ++sl) {
+          uint8_t* slab = staging + (sl % S::NSLAB) * S::SLAB_BYTES;
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(S::NSLAB - 1) : "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          uint32_t ra[16], rb[16];
+          tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32), ra);
+          tmem_ld16_nowait(lane_base + (uint32_t)(sl * 32 + 16), rb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t* src = c < 4 ? &ra[c * 4] : &rb[(c - 4) * 4];
+            *reinterpret_cast<float4*>(slab + r * 128 + ((c ^ (r & 7)) << 4)) =
+                make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]), __uint_as_float(src[3]));
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (issuer) {
+            if (n0 + sl * 32 < No)
+              asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                           ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+      }
+      if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
+  }
+  if (threadIdx.x == 0 && abort_flag && error_flag != nullptr) atomicExch(error_flag, 1);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -647,8 +822,51 @@ int launch_persistent(const float* A, const float* B, float* C, const float* bia
   int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   int64_t total = (int64_t)tiles_m * tiles_n;
   int64_t grid = total < sm_count() ? total : sm_count();
-  gemm_tf32_persistent_kernel<BN><<<(unsigned)grid, PERSISTENT_THREADS, S::TOTAL, st>>>(ma, mb, mc, bias, M, N, K, tiles_m, tiles_n,
-                                                                                 accumulate, col_partials, error_flag);
+  gc::launch_pdl(gemm_tf32_persistent_kernel<BN>, dim3((unsigned)grid), dim3(PERSISTENT_THREADS), (size_t)S::TOTAL, st, ma, mb, mc, bias,
+                 M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag);
+  return (int)cudaGetLastError();
+}
+
+
+// Row-major [P, D] fp32 matrix as an MN-major operand: box = 32 floats x 32 rows (4 KB), shared-memory layout
+// "128-byte swizzle, 32-byte atoms" (the MN-major layout of 32-bit types).
+int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64_t ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)P};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)BK};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BN>
+int launch_tn(const float* A, const float* B, float* C, int P, int Mo, int No, int64_t lda, int64_t ldb, int64_t ldc,
+              int* error_flag, cudaStream_t st) {
+  using S = TnSmem<BN>;
+  CUtensorMap ma, mb, mc;
+  if (make_map_mn(&ma, A, P, Mo, lda) != 0 || make_map_mn(&mb, B, P, No, ldb) != 0 ||
+      make_map(&mc, C, Mo, No, ldc, BM) != 0)
+    return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tn_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  int tiles_m = (Mo + BM - 1) / BM, tiles_n = (No + BN - 1) / BN;
+  int tiles = tiles_m * tiles_n;
+  int total_k = (P + BK - 1) / BK;
+  // about two CTAs per SM over all tiles, at least 8 k-blocks each so that the pipeline fills
+  int splits = (2 * sm_count() + tiles - 1) / tiles;
+  if (splits > (total_k + 7) / 8) splits = (total_k + 7) / 8;
+  if (splits < 1) splits = 1;
+  int per = (total_k + splits - 1) / splits;
+  splits = (total_k + per - 1) / per;
+  gemm_tn_tf32_kernel<BN><<<(unsigned)(tiles * splits), GEMM_THREADS, S::TOTAL, st>>>(ma, mb, mc, P, Mo, No, tiles_n, splits, per,
+                                                                                     error_flag);
   return (int)cudaGetLastError();
 }
 
@@ -742,6 +960,31 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
     case 64: return launch<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
     case 128: return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
     default: return launch<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
+  }
+}
+
+// 1 when C[Mo, No] += A[P, Mo]^T B[P, No] can run on the tensor cores: Mo and No multiples of 32, 16-byte aligned
+// bases, row strides multiples of 16 bytes.
+int gc_cuda_gemm_tn_tf32_supported(const void* A, const void* B, const void* C, int P, int Mo, int No, int64_t lda, int64_t ldb,
+                                   int64_t ldc) {
+  if (P < 1 || Mo < 32 || No < 32 || (Mo & 31) || (No & 31)) return 0;
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(B) & 15u) || (reinterpret_cast<uintptr_t>(C) & 15u)) return 0;
+  if ((lda & 3) || (ldb & 3) || (ldc & 3) || lda < Mo || ldb < No || ldc < No) return 0;
+  return encode_fn() != nullptr ? 1 : 0;
+}
+
+// C[Mo, No] += A[P, Mo]^T * B[P, No] (weight gradient of a 1x1 convolution: A = dY, B = X).  The partial products of
+// the split contraction are added onto C by TMA reduce stores: zero C first for a plain product.
+int gc_cuda_gemm_tn_tf32(const float* A, const float* B, float* C, int P, int Mo, int No, int64_t lda, int64_t ldb, int64_t ldc,
+                         int* error_flag, void* cs) {
+  if (!gc_cuda_gemm_tn_tf32_supported(A, B, C, P, Mo, No, lda, ldb, ldc)) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)cs;
+  int bn = g_tile_choice ? g_tile_choice : (No <= 64 ? 64 : (No <= 128 ? 128 : 256));
+  switch (bn) {
+    case 64: return launch_tn<64>(A, B, C, P, Mo, No, lda, ldb, ldc, error_flag, st);
+    case 128: return launch_tn<128>(A, B, C, P, Mo, No, lda, ldb, ldc, error_flag, st);
+    case 256: return launch_tn<256>(A, B, C, P, Mo, No, lda, ldb, ldc, error_flag, st);
+    default: return (int)cudaErrorInvalidValue;
   }
 }
 

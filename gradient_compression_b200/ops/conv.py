@@ -28,6 +28,9 @@ ENABLED = os.environ.get("GCB200_TC_CONV", "1") == "1"
 # GradLink (accumulating input-gradient GEMMs of identity blocks) on / off, for measurements.
 LINK_ENABLED = os.environ.get("GCB200_GRAD_LINK", "1") == "1"
 
+# Weight gradients of these convolutions on the split-K tcgen05 GEMM (off: cuDNN).
+WGRAD_ENABLED = os.environ.get("GCB200_TC_WGRAD", "1") == "1"
+
 # Below this many output positions (N*H*W) cuDNN's kernels win by more than the fused statistics return.
 MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "4096"))
 
@@ -83,7 +86,6 @@ class _TransposedWeights:
         with torch.cuda.device(table.device):
             nat.check(nat.cuda().gc_cuda_batched_transpose(table.data_ptr(), table.shape[0], tiles, nat.stream_ptr()),
                       "batched_transpose")
-        nat.count_launch()
         for e in mine:
             e[2] = e[0]()._version
 
@@ -218,8 +220,15 @@ class _Conv1x1BNAct(torch.autograd.Function):
                         dx += acc
             if link is not None:
                 link.conv_done = True
-            dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
-                                                     [False, True, False])[1]
+            dw = None
+            if ctx.needs_input_grad[1]:
+                if WGRAD_ENABLED and cout % 32 == 0 and cin % 32 == 0:
+                    # dW[Cout, Cin] = dY^T X over all positions: split-K GEMM with MN-major tcgen05 operands
+                    dw2d = gemm.gemm_tn_tf32(_as_2d(dconv), _as_2d(x))
+                    dw = dw2d.view(cout, cin, 1, 1).contiguous(memory_format=torch.channels_last)
+                else:
+                    dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
+                                                             [False, True, False])[1]
             dcb = dconv.sum((0, 2, 3)) if ctx.has_cbias else None
         return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None
 

@@ -69,6 +69,34 @@ def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None, accumulate=False)
     return out
 
 
+def tn_supported(a_pm, b_pn, out):
+    ok = all(t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1 for t in (a_pm, b_pn, out))
+    if not ok or a_pm.shape[0] != b_pn.shape[0] or out.shape != (a_pm.shape[1], b_pn.shape[1]):
+        return False
+    return bool(nat.cuda().gc_cuda_gemm_tn_tf32_supported(a_pm.data_ptr(), b_pn.data_ptr(), out.data_ptr(), a_pm.shape[0],
+                                                          a_pm.shape[1], b_pn.shape[1], a_pm.stride(0), b_pn.stride(0), out.stride(0)))
+
+
+def gemm_tn_tf32(a_pm, b_pn, out=None, accumulate=False):
+    """``out[Mo, No] (+)= a_pm[P, Mo].T @ b_pn[P, No]``: the contraction runs over the rows, which is the weight gradient
+    of a 1x1 convolution (``a_pm`` = output gradient, ``b_pn`` = input, rows = positions).  On the tensor-core path both
+    operands are MN-major tcgen05 operands and the contraction is split over CTAs whose partial tiles are added onto
+    ``out`` by TMA reduce stores (so the summation order of the partials is not fixed)."""
+    if out is None:
+        assert not accumulate
+        out = torch.zeros(a_pm.shape[1], b_pn.shape[1], dtype=torch.float32, device=a_pm.device)
+    elif not accumulate:
+        out.zero_()
+    if not tn_supported(a_pm, b_pn, out):
+        out.add_(a_pm.t() @ b_pn)
+        return out
+    with torch.cuda.device(a_pm.device):
+        nat.check(nat.cuda().gc_cuda_gemm_tn_tf32(a_pm.data_ptr(), b_pn.data_ptr(), out.data_ptr(), a_pm.shape[0], a_pm.shape[1],
+                                                  b_pn.shape[1], a_pm.stride(0), b_pn.stride(0), out.stride(0),
+                                                  _error_flag(a_pm.device).data_ptr(), nat.stream_ptr()), "gemm_tn_tf32")
+    return out
+
+
 KERNELS = {"auto": 0, "tile": 1, "persistent": 2}
 
 

@@ -140,3 +140,38 @@ def test_accumulate_adds_onto_the_output(m, n, k):
     gemm.gemm_tf32(a, b, out=c[:m, :n], accumulate=True)          # twice: the reduce really reads what is there
     ref[:m, :n] += a @ b.t()
     assert torch.equal(c, ref)
+
+
+@pytest.mark.parametrize("p,mo,no", [(64, 128, 64), (4096, 64, 256), (40000, 256, 64), (1000, 96, 160), (8192, 512, 128),
+                                     (2048, 2048, 512), (33, 32, 32)])
+def test_gemm_tn_weight_gradient_shape(p, mo, no):
+    """out = A^T B with the contraction over the rows (both operands MN-major for the tensor core, split-K with TMA
+    reduce stores).  Small integers: TF32 represents them and every partial sum is exact in fp32, so the result
+    is exact whatever the order in which the splits land."""
+    from gradient_compression_b200.ops import gemm
+
+    g = torch.Generator().manual_seed(p + mo + no)
+    a = torch.randint(-3, 4, (p, mo), generator=g).float().cuda()
+    b = torch.randint(-3, 4, (p, no), generator=g).float().cuda()
+    out = torch.full((mo, no), float("nan"), device="cuda")
+    assert gemm.tn_supported(a, b, out)
+    gemm.gemm_tn_tf32(a, b, out=out)
+    gemm.check()
+    ref = (a.double().t() @ b.double())
+    assert torch.equal(out.double(), ref)
+    gemm.gemm_tn_tf32(a, b, out=out, accumulate=True)
+    gemm.check()
+    assert torch.equal(out.double(), 2 * ref)
+
+
+def test_gemm_tn_random_inputs_and_fallback():
+    from gradient_compression_b200.ops import gemm
+
+    a = torch.randn(20000, 128, device="cuda")
+    b = torch.randn(20000, 96, device="cuda")
+    ref = (a.double().t() @ b.double()).float()
+    out = gemm.gemm_tn_tf32(a, b)
+    gemm.check()
+    assert float((out - ref).abs().max() / ref.abs().max()) < 3e-3
+    a2, b2 = torch.randn(500, 20, device="cuda"), torch.randn(500, 12, device="cuda")      # not multiples of 32: plain matmul
+    assert torch.allclose(gemm.gemm_tn_tf32(a2, b2), a2.t() @ b2, atol=1e-3)
