@@ -1,7 +1,7 @@
 """Per-kernel device time of one training step under CUDA-graph replay (torch profiler / CUPTI timeline, real
 cache conditions -- unlike ncu, nothing is flushed or serialised).
 
-    python -m gradient_compression_b200.benchmarks.step_profile --model ResNet50
+    python -m gradient_compression_b200.benchmarks.step_profile --model ResNet50 [--eager-ops]
 """
 import argparse
 import collections
@@ -16,6 +16,8 @@ def main(argv=None):
     ap.add_argument("--reducer", default="QSGDMaxNormReducer")
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--eager-ops", action="store_true",
+                    help="run the step eagerly and list the torch operators by device time (which op launches which kernels)")
     args = ap.parse_args(argv)
 
     from .. import make_reducer
@@ -30,7 +32,7 @@ def main(argv=None):
                  synthetic_test_size=args.batch)
     opt = FlatSGD(task.arena, lr=0.1)
     red = make_reducer(args.reducer, dev, None, {"quantization_level": 8, "seed": 1})
-    step = GraphedStep(task, red, opt, enabled=True)
+    step = GraphedStep(task, red, opt, enabled=not args.eager_ops)
     x = torch.randn(args.batch, 3, 32, 32, device=dev).contiguous(memory_format=torch.channels_last)
     y = torch.randint(0, 10, (args.batch,), device=dev)
     for _ in range(8):
@@ -40,6 +42,12 @@ def main(argv=None):
         for _ in range(args.steps):
             step((x, y))
         torch.cuda.synchronize()
+    if args.eager_ops:
+        rows = [(e.key, e.count // args.steps, e.self_device_time_total / args.steps) for e in prof.key_averages()
+                if e.self_device_time_total > 0]
+        for key, cnt, t in sorted(rows, key=lambda r: -r[2])[:40]:
+            print(f"{t:9.1f} us {cnt:4d}  {key[:90]}")
+        return
     agg = collections.defaultdict(lambda: [0, 0.0])
     for ev in prof.events():
         if ev.device_type == torch.autograd.DeviceType.CUDA:

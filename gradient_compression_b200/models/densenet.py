@@ -8,7 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn import bn_act
+from ..ops.bn import bn_act, defer_batch_counters
 from .layers import bn, conv, linear
 
 
@@ -51,6 +51,7 @@ class DenseNet(nn.Module):
                 planes = out_planes
         self.bn = bn(planes)
         self.linear = linear(planes, num_classes)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = self.conv1(x)

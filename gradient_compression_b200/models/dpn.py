@@ -6,7 +6,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn import bn_act
+from ..ops.bn import bn_act, defer_batch_counters
 from .layers import bn, conv, linear
 
 
@@ -44,6 +44,7 @@ class DPN(nn.Module):
                 self.last_planes = cfg["out_planes"][i] + (j + 2) * cfg["dense_depth"][i]
             setattr(self, f"layer{i + 1}", nn.Sequential(*layers))
         self.linear = linear(cfg["out_planes"][3] + (cfg["num_blocks"][3] + 1) * cfg["dense_depth"][3], 10)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))

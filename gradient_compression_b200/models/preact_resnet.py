@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn import bn_act
+from ..ops.bn import bn_act, defer_batch_counters
 from .layers import bn, conv, linear
 
 
@@ -57,6 +57,7 @@ class PreActResNet(nn.Module):
                 self.in_planes = width * block.expansion
             setattr(self, f"layer{i}", nn.Sequential(*blocks))
         self.linear = linear(512 * block.expansion, num_classes)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = self.layer4(self.layer3(self.layer2(self.layer1(self.conv1(x)))))

@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn import bn_act
+from ..ops.bn import bn_act, defer_batch_counters
 from ..ops.conv import GradLink, conv_bn_act
 from .layers import bn, conv, linear
 
@@ -66,6 +66,7 @@ class ResNet(nn.Module):
         for i, (width, depth, stride) in enumerate(zip((64, 128, 256, 512), num_blocks, (1, 2, 2, 2)), start=1):
             setattr(self, f"layer{i}", self._stage(block, width, depth, stride))
         self.linear = linear(512 * block.expansion, num_classes)
+        defer_batch_counters(self)
 
     def _stage(self, block, planes, depth, stride):
         blocks = []

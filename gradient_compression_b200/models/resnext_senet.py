@@ -6,7 +6,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn import bn_act
+from ..ops.bn import bn_act, defer_batch_counters
 from .layers import bn, conv, linear
 
 
@@ -54,6 +54,7 @@ class ResNeXt(nn.Module):
             self.bottleneck_width *= 2
             setattr(self, f"layer{i}", nn.Sequential(*blocks))
         self.linear = linear(cardinality * bottleneck_width * 8, num_classes)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
@@ -126,6 +127,7 @@ class SENet(nn.Module):
                 self.in_planes = width
             setattr(self, f"layer{i}", nn.Sequential(*blocks))
         self.linear = linear(512, num_classes)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
@@ -184,6 +186,7 @@ class RegNet(nn.Module):
                 self.in_planes = cfg["widths"][i]
             setattr(self, f"layer{i + 1}", nn.Sequential(*blocks))
         self.linear = linear(cfg["widths"][-1], num_classes)
+        defer_batch_counters(self)
 
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
@@ -267,6 +270,7 @@ class PNASNet(nn.Module):
         self.layer4 = self._down(num_planes * 4)
         self.layer5 = self._stage(num_planes * 4, num_cells)
         self.linear = linear(num_planes * 4, 10)
+        defer_batch_counters(self)
 
     def _stage(self, planes, n):
         cells = []

@@ -17,7 +17,7 @@ import torch
 
 from . import _native as nat
 from . import gemm
-from .bn import _cl, _scratch_for, bn_act, kernel_path_ok, own_grad, take_owned_grad
+from .bn import _cl, _scratch_for, bn_act, count_batch, kernel_path_ok, own_grad, take_owned_grad
 
 # On by default.  Measured on the CIFAR ResNet-50 step (batch 128, one B200, three back-to-back pairs of runs): 8.04 /
 # 8.28 / 8.26 ms with this path against 8.34 / 8.37 / 8.40 ms with cuDNN convolutions everywhere.  GCB200_TC_CONV=0 (or
@@ -257,7 +257,7 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
     training = bn.training or bn.running_mean is None
     momentum = 0.1 if bn.momentum is None else bn.momentum
     if training and bn.track_running_stats and bn.num_batches_tracked is not None:
-        bn.num_batches_tracked.add_(1)
+        count_batch(bn)
     rm = bn.running_mean if bn.track_running_stats else None
     rv = bn.running_var if bn.track_running_stats else None
     return _Conv1x1BNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,

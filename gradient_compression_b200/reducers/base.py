@@ -18,6 +18,8 @@ Differences from the reference, by design:
 """
 from __future__ import annotations
 
+import functools
+
 import torch
 import torch.distributed as dist
 
@@ -95,6 +97,25 @@ def n_bits(tensor):
     return 8 * tensor.nelement() * tensor.element_size()
 
 
+def physical(t):
+    """The contiguous view of ``t`` in the order its elements lie in memory.  Only 4-D channels-last tensors differ
+    from themselves: [N, C, H, W] strided as NHWC becomes the contiguous [N, H, W, C] view.  Reducers work on element
+    vectors and on matrices whose rows are dim 0, so the order inside a row is theirs to choose; taking the memory
+    order keeps a flat gradient arena zero-copy for channels-last weights."""
+    if t.dim() == 4 and not t.is_contiguous() and t.is_contiguous(memory_format=torch.channels_last):
+        return t.permute(0, 2, 3, 1)
+    return t
+
+
+def _physical_args(reduce_fn):
+    @functools.wraps(reduce_fn)
+    def reduce(self, grad_in, grad_out):
+        return reduce_fn(self, [physical(t) for t in grad_in], [physical(t) for t in grad_out])
+
+    reduce._physical_wrapped = True
+    return reduce
+
+
 class Reducer:
     """Base class of all reducers.
 
@@ -104,6 +125,12 @@ class Reducer:
     """
 
     fused_capable = False
+
+    def __init_subclass__(cls, **kwargs):
+        super().__init_subclass__(**kwargs)
+        fn = cls.__dict__.get("reduce")
+        if fn is not None and not getattr(fn, "_physical_wrapped", False):
+            cls.reduce = _physical_args(fn)         # every reduce() sees contiguous tensors in memory order
 
     def __init__(self, device, timer=None, backend="auto", seed=0, group=None, reference_compat=False):
         if _dist_on():

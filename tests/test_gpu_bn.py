@@ -246,3 +246,35 @@ def test_identity_block_gradient_link(tc_conv, owned):
     assert torch.equal(dy_l, dy)                       # the incoming gradient was not written to
     assert float((gx_l - gx_p).norm() / gx_p.norm()) < 1e-6
     assert float((gw_l - gw_p).norm() / gw_p.norm()) < 1e-6
+
+
+def test_batch_counters_are_batched_but_exact():
+    """``num_batches_tracked`` of every batch norm of a zoo model moves by one per training forward (one multi-tensor
+    launch at the end of the forward), stays put in eval mode, and is counted per use when a layer runs twice."""
+    from gradient_compression_b200 import models
+    from gradient_compression_b200.ops import bn as bnmod
+
+    model = models.ResNet18().cuda()
+    x = torch.randn(4, 3, 32, 32, device="cuda")
+    model.train()
+    for _ in range(3):
+        model(x)
+    assert not bnmod._pending_counters
+    counters = [m.num_batches_tracked for m in model.modules() if isinstance(m, torch.nn.BatchNorm2d)]
+    assert len(counters) > 10 and all(int(c) == 3 for c in counters)
+    model.eval()
+    model(x)
+    assert all(int(c) == 3 for c in counters)
+    # one layer used twice in a forward
+    class Twice(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.bn = torch.nn.BatchNorm2d(8)
+            bnmod.defer_batch_counters(self)
+
+        def forward(self, t):
+            return bnmod.bn_act(self.bn, bnmod.bn_act(self.bn, t))
+
+    tw = Twice().cuda()
+    tw(torch.randn(4, 8, 8, 8, device="cuda").contiguous(memory_format=torch.channels_last))
+    assert int(tw.bn.num_batches_tracked) == 2
