@@ -197,16 +197,21 @@ def run_ours(args, world, rank, local_rank):
 
     e2e = None
     if not args.no_e2e:
-        loader = task.train_dataloader(args.batch)
+        from gradient_compression_b200.train.data import LaggedReadback
+        loader = task.train_dataloader(args.batch)        # pinned host batches; the copy of the next ones runs on a side stream
         it = iter(loader)
+        reader = LaggedReadback(device, lag=1)
         for _ in range(2):
             float(step_fn(next(it)).item())
         barrier_sync()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            batch = next(it)                      # pinned host batch -> device (non_blocking copy inside the loader)
+            batch = next(it)                      # host -> device copy of this step's inputs (issued one step ahead)
             loss = step_fn(batch)
-            loss_host = loss.item()               # device -> host read of the step's result
+            v = reader.push(loss)                 # device -> host read of this step's loss, collected one step later
+            if v is not None:
+                loss_host = v
+        loss_host = reader.drain()[-1]            # the last step's loss is read before the clock stops
         barrier_sync()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, device) / args.steps
         e2e = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,

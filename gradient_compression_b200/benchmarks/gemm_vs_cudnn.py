@@ -36,6 +36,7 @@ def _median_us(fn, flush, iters=10, warmup=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--sweep", action="store_true", help="also time both kernels at every tile width")
+    ap.add_argument("--wgrad", action="store_true", help="time the weight-gradient (TN, split-K) GEMM against cuDNN's wgrad")
     args = ap.parse_args()
     torch.backends.cudnn.benchmark = True
     flush = torch.zeros(64 << 20, device="cuda")
@@ -45,6 +46,21 @@ def main():
         w = torch.randn(n, k, 1, 1, device="cuda").contiguous(memory_format=torch.channels_last)
         a = x.permute(0, 2, 3, 1).reshape(m, k)
         b = w.view(n, k)
+        if args.wgrad:
+            dy = torch.randn(128, n, hw, hw, device="cuda").contiguous(memory_format=torch.channels_last)
+            dy2d = dy.permute(0, 2, 3, 1).reshape(m, n)
+            dw = torch.zeros(n, k, device="cuda")
+            res = {}
+            for ctas, mink in ((2, 8), (1, 8), (4, 8), (2, 4), (2, 16)):
+                gemm.configure_tn(ctas, mink)
+                res[f"ctas{ctas}_min{mink}"] = round(_median_us(lambda: gemm.gemm_tn_tf32(dy2d, a, out=dw, accumulate=True), flush, iters=6), 1)
+            gemm.configure_tn()
+            t_cudnn = _median_us(lambda: torch.ops.aten.convolution_backward(dy, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
+                                                                             [False, True, False]), flush, iters=6)
+            nbytes = 4 * (m * k + m * n)
+            print(json.dumps({"P": m, "Cin": k, "Cout": n, "ours_us": res, "cudnn_us": round(t_cudnn, 1),
+                              "roofline_us": round(nbytes / 6566e3, 1)}))
+            continue
         out = torch.empty(m, n, device="cuda")
         sweep = {}
         if args.sweep:                        # every kernel / tile width, to calibrate the choice

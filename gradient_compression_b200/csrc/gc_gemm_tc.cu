@@ -842,6 +842,10 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// split-K policy of the TN kernel (see gc_cuda_gemm_tn_config).  One CTA per SM: measured 10-25 % faster than two on the
+// 131072- and 32768-position weight gradients of ResNet-50 (fewer partial tiles to add, longer pipelines), equal below.
+int g_tn_ctas_per_sm = 1, g_tn_min_kblocks = 8;
+
 template <int BN>
 int launch_tn(const float* A, const float* B, float* C, int P, int Mo, int No, int64_t lda, int64_t ldb, int64_t ldc,
               int* error_flag, cudaStream_t st) {
@@ -859,9 +863,9 @@ int launch_tn(const float* A, const float* B, float* C, int P, int Mo, int No, i
   int tiles_m = (Mo + BM - 1) / BM, tiles_n = (No + BN - 1) / BN;
   int tiles = tiles_m * tiles_n;
   int total_k = (P + BK - 1) / BK;
-  // about two CTAs per SM over all tiles, at least 8 k-blocks each so that the pipeline fills
-  int splits = (2 * sm_count() + tiles - 1) / tiles;
-  if (splits > (total_k + 7) / 8) splits = (total_k + 7) / 8;
+  // about g_tn_ctas_per_sm CTAs per SM over all tiles, at least g_tn_min_kblocks k-blocks each so that the pipeline fills
+  int splits = (g_tn_ctas_per_sm * sm_count() + tiles - 1) / tiles;
+  if (splits > (total_k + g_tn_min_kblocks - 1) / g_tn_min_kblocks) splits = (total_k + g_tn_min_kblocks - 1) / g_tn_min_kblocks;
   if (splits < 1) splits = 1;
   int per = (total_k + splits - 1) / splits;
   splits = (total_k + per - 1) / per;
@@ -961,6 +965,12 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
     case 128: return launch<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
     default: return launch<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
   }
+}
+
+// For measurements: CTAs per SM the split contraction aims at, and the fewest k-blocks (of 32 rows) a split may get.
+void gc_cuda_gemm_tn_config(int ctas_per_sm, int min_kblocks) {
+  g_tn_ctas_per_sm = ctas_per_sm > 0 ? ctas_per_sm : 1;
+  g_tn_min_kblocks = min_kblocks > 0 ? min_kblocks : 8;
 }
 
 // 1 when C[Mo, No] += A[P, Mo]^T B[P, No] can run on the tensor cores: Mo and No multiples of 32, 16-byte aligned

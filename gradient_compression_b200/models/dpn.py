@@ -7,7 +7,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 class Bottleneck(nn.Module):
@@ -49,7 +49,7 @@ class DPN(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def _cfg(num_blocks):

@@ -6,7 +6,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 class PreActBlock(nn.Module):
@@ -61,7 +61,7 @@ class PreActResNet(nn.Module):
 
     def forward(self, x):
         x = self.layer4(self.layer3(self.layer2(self.layer1(self.conv1(x)))))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def PreActResNet18():

@@ -8,7 +8,7 @@ import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
 from ..ops.conv import GradLink, conv_bn_act
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 def _projection(cin, cout, stride):
@@ -78,8 +78,7 @@ class ResNet(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
-        x = F.avg_pool2d(x, 4)
-        return self.linear(x.flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def ResNet18():

@@ -7,7 +7,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 def _proj(cin, cout, stride):
@@ -59,7 +59,7 @@ class ResNeXt(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer3(self.layer2(self.layer1(x)))
-        return self.linear(F.avg_pool2d(x, 8).flatten(1))
+        return self.linear(head_pool(x, 8))
 
 
 def ResNeXt29_2x64d():
@@ -132,7 +132,7 @@ class SENet(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def SENet18():
@@ -287,7 +287,7 @@ class PNASNet(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer5(self.layer4(self.layer3(self.layer2(self.layer1(x)))))
-        return self.linear(F.avg_pool2d(x, 8).flatten(1))
+        return self.linear(head_pool(x, 8))
 
 
 def PNASNetA():

@@ -8,7 +8,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 def channel_shuffle(x, groups):
@@ -66,7 +66,7 @@ class ShuffleNet(nn.Module):
     def forward(self, x):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer3(self.layer2(self.layer1(x)))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def ShuffleNetG2():
@@ -151,7 +151,7 @@ class ShuffleNetV2(nn.Module):
         x = bn_act(self.bn1, self.conv1(x))
         x = self.layer3(self.layer2(self.layer1(x)))
         x = bn_act(self.bn2, self.conv2(x))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))
 
 
 def ShuffleNetV2_x0_5():

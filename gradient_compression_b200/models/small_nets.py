@@ -7,7 +7,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn import bn_act
-from .layers import bn, conv, linear
+from .layers import bn, conv, head_pool, linear
 
 
 class LeNet(nn.Module):
@@ -107,7 +107,7 @@ class MobileNet(nn.Module):
 
     def forward(self, x):
         x = self.layers(bn_act(self.bn1, self.conv1(x)))
-        return self.linear(F.avg_pool2d(x, 2).flatten(1))
+        return self.linear(head_pool(x, 2))
 
 
 class _InvertedResidual(nn.Module):
@@ -151,4 +151,4 @@ class MobileNetV2(nn.Module):
     def forward(self, x):
         x = self.layers(bn_act(self.bn1, self.conv1(x)))
         x = bn_act(self.bn2, self.conv2(x))
-        return self.linear(F.avg_pool2d(x, 4).flatten(1))
+        return self.linear(head_pool(x, 4))

@@ -122,6 +122,7 @@ def cuda():
         _declare(lib, "gc_cuda_gemm_tf32_supported", c_int, [P, P, c_int, c_int, c_int, c_i64, c_i64])
         _declare(lib, "gc_cuda_gemm_tf32", c_int, [P, P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, c_int, P, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_m_tiles", c_int, [c_int])
+        _declare(lib, "gc_cuda_gemm_tn_config", None, [c_int, c_int])
         _declare(lib, "gc_cuda_gemm_tn_tf32_supported", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64])
         _declare(lib, "gc_cuda_gemm_tn_tf32", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_config", None, [c_int, c_int])

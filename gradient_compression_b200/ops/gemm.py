@@ -106,6 +106,11 @@ def configure(kernel="auto", tile_n=0):
     nat.cuda().gc_cuda_gemm_tf32_config(KERNELS[kernel], int(tile_n))
 
 
+def configure_tn(ctas_per_sm=1, min_kblocks=8):
+    """Split-K policy of ``gemm_tn_tf32`` (for measurements)."""
+    nat.cuda().gc_cuda_gemm_tn_config(int(ctas_per_sm), int(min_kblocks))
+
+
 def m_tiles(m):
     return int(nat.cuda().gc_cuda_gemm_tf32_m_tiles(int(m)))
 

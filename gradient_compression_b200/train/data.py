@@ -103,3 +103,88 @@ class TorchvisionLoaders:
                                       drop_last=True, num_workers=max(world, 2), persistent_workers=True)
             self._bs = batch_size
         return self._loader
+
+
+class DevicePrefetcher:
+    """Iterates over (images, labels) host batches and yields device batches, with the host-to-device copy of the next
+    ``depth`` batches already in flight on a side stream while the caller computes on the current one (pinned host
+    memory makes the copies asynchronous).  ``convert`` maps the copied pair to what the model wants (for example
+    channels-last images); it runs on the side stream too."""
+
+    def __init__(self, batches, device, convert=None, depth=2):
+        self._it = iter(batches)
+        self._device = torch.device(device)
+        self._convert = convert
+        self._depth = max(1, int(depth))
+        self._stream = torch.cuda.Stream(self._device) if self._device.type == "cuda" else None
+        self._queue = []
+
+    def _issue(self):
+        try:
+            imgs, labels = next(self._it)
+        except StopIteration:
+            return False
+        if self._stream is None:
+            out = (imgs.to(self._device), labels.to(self._device))
+            self._queue.append((self._convert(*out) if self._convert else out, None))
+            return True
+        with torch.cuda.stream(self._stream):
+            out = (imgs.to(self._device, non_blocking=True), labels.to(self._device, non_blocking=True))
+            if self._convert:
+                out = self._convert(*out)
+            ev = torch.cuda.Event()
+            ev.record(self._stream)
+        self._queue.append((out, ev))
+        return True
+
+    def __iter__(self):
+        while len(self._queue) < self._depth and self._issue():
+            pass
+        while self._queue:
+            out, ev = self._queue.pop(0)
+            if ev is not None:
+                torch.cuda.current_stream(self._device).wait_event(ev)
+                for t in out:
+                    t.record_stream(torch.cuda.current_stream(self._device))
+            self._issue()                       # keep the pipeline full before handing the batch out
+            yield out
+
+
+class LaggedReadback:
+    """Device scalars read on the host one step late: ``push(t)`` starts an asynchronous copy of ``t`` into pinned host
+    memory and returns the value pushed ``lag`` calls earlier (``None`` until there is one), so that reading the loss
+    of every step never stalls the stream that is computing the next one.  ``drain()`` returns what is still pending."""
+
+    def __init__(self, device, lag=1):
+        self._device = torch.device(device)
+        self._lag = max(1, int(lag))
+        self._pending = []
+        self._free = []
+
+    def push(self, t):
+        if self._device.type != "cuda":
+            self._pending.append((float(t), None, None))
+        else:
+            buf = self._free.pop() if self._free else torch.empty(1, dtype=torch.float32).pin_memory()
+            buf.copy_(t.detach().reshape(1).float(), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self._device))
+            self._pending.append((None, buf, ev))
+        if len(self._pending) > self._lag:
+            return self._take()
+        return None
+
+    def _take(self):
+        val, buf, ev = self._pending.pop(0)
+        if buf is None:
+            return val
+        ev.synchronize()
+        val = float(buf[0])
+        self._free.append(buf)
+        return val
+
+    def drain(self):
+        out = []
+        while self._pending:
+            out.append(self._take())
+        return out

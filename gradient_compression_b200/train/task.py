@@ -84,11 +84,25 @@ class CIFAR:
             imgs = imgs.contiguous(memory_format=torch.channels_last)
         return imgs, labels
 
-    def train_dataloader(self, batch_size=32):
+    def _convert(self, imgs, labels):
+        if self._channels_last:
+            imgs = imgs.contiguous(memory_format=torch.channels_last)
+        return imgs, labels
+
+    def train_dataloader(self, batch_size=32, prefetch=None):
+        """Device batches of one epoch.  ``prefetch`` (default: on for host-resident data and a CUDA device): the copy of
+        the next batches runs on a side stream while the current step computes (``DevicePrefetcher``)."""
         loader = self._train_set.loader(batch_size, self._epoch)
         self.len_train_loader = len(loader)
-        for imgs, labels in loader:
-            yield self._to_device(imgs, labels)
+        if prefetch is None:
+            prefetch = self._device.type == "cuda" and self._data_kind in ("synthetic", "cifar10")
+        if prefetch:
+            from .data import DevicePrefetcher
+
+            yield from DevicePrefetcher(loader, self._device, convert=self._convert, depth=2)
+        else:
+            for imgs, labels in loader:
+                yield self._to_device(imgs, labels)
         self._epoch += 1
 
     def test_dataloader(self, batch_size=32):
