@@ -50,3 +50,46 @@ def test_gpu_batches_match_cpu_oracle_bit_for_bit():
         xc, yc = cpu.batch(128, epoch, index)
         xg, yg = gpu.batch(128, epoch, index)
         assert torch.equal(xg.cpu(), xc) and torch.equal(yg.cpu(), yc)
+
+
+def _host_batches(n=5):
+    g = torch.Generator().manual_seed(9)
+    return [(torch.randn(4, 3, 8, 8, generator=g), torch.randint(0, 10, (4,), generator=g)) for _ in range(n)]
+
+
+def test_prefetcher_and_lagged_readback_on_cpu():
+    from gradient_compression_b200.train.data import DevicePrefetcher, LaggedReadback
+
+    batches = _host_batches()
+    got = list(DevicePrefetcher(batches, "cpu", depth=2))
+    assert len(got) == len(batches) and all(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) for a, b in zip(got, batches))
+    r = LaggedReadback("cpu", lag=1)
+    seen = [r.push(torch.tensor(float(i))) for i in range(4)]
+    assert seen == [None, 0.0, 1.0, 2.0] and r.drain() == [3.0]
+
+
+@pytest.mark.gpu
+def test_prefetcher_and_lagged_readback_on_gpu():
+    """Batches arrive complete and in order although their copies run ahead on a side stream; scalars read one step
+    late are the values of their own step even when the producing tensor is overwritten in place afterwards."""
+    from gradient_compression_b200.train.data import DevicePrefetcher, LaggedReadback
+
+    batches = [(x.pin_memory(), y.pin_memory()) for x, y in _host_batches(8)]
+    conv = lambda x, y: (x.contiguous(memory_format=torch.channels_last), y)
+    got = []
+    for x, y in DevicePrefetcher(batches, "cuda", convert=conv, depth=3):
+        assert x.is_cuda and x.is_contiguous(memory_format=torch.channels_last)
+        got.append((x.sum() * 1.0, y.clone()))              # consume on the current stream
+    assert len(got) == 8
+    for (s, y), (hx, hy) in zip(got, batches):
+        assert abs(float(s) - float(hx.sum())) < 1e-3 and torch.equal(y.cpu(), hy)
+    r = LaggedReadback("cuda", lag=1)
+    static = torch.zeros((), device="cuda")
+    out = []
+    for i in range(5):
+        static.fill_(float(i))                              # the same tensor every step, as a replayed graph's output
+        v = r.push(static)
+        if v is not None:
+            out.append(v)
+    out += r.drain()
+    assert out == [0.0, 1.0, 2.0, 3.0, 4.0]
