@@ -142,6 +142,17 @@ def case_gemm_narrow(n):
     return (lambda: gemm.gemm_tf32(a, b, out=out)), 4 * (m * k + nn * k + m * nn), "gemm_tf32_persistent_kernel<64>"
 
 
+def case_gemm_tn(n):
+    """Weight gradient of a first-stage 1x1 convolution: dW[256, 64] = dY[131072, 256]^T X[131072, 64] (168 MB of reads)."""
+    from ..ops import gemm
+    p, mo, no = 131072, 256, 64
+    a = torch.randn(p, mo, device="cuda")
+    b = torch.randn(p, no, device="cuda")
+    out = torch.zeros(mo, no, device="cuda")
+    return (lambda: gemm.gemm_tn_tf32(a, b, out=out, accumulate=True)), 4 * (p * mo + p * no), \
+        "gemm_tn_tf32_kernel<64>: MN-major tcgen05 operands, split-K over 148 CTAs, TMA reduce stores"
+
+
 def case_gemm_deep(n):
     """Compute-heavier GEMM: [8192, 2048] x [2048, 2048]^T (69 GFLOP)."""
     from ..ops import gemm
@@ -154,7 +165,7 @@ def case_gemm_deep(n):
 
 
 CASES = {"qsgd": case_qsgd, "absmax": case_absmax, "sgd": case_sgd, "pack": case_pack, "bn_fwd": case_bn_fwd,
-         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_narrow": case_gemm_narrow,
+         "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_narrow": case_gemm_narrow, "gemm_tn": case_gemm_tn,
          "gemm_deep": case_gemm_deep}
 
 
