@@ -37,6 +37,45 @@ def _digest(paths, extra=""):
     return h.hexdigest()
 
 
+def _flags_only(cmd):
+    """The part of a compiler command that decides what gets built: everything except absolute paths, so that a library
+    built in one checkout is recognised as current when the tree is copied somewhere else."""
+    return " ".join(os.path.basename(c) if os.path.isabs(c) else c for c in cmd)
+
+
+class _BuildLock:
+    """Exclusive lock for the library directory: ranks of one job that all find a stale library build it once."""
+
+    def __init__(self):
+        self._f = None
+
+    def __enter__(self):
+        import fcntl
+
+        os.makedirs(LIBDIR, exist_ok=True)
+        self._f = open(os.path.join(LIBDIR, ".build.lock"), "w")
+        fcntl.flock(self._f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+
+        fcntl.flock(self._f, fcntl.LOCK_UN)
+        self._f.close()
+
+
+def _compile(cmd, out):
+    """Run the compiler into a temporary file and move it into place, so that nobody ever loads a half-written library."""
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [tmp if c == out else c for c in cmd]
+    try:
+        subprocess.run(cmd, check=True)
+        os.replace(tmp, out)
+    finally:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+
+
 def _stale(lib, digest):
     stamp = lib + ".sha256"
     if not os.path.exists(lib) or not os.path.exists(stamp):
@@ -63,15 +102,17 @@ def build_host(force=False, verbose=False):
     srcs = _sources(HOST_SOURCES)
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-Wno-unknown-pragmas",
            "-I", CSRC, "-o", host_lib_path()] + srcs
-    digest = _digest(srcs, " ".join(cmd))
+    digest = _digest(srcs, _flags_only(cmd))
     if not force and not _stale(host_lib_path(), digest):
         return host_lib_path()
     if shutil.which("g++") is None:
         raise RuntimeError("g++ not found: cannot build libgcb200_host.so")
-    if verbose:
-        print(" ".join(cmd))
-    subprocess.run(cmd, check=True)
-    _finish(host_lib_path(), digest)
+    with _BuildLock():
+        if force or _stale(host_lib_path(), digest):          # another process may have built it while we waited
+            if verbose:
+                print(" ".join(cmd))
+            _compile(cmd, host_lib_path())
+            _finish(host_lib_path(), digest)
     return host_lib_path()
 
 
@@ -89,15 +130,17 @@ def build_cuda(force=False, verbose=False, ptxas_info=False):
     if ptxas_info:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
-    digest = _digest(srcs, " ".join(c for c in cmd if c not in ("-Xptxas", "-v")))
+    digest = _digest(srcs, _flags_only([c for c in cmd if c not in ("-Xptxas", "-v")]))
     if not force and not _stale(cuda_lib_path(), digest):
         return cuda_lib_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libgcb200_cuda.so")
-    if verbose:
-        print(" ".join(cmd))
-    subprocess.run(cmd, check=True)
-    _finish(cuda_lib_path(), digest)
+    with _BuildLock():
+        if force or _stale(cuda_lib_path(), digest):
+            if verbose:
+                print(" ".join(cmd))
+            _compile(cmd, cuda_lib_path())
+            _finish(cuda_lib_path(), digest)
     return cuda_lib_path()
 
 
