@@ -1,15 +1,19 @@
-// TF32 GEMM on the 5th-generation tensor cores:  C[M, N] (fp32) = A[M, K] * B[N, K]^T (+ bias[N]),
-// A and B row-major with K contiguous ("K-major"), fp32 in memory, kind::tf32 in the MMA (the tensor core
-// reads the upper 19 bits of every fp32 word -- the same precision cuDNN uses for the reference's
-// convolutions).  Shapes this serves: 1x1 convolutions on channels-last activations (A = activations
-// [N*H*W, Cin], B = weight [Cout, Cin]), linear layers, and PowerSGD's P = M Q with Q stored transposed.
+// TF32 GEMMs on the 5th-generation tensor cores, fp32 in memory, kind::tf32 in the MMA (the tensor core reads
+// the upper 19 bits of every fp32 word -- the same precision cuDNN uses for the reference's convolutions).
 //
-// One CTA per 128 x BN output tile, no clusters, no multicast:
+//   gemm_tf32_persistent_kernel  C[M, N] (=, +=) A[M, K] * B[N, K]^T (+ bias): both operands K-major.  1x1 convolutions
+//                                on channels-last activations (A = activations [N*H*W, Cin], B = weight [Cout, Cin]) and
+//                                their input gradients; optional per-column sums of C (batch-norm statistics) from the
+//                                epilogue.  One CTA per SM walks the tiles with a double-buffered TMEM accumulator.
+//   gemm_tf32_kernel             the same product with one CTA per 128 x BN tile: narrow outputs (N <= 16) and outputs that
+//                                do not meet the TMA store rules (plain-store epilogue).
+//   gemm_tn_tf32_kernel          C[Mo, No] += A[P, Mo]^T * B[P, No]: both operands MN-major, split-K.  Weight gradients.
+//
+// Common structure, no clusters, no multicast:
 //   warp 0   TMA producer: cp.async.bulk.tensor.2d (128-byte swizzle) into a ring of shared-memory stages
 //   warp 1   allocates TMEM, issues tcgen05.mma (one elected thread), commits stages back to the producer
-//   warps 2-5  epilogue: tcgen05.ld of the 128 x BN fp32 accumulator from TMEM, bias add, then either a TMA
-//              store of 32-column slabs staged (128-byte swizzled, bank-conflict free) in the drained pipeline
-//              buffers, or plain stores when C does not meet the TMA alignment rules
+//   warps 2+ epilogue: tcgen05.ld of the fp32 accumulator from TMEM, bias add, 32-column slabs staged in shared
+//            memory (128-byte swizzled, bank-conflict free) and written with TMA stores / TMA reduce stores
 // Every mbarrier wait is bounded; when one runs out the CTA sets *error_flag, abandons its tile, frees
 // its TMEM and returns.
 #include <cuda.h>

@@ -1,12 +1,18 @@
-"""1x1 convolution + batch norm (+ residual) (+ ReLU) with the convolution on the tcgen05 GEMM.
+"""1x1 convolution + batch norm (+ residual) (+ ReLU) with the convolution on the tcgen05 GEMMs.
 
 ``conv_bn_act(conv, bn, x, residual=None, relu=True)`` is ``relu(bn(conv(x)) + residual)``.  For a 1x1,
 stride-1, ungrouped convolution on channels-last fp32 CUDA tensors the convolution is the GEMM
 ``[N*H*W, Cin] x [Cout, Cin]^T`` (``ops.gemm_tf32``: TMA + tcgen05.mma kind::tf32 + TMEM), whose epilogue also
 emits the per-channel sums the batch norm needs -- the normalisation statistics are fused into the producing
 kernel, so the activation is written once and read once (by the apply pass) instead of written, read for the
-statistics and read again.  Backward: fused BN backward kernels, input gradient on the same GEMM
-(``dY x W``), weight gradient through cuDNN.  Every other convolution falls back to ``bn_act(bn, conv(x))``.
+statistics and read again.  Backward: fused BN backward kernels; input gradient ``dY x W`` on the same GEMM
+(reading transposed weights that one batched kernel refreshes after every optimiser step, and, in identity
+blocks, adding its result onto the skip connection's gradient: ``GradLink``); weight gradient ``dY^T X`` on the
+split-K GEMM with MN-major operands (``ops.gemm_tn_tf32``).  Every other convolution (3x3, strided, grouped,
+fewer than ``MIN_ROWS`` positions) falls back to ``bn_act(bn, conv(x))`` with cuDNN's convolution.
+
+The reference builds the same layers from ``nn.Conv2d`` + ``nn.BatchNorm2d`` + ``F.relu`` module calls
+(models/resnet.py:45-76 of the reference).
 """
 from __future__ import annotations
 

@@ -1,7 +1,9 @@
 """TF32 tensor-core GEMM (``csrc/gc_gemm_tc.cu``: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue).
 
 ``gemm_tf32(a, b_nk, bias=None)`` returns ``a @ b_nk.T (+ bias)`` for row-major fp32 ``a [M, K]`` and
-``b_nk [N, K]``.  On CPU (and for shapes the TMA rules exclude) it is a plain fp32 matmul.
+``b_nk [N, K]`` (optionally accumulating onto ``out`` and emitting column statistics);
+``gemm_tn_tf32(a_pm, b_pn)`` returns ``a_pm.T @ b_pn`` with the contraction over the rows (weight gradients).
+On CPU (and for shapes the TMA rules exclude) both are plain fp32 matmuls.
 """
 from __future__ import annotations
 
