@@ -1,6 +1,7 @@
 """Analysis helpers: log parsing (including the reference's committed logs), headless SVG figures and the
 analytic performance model."""
 import os
+import time
 
 import numpy as np
 import pytest
@@ -31,7 +32,7 @@ def test_figures_from_synthetic_logs(tmp_path):
         t = Timer(verbosity_level=2, quiet=True, skip_first=False)
         for label in plots.TIME_LABELS + ["batch"]:
             with t(label):
-                pass
+                time.sleep(0.0005)          # a measurable duration whatever the clock resolution
         for ep in range(3):
             m = AverageMeter("cpu")
             m.add({"top1_accuracy": 0.1 * ep, "top5_accuracy": 0.2 * ep, "cross_entropy_loss": 2.0 - ep * 0.5})
