@@ -121,25 +121,53 @@ def nvcc_path():
     return cand if os.path.exists(cand) else None
 
 
+def _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose):
+    """One ``nvcc -c`` per source, all at once: the sources are independent translation units."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    os.makedirs(objdir, exist_ok=True)
+    flags = NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-I", CSRC]
+    if ptxas_info:
+        flags = ["-Xptxas", "-v"] + flags
+
+    def one(src):
+        obj = os.path.join(objdir, os.path.basename(src) + f".{os.getpid()}.o")
+        cmd = [nvcc] + flags + ["-c", src, "-o", obj]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.run(cmd, check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(srcs), os.cpu_count() or 4)) as pool:
+        return list(pool.map(one, srcs))
+
+
 def build_cuda(force=False, verbose=False, ptxas_info=False):
     os.makedirs(LIBDIR, exist_ok=True)
     srcs = _sources(CUDA_SOURCES)
     nvcc = nvcc_path()
-    cmd = [nvcc or "nvcc"] + NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
-                                        "-I", CSRC, "-o", cuda_lib_path()] + srcs
-    if ptxas_info:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    digest = _digest(srcs, _flags_only([c for c in cmd if c not in ("-Xptxas", "-v")]))
+    # what decides the result: compiler, flags and sources (the stamp also covers every header)
+    recipe = [nvcc or "nvcc"] + NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
+                                           "-I", CSRC, "-o", cuda_lib_path()] + srcs
+    digest = _digest(srcs, _flags_only(recipe))
     if not force and not _stale(cuda_lib_path(), digest):
         return cuda_lib_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libgcb200_cuda.so")
     with _BuildLock():
         if force or _stale(cuda_lib_path(), digest):
-            if verbose:
-                print(" ".join(cmd))
-            _compile(cmd, cuda_lib_path())
+            objdir = os.path.join(LIBDIR, "obj")
+            objs = []
+            try:
+                objs = _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose)
+                link = [nvcc] + NVCC_ARCH + ["-shared", "-Xcompiler", "-fPIC", "-o", cuda_lib_path()] + objs
+                if verbose:
+                    print(" ".join(link))
+                _compile(link, cuda_lib_path())
+            finally:
+                for o in objs:
+                    if os.path.exists(o):
+                        os.remove(o)
             _finish(cuda_lib_path(), digest)
     return cuda_lib_path()
 
