@@ -424,3 +424,28 @@ void gc_host_augment(const uint8_t* images, const int64_t* labels, int64_t n_ima
 }
 
 }  // extern "C"
+
+#include "gc_conv_geom.h"
+
+extern "C" {
+
+// Geometry of the implicit-GEMM tiling of a 3x3 convolution (gc_conv_geom.h): out = {box_w, box_h, box_n, cblocks,
+// tiles, kblocks}; returns 0 for shapes the tiling does not cover.
+int gc_host_conv3x3_geom(int N, int H, int W, int C, int* out) {
+  gc::Conv3x3Geom g;
+  if (!gc::conv3x3_geom(N, H, W, C, &g)) return 0;
+  out[0] = g.box_w; out[1] = g.box_h; out[2] = g.box_n; out[3] = g.cblocks; out[4] = g.tiles; out[5] = g.kblocks;
+  return 1;
+}
+
+// Box coordinates {c, w, h, n} of (tile, k-block).
+int gc_host_conv3x3_box(int N, int H, int W, int C, int tile, int kb, int* coord) {
+  gc::Conv3x3Geom g;
+  if (!gc::conv3x3_geom(N, H, W, C, &g) || tile < 0 || tile >= g.tiles || kb < 0 || kb >= g.kblocks) return 0;
+  int c[4];
+  gc::conv3x3_box(g, tile, kb, c);
+  for (int i = 0; i < 4; ++i) coord[i] = c[i];
+  return 1;
+}
+
+}  // extern "C"

@@ -62,6 +62,8 @@ def host():
         _declare(lib, "gc_host_gram_schmidt", None, [P, c_i64, c_int, c_float])
         _declare(lib, "gc_host_topk_abs", None, [P, c_i64, c_i64, P])
         _declare(lib, "gc_host_sgd_step", None, [P, P, P, c_i64, c_float, c_float, c_float, c_int])
+        _declare(lib, "gc_host_conv3x3_geom", c_int, [c_int, c_int, c_int, c_int, P])
+        _declare(lib, "gc_host_conv3x3_box", c_int, [c_int, c_int, c_int, c_int, c_int, c_int, P])
         _declare(lib, "gc_host_augment", None, [P, P, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int, c_int, P, P, P, P])
         _declare(lib, "gc_host_elias_encode", c_i64, [P, c_i64, c_float, P, c_i64])
         _declare(lib, "gc_host_elias_decode", c_i64, [P, c_i64, P, P, c_i64])
