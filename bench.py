@@ -216,7 +216,9 @@ def run_ours(args, world, rank, local_rank):
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, device) / args.steps
         e2e = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": args.batch * 3 * 32 * 32 * 4 + args.batch * 8, "d2h_bytes_per_step": 4,
-               "last_loss": loss_host}
+               "last_loss": loss_host,
+               "pipelining": "every step copies one batch host->device (issued two steps ahead on a side stream) and reads one "
+                             "loss device->host (collected one step late); the last loss is read before the clock stops"}
     from gradient_compression_b200.ops import conv as conv_ops
     conv_path = ("1x1 (stride 1, >= %d positions): own tcgen05 TF32 GEMM with BN statistics in the epilogue, forward and "
                  "input gradient; other convolutions and weight gradients: cuDNN" % conv_ops.MIN_ROWS) if conv_ops.ENABLED \
