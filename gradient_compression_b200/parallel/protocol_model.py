@@ -1,0 +1,152 @@
+"""Host-side model checker for the flag / epoch protocol of the fused collectives (``csrc/gc_comm.cuh``).
+
+The fused kernels synchronise ranks with monotonically increasing epochs: ``signal_all(phase, epoch)`` stores the
+epoch into ``flag[phase][me]`` of every peer, ``wait_all(phase, epoch)`` spins until every ``flag[phase][*]`` of the
+own header has reached it, and ``exchange_max`` writes ``(epoch, value)`` into a slot chosen by the epoch's parity.
+Nothing is ever reset between steps, so correctness rests on ordering arguments of the kind "rank A can only overwrite
+buffer X in step e + 1 after rank B, which reads X in step e, has signalled something that A waits for".  This module
+checks those arguments mechanically: every kernel is written down as the sequence of its remotely visible actions
+(writes into the own or a peer's arena, reads from them, signals, waits), each rank runs that sequence for a number of
+steps, and ALL interleavings of the ranks' actions are explored (depth-first, with memoised states).  Every value
+carries the epoch it was written in; a read that finds any other epoch than its own step's is a violation (a stale read
+is a missing wait, a too-new one is an overwrite that came too early), and a state in which no rank can move is a
+deadlock.
+
+The model treats a rank as one sequential agent: inside a rank the per-rank grid barrier of the kernels makes every
+phase complete before the next signal is sent.  Memory is sequentially consistent, which is what the system-scope
+release stores / acquire loads of the flags provide for data written before a signal and read after the matching wait.
+
+The reference has no counterpart (it blocks on one NCCL collective after the other: reducer.py:520-549).
+"""
+from __future__ import annotations
+
+# A kernel = list of operations of ONE step, executed by every rank with its own rank id r and the step's epoch e:
+#   ("write_own", region)    r writes its part of `region` in its own arena
+#   ("write_peers", region)  r writes its part of `region` in EVERY rank's arena (a push), one action per target
+#   ("read_peers", region)   r reads, from every rank q's arena, the part of `region` that q wrote itself
+#   ("read_own", region)     r reads, from its own arena, the parts of `region` every rank pushed there
+#   ("signal", phase)        flag[phase][r] := e in every rank's header, one action per target
+#   ("wait", phase)          blocks until flag[phase][q] >= e for every q in the own header
+#   ("norm",)                exchange_max: slot[e & 1][r] := e in every header, then block until every own slot[e & 1][q] == e
+#                            (("norm", "single") models one slot per source instead of two: a seeded fault for the tests)
+# A region name may contain "{p}", replaced by the epoch's parity (buffers double-buffered by parity).
+KERNELS = {
+    # quantise + pack -> READY -> owner-pull reduce of the peers' packed rows, push of the sums -> DONE -> dequantise
+    "qsgd": [("norm",), ("write_own", "packed"), ("signal", "READY"), ("wait", "READY"), ("read_peers", "packed"),
+             ("write_peers", "sums"), ("signal", "DONE"), ("wait", "DONE"), ("read_own", "sums")],
+    # the two-scale / multi-scale kernels add the vote round: votes -> MASK -> read everybody's votes
+    "twoscale": [("norm",), ("write_own", "votes"), ("signal", "MASK"), ("wait", "MASK"), ("read_peers", "votes"),
+                 ("write_own", "packed"), ("signal", "READY"), ("wait", "READY"), ("read_peers", "packed"),
+                 ("write_peers", "sums"), ("signal", "DONE"), ("wait", "DONE"), ("read_own", "sums")],
+    # two-shot fp32 all-reduce
+    "allreduce": [("write_own", "stage"), ("signal", "STAGE"), ("wait", "STAGE"), ("read_peers", "stage"),
+                  ("write_peers", "result"), ("signal", "DONE"), ("wait", "DONE"), ("read_own", "result")],
+    # one-shot sum of a short vector: no closing round, the buffer is double-buffered by epoch parity instead
+    "small_sum": [("write_own", "buf{p}"), ("signal", "AUX"), ("wait", "AUX"), ("read_peers", "buf{p}")],
+    # shared-index Rand-K (two-scale form): votes and quantised levels are one-shot and parity double-buffered; the norm
+    # exchange at the start of the next launches is what keeps a fast rank from lapping a slow one
+    "randk": [("norm",), ("write_own", "mask{p}"), ("signal", "MASK"), ("wait", "MASK"), ("read_peers", "mask{p}"),
+              ("write_own", "levels{p}"), ("signal", "READY"), ("wait", "READY"), ("read_peers", "levels{p}")],
+    # sparse (index, value) exchange of the Top-K reducers: lists published once, read by everybody
+    "sparse": [("write_own", "lists{p}"), ("signal", "AUX"), ("wait", "AUX"), ("read_peers", "lists{p}")],
+}
+
+
+class ProtocolViolation(AssertionError):
+    pass
+
+
+def _expand(kernel_ops, world, rank, epoch):
+    """Micro-actions of one step of one rank: (kind, target rank, name, epoch)."""
+    acts = []
+    for op in kernel_ops:
+        kind = op[0]
+        name = op[1].replace("{p}", str(epoch & 1)) if len(op) > 1 else ""
+        if kind == "write_own":
+            acts.append(("write", rank, name, epoch))
+        elif kind == "write_peers":
+            acts += [("write", q, name, epoch) for q in range(world)]
+        elif kind == "read_peers":
+            acts += [("read_self_written", q, name, epoch) for q in range(world)]
+        elif kind == "read_own":
+            acts += [("read_pushed", q, name, epoch) for q in range(world)]          # q = the rank that pushed the part
+        elif kind == "signal":
+            acts += [("flag", q, name, epoch) for q in range(world)]
+        elif kind == "wait":
+            acts.append(("wait", rank, name, epoch))
+        elif kind == "norm":
+            slot = "0" if name == "single" else str(epoch & 1)      # ("norm", "single"): what would happen without the parity
+            acts += [("slot", q, slot, epoch) for q in range(world)]
+            acts.append(("wait_slots", rank, slot, epoch))
+        else:
+            raise ValueError(f"unknown operation {op!r}")
+    return acts
+
+
+def _program(schedule, world, rank):
+    """All micro-actions of a rank for a schedule = list of kernel names or operation lists, one launch per entry."""
+    acts = []
+    for step, k in enumerate(schedule):
+        acts += _expand(KERNELS[k] if isinstance(k, str) else k, world, rank, step + 1)
+    return acts
+
+
+def check(schedule, world=2, max_states=2_000_000):
+    """Explore every interleaving of ``world`` ranks running ``schedule`` (launch i uses epoch i + 1 on every rank).
+    Returns the number of distinct states visited; raises ``ProtocolViolation`` with a witness trace otherwise."""
+    programs = [_program(schedule, world, r) for r in range(world)]
+    # memory: data[(owner, region, writer)] = epoch; flags[(owner, phase, source)] = epoch; slots[(owner, parity, source)] = epoch
+    start = (tuple(0 for _ in range(world)), (), (), ())
+    seen = {start}
+    stack = [(start, ())]
+    while stack:
+        (pcs, data_t, flags_t, slots_t), trace = stack.pop()
+        data, flags, slots = dict(data_t), dict(flags_t), dict(slots_t)
+        moved = False
+        for r in range(world):
+            if pcs[r] >= len(programs[r]):
+                continue
+            kind, q, name, e = programs[r][pcs[r]]
+            nd, nf, ns = data, flags, slots
+            if kind == "wait":
+                if any(flags.get((r, name, s), 0) < e for s in range(world)):
+                    continue                                            # blocked
+            elif kind == "wait_slots":
+                if any(slots.get((r, name, s), 0) != e for s in range(world)):
+                    if any(slots.get((r, name, s), 0) > e for s in range(world)):
+                        raise ProtocolViolation(f"rank {r}, epoch {e}: a norm slot was overwritten before it was read\n"
+                                                + _format(trace))
+                    continue
+            elif kind == "write":
+                nd = dict(data)
+                nd[(q, name, r)] = e
+            elif kind == "flag":
+                nf = dict(flags)
+                nf[(q, name, r)] = e
+            elif kind == "slot":
+                ns = dict(slots)
+                ns[(q, name, r)] = e
+            elif kind in ("read_self_written", "read_pushed"):
+                key = (q, name, q) if kind == "read_self_written" else (r, name, q)
+                got = data.get(key, 0)
+                if got != e:
+                    what = "stale data (a wait is missing)" if got < e else "data of a later step (overwritten too early)"
+                    raise ProtocolViolation(f"rank {r}, epoch {e}: read of {name!r} "
+                                            f"{'written by' if kind == 'read_self_written' else 'pushed by'} rank {q} "
+                                            f"found epoch {got}: {what}\n" + _format(trace + ((r, kind, q, name, e),)))
+            moved = True
+            npcs = pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:]
+            state = (npcs, tuple(sorted(nd.items())), tuple(sorted(nf.items())), tuple(sorted(ns.items())))
+            if state not in seen:
+                if len(seen) >= max_states:
+                    raise RuntimeError("state budget exhausted: use fewer ranks or steps")
+                seen.add(state)
+                stack.append((state, trace + ((r, kind, q, name, e),)))
+        if not moved and any(pcs[r] < len(programs[r]) for r in range(world)):
+            raise ProtocolViolation("deadlock: no rank can move\n" + _format(trace))
+    return len(seen)
+
+
+def _format(trace, last=24):
+    lines = [f"  rank {r}: {kind} {name!r} -> rank {q} (epoch {e})" for (r, kind, q, name, e) in trace[-last:]]
+    return "last actions of one violating interleaving:\n" + "\n".join(lines)

@@ -1,0 +1,51 @@
+"""Exhaustive interleaving check of the fused collectives' flag / epoch protocol, and proof that the checker finds the
+faults the protocol is designed against."""
+import pytest
+
+from gradient_compression_b200.parallel.protocol_model import KERNELS, ProtocolViolation, check
+
+
+@pytest.mark.parametrize("kernel", sorted(KERNELS))
+@pytest.mark.parametrize("world,steps", [(2, 4), (3, 2)])
+def test_every_kernel_is_safe_over_consecutive_steps(kernel, world, steps):
+    assert check([kernel] * steps, world) > 0
+
+
+def test_powersgd_launch_chain_and_mixed_sequences():
+    # PowerSGD: three one-shot sums per training step (P, rank-1 tensors, Q), two training steps
+    assert check(["small_sum"] * 6, 2) > 0
+    assert check(["small_sum", "small_sum", "qsgd", "small_sum", "allreduce", "small_sum"], 2) > 0
+    assert check(["qsgd", "twoscale", "allreduce"], 3) > 0
+
+
+def _without(kernel, op):
+    ops = list(KERNELS[kernel])
+    ops.remove(op)
+    return ops
+
+
+def test_seeded_faults_are_found():
+    # one-shot sum without the parity double buffer: the fast rank overwrites what the slow one still has to read
+    single = [("write_own", "buf"), ("signal", "AUX"), ("wait", "AUX"), ("read_peers", "buf")]
+    with pytest.raises(ProtocolViolation, match="later step"):
+        check([single] * 2, 2)
+    # all-reduce that does not wait for DONE: results are read before every peer has pushed its part
+    with pytest.raises(ProtocolViolation, match="stale"):
+        check([_without("allreduce", ("wait", "DONE"))], 2)
+    # all-reduce without the closing round at all: the next step's staging overwrites a buffer still being reduced
+    no_done = [op for op in KERNELS["allreduce"] if op[1:] != ("DONE",) and op != ("read_own", "result")]
+    with pytest.raises(ProtocolViolation, match="later step"):
+        check([no_done] * 2, 2)
+    # READY signalled before the packed levels are written
+    early = list(KERNELS["qsgd"])
+    i, j = early.index(("write_own", "packed")), early.index(("signal", "READY"))
+    early[i], early[j] = early[j], early[i]
+    with pytest.raises(ProtocolViolation, match="stale"):
+        check([early], 2)
+    # a single norm slot per source instead of two: the next step's norm lands before the previous one was read
+    with pytest.raises(ProtocolViolation):
+        check([[("norm", "single")]] * 2, 2)
+    assert check([[("norm",)]] * 4, 2) > 0
+    # a wait for a signal nobody sends
+    with pytest.raises(ProtocolViolation, match="deadlock"):
+        check([[("wait", "READY")]], 2)
