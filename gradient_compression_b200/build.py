@@ -116,6 +116,21 @@ def build_host(force=False, verbose=False):
     return host_lib_path()
 
 
+def build_host_sanitized(verbose=False):
+    """The host library with AddressSanitizer and UndefinedBehaviorSanitizer, as ``libgcb200_host_san.so``.  Use:
+    ``GCB200_HOST_LIB=<that file> ASAN_OPTIONS=detect_leaks=0 LD_PRELOAD=$(gcc -print-file-name=libasan.so) python -m pytest
+    tests/test_philox_quant.py`` -- the oracles, packers and coders then run with every access and shift checked."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    out = os.path.join(LIBDIR, "libgcb200_host_san.so")
+    cmd = ["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-fsanitize=address,undefined",
+           "-fno-omit-frame-pointer", "-Wno-unknown-pragmas", "-I", CSRC, "-o", out] + _sources(HOST_SOURCES)
+    if verbose:
+        print(" ".join(cmd))
+    with _BuildLock():
+        _compile(cmd, out)
+    return out
+
+
 def nvcc_path():
     cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     return cand if os.path.exists(cand) else None
@@ -177,6 +192,9 @@ def build_all(force=False, verbose=False):
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print(build_host_sanitized(verbose=True))
+        sys.exit(0)
     force = "--force" in sys.argv
     print(build_host(force, verbose=True))
     print(build_cuda(force, verbose=True, ptxas_info="--ptxas" in sys.argv))

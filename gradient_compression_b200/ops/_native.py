@@ -34,7 +34,10 @@ def host():
     global _host
     if _host is None:
         path = _build.host_lib_path()
-        if not os.path.exists(path) or os.environ.get("GCB200_REBUILD"):
+        override = os.environ.get("GCB200_HOST_LIB")           # e.g. the sanitizer build (build.py --sanitize)
+        if override:
+            path = override
+        elif not os.path.exists(path) or os.environ.get("GCB200_REBUILD"):
             path = _build.build_host()
         else:
             try:
