@@ -150,3 +150,56 @@ def check(schedule, world=2, max_states=2_000_000):
 def _format(trace, last=24):
     lines = [f"  rank {r}: {kind} {name!r} -> rank {q} (epoch {e})" for (r, kind, q, name, e) in trace[-last:]]
     return "last actions of one violating interleaving:\n" + "\n".join(lines)
+
+
+def check_grid_barrier(nblocks=3, rounds=3, reset_before_release=True):
+    """All interleavings of ``nblocks`` blocks passing ``rounds`` consecutive per-rank grid barriers
+    (``gc_comm.cuh::grid_barrier``): read the generation; add one to the arrival count; the last arriver resets the
+    count and THEN bumps the generation, everybody else spins until the generation moves.  Checked: no block leaves
+    barrier k before every block has arrived at barrier k, and nobody is stuck.  ``reset_before_release=False`` swaps
+    the last arriver's two stores -- the fault the order of those stores guards against (a released block re-enters
+    and its arrival is wiped out by the late reset)."""
+    # per block: (round, pc) with pc 0 = read gen, 1 = atomic add, 2 / 3 = the last arriver's two stores, 4 = spin
+    start = (tuple((0, 0, 0, False) for _ in range(nblocks)), 0, 0, tuple(0 for _ in range(nblocks)))
+    seen, stack = {start}, [start]
+    while stack:
+        blocks, count, gen, arrived = stack.pop()
+        moved = False
+        for b, (rnd, pc, my_gen, last) in enumerate(blocks):
+            if rnd >= rounds:
+                continue
+            n_count, n_gen, n_arr = count, gen, arrived
+            if pc == 0:
+                nb = (rnd, 1, gen, False)
+            elif pc == 1:
+                n_arr = arrived[:b] + (rnd + 1,) + arrived[b + 1:]
+                n_count = count + 1
+                nb = (rnd, 2, my_gen, True) if count == nblocks - 1 else (rnd, 4, my_gen, False)
+            elif pc == 2:
+                if reset_before_release:
+                    n_count = 0
+                else:
+                    n_gen = gen + 1
+                nb = (rnd, 3, my_gen, True)
+            elif pc == 3:
+                if reset_before_release:
+                    n_gen = gen + 1
+                else:
+                    n_count = 0
+                nb = None                                     # leaves the barrier
+            else:
+                if gen == my_gen:
+                    continue                                  # still spinning
+                nb = None
+            if nb is None:
+                if any(a < rnd + 1 for a in arrived):
+                    raise ProtocolViolation(f"block {b} left barrier {rnd} before every block had arrived: {arrived}")
+                nb = (rnd + 1, 0, 0, False)
+            moved = True
+            state = (blocks[:b] + (nb,) + blocks[b + 1:], n_count, n_gen, n_arr)
+            if state not in seen:
+                seen.add(state)
+                stack.append(state)
+        if not moved and any(rnd < rounds for (rnd, _, _, _) in blocks):
+            raise ProtocolViolation(f"deadlock in the grid barrier: blocks {blocks}, count {count}, generation {gen}")
+    return len(seen)

@@ -49,3 +49,13 @@ def test_seeded_faults_are_found():
     # a wait for a signal nobody sends
     with pytest.raises(ProtocolViolation, match="deadlock"):
         check([[("wait", "READY")]], 2)
+
+
+def test_grid_barrier_generation_counting():
+    from gradient_compression_b200.parallel.protocol_model import check_grid_barrier
+
+    assert check_grid_barrier(nblocks=2, rounds=4) > 0
+    assert check_grid_barrier(nblocks=3, rounds=3) > 0
+    assert check_grid_barrier(nblocks=4, rounds=2) > 0
+    with pytest.raises(ProtocolViolation):          # generation bumped before the count is reset
+        check_grid_barrier(nblocks=3, rounds=3, reset_before_release=False)
