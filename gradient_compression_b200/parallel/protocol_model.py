@@ -1,4 +1,5 @@
-"""Host-side model checker for the flag / epoch protocol of the fused collectives (``csrc/gc_comm.cuh``).
+"""Host-side model checkers: the flag / epoch protocol of the fused collectives (``csrc/gc_comm.cuh``), the per-rank grid
+barrier, and the mbarrier pipeline of the persistent tensor-core GEMM (``csrc/gc_gemm_tc.cu``).
 
 The fused kernels synchronise ranks with monotonically increasing epochs: ``signal_all(phase, epoch)`` stores the
 epoch into ``flag[phase][me]`` of every peer, ``wait_all(phase, epoch)`` spins until every ``flag[phase][*]`` of the
@@ -202,4 +203,120 @@ def check_grid_barrier(nblocks=3, rounds=3, reset_before_release=True):
                 stack.append(state)
         if not moved and any(rnd < rounds for (rnd, _, _, _) in blocks):
             raise ProtocolViolation(f"deadlock in the grid barrier: blocks {blocks}, count {count}, generation {gen}")
+    return len(seen)
+
+
+class _MBarrier:
+    """mbarrier with an arrival count: the phase completes (its parity flips) when `count` arrivals have been seen;
+    ``passes(parity)`` is ``mbarrier.try_wait.parity``: true once the phase with that parity has completed."""
+
+    def __init__(self, count):
+        self.count, self.pending, self.phase = count, count, 0
+
+    def arrive(self):
+        self.pending -= 1
+        if self.pending == 0:
+            self.pending, self.phase = self.count, self.phase ^ 1
+
+    def passes(self, parity):
+        return self.phase != parity
+
+    def key(self):
+        return (self.pending, self.phase)
+
+
+def check_gemm_pipeline(tiles=5, kblocks=3, stages=3, epilogue_threads=2, acc_buffers=2, empty_parity_offset=1,
+                        acc_empty_count=None):
+    """All interleavings of the three roles of ``gemm_tf32_persistent_kernel`` (``csrc/gc_gemm_tc.cu``) over ``tiles``
+    output tiles of ``kblocks`` k-blocks each: the TMA producer (waits ``empty[s]`` with parity ``phase ^ 1``, fills
+    stage s, which completes ``full[s]``), the MMA issuer (waits ``acc_empty[buf]`` with parity ``aphase ^ 1``, then per
+    k-block waits ``full[s]`` with parity ``phase``, reads the stage, commits ``empty[s]``; after the last k-block
+    commits ``acc_full[buf]``) and the epilogue threads (wait ``acc_full[buf]`` with parity ``aphase``, read the
+    accumulator, arrive on ``acc_empty[buf]``), with ``phase = (it / stages) & 1`` for the running k-block counter
+    ``it`` and ``buf = tile & 1``, ``aphase = (tile >> 1) & 1``.  Checked: a stage is never refilled before it was read
+    nor read before it was filled, an accumulator is never overwritten before every epilogue thread drained it nor
+    drained before it is complete, and nobody is stuck.  Seeded faults for the tests: ``empty_parity_offset=0`` (waiting
+    for the wrong parity of a fresh ``empty`` barrier) and ``acc_empty_count`` smaller than the number of epilogue threads
+    (the accumulator is handed back while somebody still reads it)."""
+    total = tiles * kblocks
+
+    def initial():
+        return {"full": [_MBarrier(1) for _ in range(stages)], "empty": [_MBarrier(1) for _ in range(stages)],
+                "acc_full": [_MBarrier(1) for _ in range(acc_buffers)],
+                "acc_empty": [_MBarrier(acc_empty_count or epilogue_threads) for _ in range(acc_buffers)]}
+
+    # state: producer it, mma (tile, k, waited_acc), epilogue tiles (per thread), stage contents, accumulator contents, barriers
+    def freeze(st):
+        return (st["p"], st["m"], tuple(st["e"]), tuple(st["stage"]), tuple(st["acc"]), tuple(st["drained"]),
+                tuple(tuple(b.key() for b in st["bars"][k]) for k in ("full", "empty", "acc_full", "acc_empty")))
+
+    import copy
+
+    st0 = {"p": 0, "m": (0, 0, False), "e": [0] * epilogue_threads, "stage": [-1] * stages, "acc": [-1] * acc_buffers,
+           "drained": [0] * acc_buffers, "bars": initial()}
+    seen, stack = {freeze(st0)}, [st0]
+    while stack:
+        st = stack.pop()
+        succ = []
+        # producer: k-block `it` goes into stage it % stages
+        it = st["p"]
+        if it < total:
+            s, phase = it % stages, (it // stages) & 1
+            if st["bars"]["empty"][s].passes(phase ^ empty_parity_offset):
+                n = copy.deepcopy(st)
+                if n["stage"][s] != -1:
+                    raise ProtocolViolation(f"producer refills stage {s} (k-block {it}) before k-block {n['stage'][s]} was read")
+                n["stage"][s] = it
+                n["bars"]["full"][s].arrive()
+                n["p"] = it + 1
+                succ.append(n)
+        # MMA issuer
+        tile, k, waited = st["m"]
+        if tile < tiles:
+            buf, aphase = tile % acc_buffers, (tile // acc_buffers) & 1
+            if not waited:
+                if st["bars"]["acc_empty"][buf].passes(aphase ^ 1):
+                    n = copy.deepcopy(st)
+                    if n["acc"][buf] != -1 and n["drained"][buf] < epilogue_threads:
+                        raise ProtocolViolation(f"MMA starts tile {tile} in accumulator {buf} before tile {n['acc'][buf]} was drained")
+                    n["acc"][buf], n["drained"][buf] = -1, 0
+                    n["m"] = (tile, 0, True)
+                    succ.append(n)
+            else:
+                mit = tile * kblocks + k
+                s, phase = mit % stages, (mit // stages) & 1
+                if st["bars"]["full"][s].passes(phase):
+                    n = copy.deepcopy(st)
+                    if n["stage"][s] != mit:
+                        raise ProtocolViolation(f"MMA reads stage {s} expecting k-block {mit}, found {n['stage'][s]}")
+                    n["stage"][s] = -1
+                    n["bars"]["empty"][s].arrive()
+                    if k + 1 == kblocks:
+                        n["acc"][buf] = tile
+                        n["bars"]["acc_full"][buf].arrive()
+                        n["m"] = (tile + 1, 0, False)
+                    else:
+                        n["m"] = (tile, k + 1, True)
+                    succ.append(n)
+        # epilogue threads
+        for t in range(epilogue_threads):
+            et = st["e"][t]
+            if et < tiles:
+                buf, aphase = et % acc_buffers, (et // acc_buffers) & 1
+                if st["bars"]["acc_full"][buf].passes(aphase):
+                    n = copy.deepcopy(st)
+                    if n["acc"][buf] != et:
+                        raise ProtocolViolation(f"epilogue thread {t} drains accumulator {buf} expecting tile {et}, found {n['acc'][buf]}")
+                    n["drained"][buf] += 1
+                    n["bars"]["acc_empty"][buf].arrive()
+                    n["e"][t] = et + 1
+                    succ.append(n)
+        done = st["p"] >= total and st["m"][0] >= tiles and all(e >= tiles for e in st["e"])
+        if not succ and not done:
+            raise ProtocolViolation(f"pipeline deadlock: producer at {st['p']}, MMA at {st['m']}, epilogue at {st['e']}")
+        for n in succ:
+            key = freeze(n)
+            if key not in seen:
+                seen.add(key)
+                stack.append(n)
     return len(seen)

@@ -59,3 +59,22 @@ def test_grid_barrier_generation_counting():
     assert check_grid_barrier(nblocks=4, rounds=2) > 0
     with pytest.raises(ProtocolViolation):          # generation bumped before the count is reset
         check_grid_barrier(nblocks=3, rounds=3, reset_before_release=False)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(tiles=4, kblocks=1, stages=3), dict(tiles=3, kblocks=7, stages=2),
+                                dict(tiles=6, kblocks=2, stages=5, epilogue_threads=3), dict(tiles=7, kblocks=4, stages=4)])
+def test_gemm_pipeline_parities(kw):
+    """Stage ring, double-buffered accumulator and their mbarrier parities of the persistent tensor-core GEMM."""
+    from gradient_compression_b200.parallel.protocol_model import check_gemm_pipeline
+
+    assert check_gemm_pipeline(**kw) > 0
+
+
+def test_gemm_pipeline_seeded_faults():
+    from gradient_compression_b200.parallel.protocol_model import check_gemm_pipeline
+
+    with pytest.raises(ProtocolViolation):          # producer waits for the wrong parity of a fresh barrier
+        check_gemm_pipeline(empty_parity_offset=0)
+    with pytest.raises(ProtocolViolation):          # accumulator released after one of two epilogue threads arrived
+        check_gemm_pipeline(acc_empty_count=1)
+    assert check_gemm_pipeline(acc_buffers=1, tiles=3) > 0      # the arithmetic also holds for a single accumulator
