@@ -109,7 +109,8 @@ class DevicePrefetcher:
     """Iterates over (images, labels) host batches and yields device batches, with the host-to-device copy of the next
     ``depth`` batches already in flight on a side stream while the caller computes on the current one (pinned host
     memory makes the copies asynchronous).  ``convert`` maps the copied pair to what the model wants (for example
-    channels-last images); it runs on the side stream too."""
+    channels-last images); it runs on the side stream too.  The reference copies every batch in line with
+    ``.to(device)`` inside its loader generator (model_dispatcher.py:80-84)."""
 
     def __init__(self, batches, device, convert=None, depth=2):
         self._it = iter(batches)
@@ -153,7 +154,8 @@ class DevicePrefetcher:
 class LaggedReadback:
     """Device scalars read on the host one step late: ``push(t)`` starts an asynchronous copy of ``t`` into pinned host
     memory and returns the value pushed ``lag`` calls earlier (``None`` until there is one), so that reading the loss
-    of every step never stalls the stream that is computing the next one.  ``drain()`` returns what is still pending."""
+    of every step never stalls the stream that is computing the next one.  ``drain()`` returns what is still pending.
+    (The reference reads metrics with ``.item()`` inside the step: model_dispatcher.py:140-164.)"""
 
     def __init__(self, device, lag=1):
         self._device = torch.device(device)
