@@ -3,7 +3,6 @@ convolution, shortcuts are a bare 1x1 convolution taken from the activated input
 from __future__ import annotations
 
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
 from .layers import bn, conv, head_pool, linear

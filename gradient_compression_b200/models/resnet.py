@@ -4,7 +4,6 @@ Attribute names match the reference so ``state_dict`` keys are interchangeable."
 from __future__ import annotations
 
 import torch.nn as nn
-import torch.nn.functional as F
 
 from ..ops.bn import bn_act, defer_batch_counters
 from ..ops.conv import GradLink, conv_bn_act

@@ -23,7 +23,7 @@ import torch
 
 from . import _native as nat
 from . import gemm
-from .bn import _cl, _scratch_for, bn_act, count_batch, kernel_path_ok, own_grad, take_owned_grad
+from .bn import _cl, _scratch_for, bn_act, count_batch, own_grad, take_owned_grad
 
 # On by default.  Measured on the CIFAR ResNet-50 step (batch 128, one B200, three back-to-back pairs of runs): 8.04 /
 # 8.28 / 8.26 ms with this path against 8.34 / 8.37 / 8.40 ms with cuDNN convolutions everywhere.  GCB200_TC_CONV=0 (or

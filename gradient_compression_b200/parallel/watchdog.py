@@ -8,7 +8,6 @@ left waiting on a rank that is gone.  Device-side waits are bounded separately (
 """
 from __future__ import annotations
 
-import os
 import threading
 import time
 

@@ -10,13 +10,10 @@ own gradient / W (what the reference does, reducer.py:754-761), ``"zero"`` = 0.
 """
 from __future__ import annotations
 
-import torch
-
 from .. import compressors as C
 from .. import ops
 from .base import Reducer, TensorBuffer, n_bits
 from .multiscale import QSGDMaxNormTwoScaleReducer
-from .qsgd import _write_flat
 
 
 class _IndexQueue:
