@@ -164,7 +164,34 @@ def case_gemm_deep(n):
         f"gemm_tf32_kernel: {2 * m * nn * k / 1e9:.0f} GFLOP"
 
 
-CASES = {"qsgd": case_qsgd, "absmax": case_absmax, "sgd": case_sgd, "pack": case_pack, "bn_fwd": case_bn_fwd,
+def _conv_tensors(hw=16, c=128, batch=128):
+    cl = torch.channels_last
+    x = torch.randn(batch, c, hw, hw, device="cuda").contiguous(memory_format=cl)
+    w = torch.randn(c, c, 3, 3, device="cuda").contiguous(memory_format=cl)
+    return x, w
+
+
+def case_conv3x3(n):
+    """3x3 convolution of ResNet-50's second stage, forward with BN statistics: 128 x 16 x 16 x 128 -> 128 channels."""
+    from ..ops import conv, gemm
+    x, w = _conv_tensors()
+    out = torch.empty_like(x)
+    m = x.shape[0] * 256
+    part = torch.empty(gemm.m_tiles(m), 2, 128, device="cuda")
+    return (lambda: conv.conv_forward(x, w, None, 1, 1, col_partials=part, out=out)), 4 * (2 * x.numel() + w.numel()), \
+        f"gemm_tf32_persistent_kernel, A from shifted 4-D TMA boxes: {2 * m * 128 * 1152 / 1e9:.2f} GFLOP"
+
+
+def case_conv3x3_wgrad(n):
+    """Weight gradient of the same layer: dW[128, 9 * 128] from dY and shifted boxes of X."""
+    from ..ops import conv
+    x, w = _conv_tensors()
+    dy = torch.randn_like(x)
+    return (lambda: conv.conv_wgrad(dy, x, 3, 1, 1)), 4 * (2 * x.numel() + w.numel()), \
+        f"gemm_tn_tf32_kernel, B from shifted 4-D TMA boxes: {2 * x.shape[0] * 256 * 128 * 1152 / 1e9:.2f} GFLOP"
+
+
+CASES = {"conv3x3": case_conv3x3, "conv3x3_wgrad": case_conv3x3_wgrad, "qsgd": case_qsgd, "absmax": case_absmax, "sgd": case_sgd, "pack": case_pack, "bn_fwd": case_bn_fwd,
          "bn_bwd": case_bn_bwd, "topk": case_topk, "psgd": case_psgd, "gemm": case_gemm, "gemm_narrow": case_gemm_narrow, "gemm_tn": case_gemm_tn,
          "gemm_deep": case_gemm_deep}
 

@@ -1,0 +1,202 @@
+// Convolutions of NHWC fp32 activations as implicit GEMMs on the 5th-generation tensor cores (tcgen05, kind::tf32,
+// accumulator in TMEM), the layers the reference builds with nn.Conv2d (models/resnet.py:52,84 and models/vgg.py:104
+// of the reference: 3x3 with padding 1 at stride 1 or 2, 1x1 at stride 2 in projection shortcuts).
+//
+//   forward / input gradient   Y[N*Ho*Wo, Cout] (=, +=) sum over taps (r, s), channels c of
+//                              X[n, ho*stride + r - pad, wo*stride + s - pad, c] * Wt[Cout][r][s][c]  (+ bias)
+//                              = gemm_tf32_persistent_kernel whose A operand is one shifted 4-D TMA box per filter tap
+//                              and 32-channel block (k-block = tap * Cin/32 + channel block); pixels outside the image
+//                              are the box's out-of-range part, which TMA fills with zeros: that is the padding.  The
+//                              convolution stride is the map's element stride.  The weight matrix is the channels-last
+//                              filter read as [Cout, R*S*Cin].  The input gradient of a stride-1 convolution is the same
+//                              kernel on dY with the filter rotated by 180 degrees and its channel axes swapped.
+//                              Batch-norm statistics and bias come from the GEMM epilogue as for the 1x1 case.
+//   weight gradient            dW[Cout, R*S*Cin] += dY[P, Cout]^T * X_shifted[P, Cin] per tap = gemm_tn_tf32_kernel
+//                              whose B operand is a shifted 4-D box of 32 output positions x 32 channels.
+//   im2col_small_kernel        the 3-channel stem: its rows are 12 bytes apart, which no tensor map can describe,
+//                              so the 27 taps of every position are gathered into rows of 32 floats once and the
+//                              convolution becomes a plain GEMM with K = 32.
+#include "gc_tc.cuh"
+
+namespace {
+
+struct Shape {
+  int N, H, W, Cin, Cout, R, stride, pad, Ho, Wo;
+};
+
+bool make_shape(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad, Shape* s) {
+  if (N < 1 || H < 1 || W < 1 || Cin < 1 || Cout < 1 || R < 1 || R > 7 || stride < 1 || stride > 2 || pad < 0 || pad >= R) return false;
+  if (H + 2 * pad < R || W + 2 * pad < R) return false;
+  *s = Shape{N, H, W, Cin, Cout, R, stride, pad, (H + 2 * pad - R) / stride + 1, (W + 2 * pad - R) / stride + 1};
+  return true;
+}
+
+// `rows` consecutive output positions in (n, ho, wo) order as one box of bw x bh x bn positions: part of an output
+// row, whole output rows of one image, or whole images.
+bool box_for(int rows, int Ho, int Wo, int* bw, int* bh, int* bn) {
+  if (Wo >= rows) {
+    if (Wo % rows) return false;
+    *bw = rows; *bh = 1; *bn = 1;
+    return true;
+  }
+  if (rows % Wo) return false;
+  const int r = rows / Wo;
+  if (Ho >= r) {
+    if (Ho % r) return false;
+    *bw = Wo; *bh = r; *bn = 1;
+    return true;
+  }
+  if (r % Ho) return false;
+  *bw = Wo; *bh = Ho; *bn = r / Ho;
+  return true;
+}
+
+// 4-D map {C, W, H, N} of an NHWC activation; one box = 32 channels of bw x bh x bn output positions, read at the
+// convolution's stride.  128-byte rows in shared memory, swizzled as the operand kind needs.
+int make_map_nhwc(CUtensorMap* map, const float* base, const Shape& s, int bw, int bh, int bn, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)s.Cin, (cuuint64_t)s.W, (cuuint64_t)s.H, (cuuint64_t)s.N};
+  cuuint64_t strides[3] = {(cuuint64_t)s.Cin * 4, (cuuint64_t)s.W * s.Cin * 4, (cuuint64_t)s.H * s.W * s.Cin * 4};
+  cuuint32_t box[4] = {32, (cuuint32_t)(bw * s.stride), (cuuint32_t)(bh * s.stride), (cuuint32_t)bn};
+  cuuint32_t estr[4] = {1, (cuuint32_t)s.stride, (cuuint32_t)s.stride, 1};
+  if (box[1] > 256 || box[2] > 256 || box[3] > 256) return -3;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+ConvA conv_a(const Shape& s) { return ConvA{s.R * s.R, s.R, s.Cin / 32, s.Ho * s.Wo, s.Wo, s.stride, s.pad}; }
+
+bool fwd_ok(const Shape& s) {
+  int bw, bh, bn;
+  if ((s.Cin & 31) || (s.Cout & 3) || s.Cout < 32) return false;
+  if ((int64_t)s.N * s.Ho * s.Wo > 0x7fffffff) return false;
+  return box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr;
+}
+
+bool wgrad_ok(const Shape& s) {
+  int bw, bh, bn;
+  if ((s.Cin & 63) || (s.Cout & 31)) return false;
+  return box_for(BK, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr;
+}
+
+// A[p][k] = x[n, h + r - pad, w + s - pad, c] with k = (r * R + s) * Cin + c (zero outside the image and for
+// k >= R*R*Cin), stride 1; wpad[co][k] = w[co][k] padded to Kp columns.  One thread per (position, 4 columns).
+__global__ void __launch_bounds__(256) im2col_small_kernel(const float* __restrict__ x, float* __restrict__ A, int N, int H, int W,
+                                                           int Cin, int R, int pad, int Kp, const float* __restrict__ w,
+                                                           float* __restrict__ wpad, int Cout, int64_t quads) {
+  const int K = R * R * Cin;
+  const int qpr = Kp >> 2;
+  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t p = q / qpr;
+    const int k0 = (int)(q - p * qpr) * 4;
+    const int wo = (int)(p % W), ho = (int)((p / W) % H);
+    const int64_t n = p / ((int64_t)W * H);
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + j;
+      float val = 0.f;
+      if (k < K) {
+        const int tap = k / Cin, c = k - tap * Cin;
+        const int r = tap / R, s = tap - r * R;
+        const int hi = ho + r - pad, wi = wo + s - pad;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W) val = x[((n * H + hi) * W + wi) * Cin + c];
+      }
+      v[j] = val;
+    }
+    *reinterpret_cast<float4*>(A + p * Kp + k0) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+  if (wpad != nullptr) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < Cout * Kp; i += gridDim.x * blockDim.x) {
+      const int co = i / Kp, k = i - co * Kp;
+      wpad[i] = k < K ? w[co * K + k] : 0.f;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// 1 when forward (and, on rotated weights, the input gradient) of this convolution can run on the tensor cores:
+// Cin a multiple of 32, Cout a multiple of 4 and >= 32, and 128 consecutive output positions form one box.
+int gc_cuda_conv_fwd_supported(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
+  Shape s;
+  return make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) && fwd_ok(s) ? 1 : 0;
+}
+
+// y[N*Ho*Wo, Cout] (=, += when accumulate) conv(x[N, H, W, Cin], w[Cout, R*R*Cin]) (+ bias[Cout]); x, w, y 16-byte aligned.
+// col_partials (may be NULL): [ceil(N*Ho*Wo / 128)][2][Cout] per-tile column sums and sums of squares of y.
+int gc_cuda_conv_fwd(const float* x, const float* w, float* y, const float* bias, int N, int H, int W, int Cin, int Cout, int R,
+                     int stride, int pad, int accumulate, float* col_partials, int* error_flag, void* cs) {
+  Shape s;
+  if (!make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) || !fwd_ok(s)) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(w) & 15u) || (reinterpret_cast<uintptr_t>(y) & 15u))
+    return (int)cudaErrorInvalidValue;
+  const int M = N * s.Ho * s.Wo, K = R * R * Cin;
+  int bw, bh, bn;
+  box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn);
+  const int tile = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, Cout, K);
+  CUtensorMap ma, mb, mc;
+  if (make_map_nhwc(&ma, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0 || make_map(&mb, w, Cout, K, K, tile) != 0 ||
+      make_map(&mc, y, M, Cout, Cout, BM) != 0)
+    return (int)cudaErrorInvalidValue;
+  const ConvA ca = conv_a(s);
+  cudaStream_t st = (cudaStream_t)cs;
+  switch (tile) {
+    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
+    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
+    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+// 1 when the weight gradient of this convolution can run on the tensor cores: Cin a multiple of 64, Cout of 32, and
+// 32 consecutive output positions form one box.
+int gc_cuda_conv_wgrad_supported(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
+  Shape s;
+  return make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) && wgrad_ok(s) ? 1 : 0;
+}
+
+// dw[Cout, R*R*Cin] += dy[N*Ho*Wo, Cout]^T x_shifted: zero dw first for a plain gradient (the split contraction adds its
+// partial tiles with TMA reduce stores, in no fixed order).
+int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H, int W, int Cin, int Cout, int R, int stride,
+                       int pad, int* error_flag, void* cs) {
+  Shape s;
+  if (!make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) || !wgrad_ok(s)) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(dw) & 15u))
+    return (int)cudaErrorInvalidValue;
+  const int P = N * s.Ho * s.Wo, No = R * R * Cin;
+  int bw, bh, bn;
+  box_for(BK, s.Ho, s.Wo, &bw, &bh, &bn);
+  int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : 64);      // a tile's columns stay inside one filter tap
+  if (gctc::tile_choice && Cin % gctc::tile_choice == 0) tile = gctc::tile_choice;
+  CUtensorMap ma, mb, mc;
+  if (make_map_mn(&ma, dy, P, Cout, Cout) != 0 || make_map_nhwc(&mb, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) != 0 ||
+      make_map(&mc, dw, Cout, No, No, BM) != 0)
+    return (int)cudaErrorInvalidValue;
+  const ConvA ca = conv_a(s);
+  cudaStream_t st = (cudaStream_t)cs;
+  switch (tile) {
+    case 64: return launch_tn_maps<64>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
+    case 128: return launch_tn_maps<128>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
+    case 256: return launch_tn_maps<256>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+// Rows of Kp = 32-float-padded filter taps for a stride-1 convolution with few input channels (the 3-channel stem):
+// A[N*H*W, Kp] from x[N, H, W, Cin], and (when wpad is given) the filter w[Cout, R*R*Cin] padded to wpad[Cout, Kp].
+int gc_cuda_im2col_small(const float* x, float* A, int N, int H, int W, int Cin, int R, int pad, int Kp, const float* w,
+                         float* wpad, int Cout, void* cs) {
+  if (N < 1 || H < 1 || W < 1 || Cin < 1 || R < 1 || pad < 0 || Kp < R * R * Cin || (Kp & 3) || 2 * pad != R - 1) return (int)cudaErrorInvalidValue;
+  const int64_t quads = (int64_t)N * H * W * (Kp >> 2);
+  int64_t blocks = (quads + 255) / 256;
+  if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
+  im2col_small_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)cs>>>(x, A, N, H, W, Cin, R, pad, Kp, w, wpad, Cout, quads);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

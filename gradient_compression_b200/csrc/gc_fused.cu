@@ -621,8 +621,8 @@ __global__ void __launch_bounds__(THREADS, 2) allreduce_fused_kernel(LaunchViews
 // ------------------------------------------------------------------------------------------ small one-shot fp32 sum
 struct SmallSumParams {
   Common c;
-  int64_t off_buf;   // double-buffered by epoch parity: off_buf + parity * stride_bytes
-  int64_t stride_bytes;
+  int64_t off_buf;   // double-buffered by epoch parity: off_buf + parity * half_bytes
+  int64_t half_bytes;   // distance between the two parity regions: fixed per arena, independent of the call's size
   float alpha;
 };
 
@@ -640,7 +640,7 @@ __global__ void __launch_bounds__(THREADS) small_sum_kernel(LaunchViews lv, Smal
     for (int64_t i = tid; i < n; i += stride) v.out[i] = v.in[i] * p.alpha;
     return;
   }
-  int64_t off = p.off_buf + (int64_t)(epoch & 1) * p.stride_bytes;
+  int64_t off = p.off_buf + (int64_t)(epoch & 1) * p.half_bytes;
   float* mine = reinterpret_cast<float*>(v.arena[v.rank] + off);
   for (int64_t i = tid; i < n; i += stride) mine[i] = v.in[i];
   grid_barrier(w, c.nblocks, 0x50);
@@ -663,8 +663,11 @@ struct RandkParams {
   int64_t start, k;
   int s_lo, s_hi;          // s_hi == 0: single scale
   int zero_unselected;     // 0: unselected coordinates become in / W ; 1: zero
-  int64_t off_vals, off_levels, off_mask;   // scratch regions (levels / mask double-buffered by parity)
-  int64_t stride_bytes;
+  int64_t off_vals, off_levels, off_mask;   // scratch regions inside a parity region (selected by epoch & 1)
+  int64_t half_bytes;                       // distance between the two parity regions: fixed per arena
+  int64_t* window;         // device-resident start of this step's window (may be NULL: p.start is used).  The kernel
+                           // advances it by K, wrapping at n, so a launch replayed from a CUDA graph walks the
+                           // permutation like a sequence of fresh launches does.
 };
 
 __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, RandkParams p) {
@@ -674,22 +677,24 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
   Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
   const uint32_t epoch = next_epoch(c.hdr);
   const uint32_t rng_step = p.c.step + (p.c.step_from_device ? launch_calls(c.hdr) : 0u);
-  const int64_t n = p.c.n, k = p.k;
+  const int64_t n = p.c.n;
+  const int64_t start = p.window != nullptr ? *((volatile const int64_t*)p.window) : p.start;
+  const int64_t k = p.k < n - start ? p.k : n - start;
   const int world = p.c.world;
   const bool al_in = (reinterpret_cast<uintptr_t>(v.in) & 15u) == 0;
   const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
   const int64_t stride = (int64_t)c.nblocks * THREADS;
   const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
   uint8_t* my = v.arena[v.rank];
-  float* vals = reinterpret_cast<float*>(my + p.off_vals);
-  const int par = epoch & 1;
-  int32_t* levels = reinterpret_cast<int32_t*>(my + p.off_levels + par * p.stride_bytes);
-  uint8_t* mask = my + p.off_mask + par * p.stride_bytes;
+  const int64_t par_off = (int64_t)(epoch & 1) * p.half_bytes;
+  float* vals = reinterpret_cast<float*>(my + p.off_vals + par_off);
+  int32_t* levels = reinterpret_cast<int32_t*>(my + p.off_levels + par_off);
+  uint8_t* mask = my + p.off_mask + par_off;
 
   // gather the K selected coordinates first (the dense pass below may overwrite them in place)
   float m = 0.0f;
   for (int64_t i = tid; i < k; i += stride) {
-    float x = v.in[perm_eval(p.perm, (uint64_t)(p.start + i))];
+    float x = v.in[perm_eval(p.perm, (uint64_t)(start + i))];
     vals[i] = x;
     m = fmaxf(m, abs_for_max(x));
   }
@@ -719,6 +724,9 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
     }
   }
   float norm = (world > 1) ? exchange_max(w, v, world, epoch, m, c.bid == 0, smem) : m;
+  // every block of every rank of this launch has read the window by now (own rank: the grid barrier inside rank_max;
+  // other virtual ranks of an emulated group: they published their maxima after theirs): one thread advances it
+  if (p.window != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *p.window = start + k >= n ? 0 : start + k;
   const bool two = p.s_hi > 0;
   float sc_lo = (norm > 0.0f) ? (float)p.s_lo / norm : 0.0f;
   float sc_hi = (norm > 0.0f && two) ? (float)p.s_hi / norm : 0.0f;
@@ -749,7 +757,7 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
       if (world > 1) {
 #pragma unroll
         for (int src = 0; src < MAXW; ++src)
-          if (src < world) hi = hi && (v.arena[src] + p.off_mask + par * p.stride_bytes)[i] != 0;
+          if (src < world) hi = hi && (v.arena[src] + p.off_mask + par_off)[i] != 0;
       }
       if (hi) q = qh;
     }
@@ -767,9 +775,9 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
     int acc = 0;
 #pragma unroll
     for (int src = 0; src < MAXW; ++src)
-      if (src < world) acc += reinterpret_cast<const int32_t*>(v.arena[src] + p.off_levels + par * p.stride_bytes)[i];
+      if (src < world) acc += reinterpret_cast<const int32_t*>(v.arena[src] + p.off_levels + par_off)[i];
     bool hi = two && vals[i] != 0.0f;
-    v.out[perm_eval(p.perm, (uint64_t)(p.start + i))] = mul_rn(hi ? dq_hi : dq_lo, (float)acc);
+    v.out[perm_eval(p.perm, (uint64_t)(start + i))] = mul_rn(hi ? dq_hi : dq_lo, (float)acc);
   }
 }
 
@@ -781,7 +789,7 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
 struct SparseParams {
   Common c;
   int64_t count;
-  int64_t off_idx, off_val, stride_bytes;   // list regions, double-buffered by epoch parity
+  int64_t off_idx, off_val, half_bytes;     // list regions inside a parity region; fixed distance between the two regions
   float alpha;
 };
 
@@ -795,7 +803,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_fused_kernel(LaunchViews lv
   const bool al_out = (reinterpret_cast<uintptr_t>(v.out) & 15u) == 0;
   const int64_t stride = (int64_t)c.nblocks * THREADS;
   const int64_t tid = (int64_t)c.bid * THREADS + threadIdx.x;
-  const int par = epoch & 1;
+  const int64_t par_off = (int64_t)(epoch & 1) * p.half_bytes;
   const int32_t* my_idx = reinterpret_cast<const int32_t*>(v.aux);
   {
     int64_t nq = (n + 3) / 4;
@@ -803,8 +811,8 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_fused_kernel(LaunchViews lv
     for (int64_t q = tid; q < nq; q += stride) store_quad(v.out, q * 4, n, al_out, z);
   }
   if (world > 1) {
-    int32_t* pub_idx = reinterpret_cast<int32_t*>(v.arena[v.rank] + p.off_idx + par * p.stride_bytes);
-    float* pub_val = reinterpret_cast<float*>(v.arena[v.rank] + p.off_val + par * p.stride_bytes);
+    int32_t* pub_idx = reinterpret_cast<int32_t*>(v.arena[v.rank] + p.off_idx + par_off);
+    float* pub_val = reinterpret_cast<float*>(v.arena[v.rank] + p.off_val + par_off);
     for (int64_t i = tid; i < p.count; i += stride) { pub_idx[i] = my_idx[i]; pub_val[i] = v.in[i]; }
   }
   grid_barrier(w, c.nblocks, 0x70);
@@ -814,8 +822,8 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_fused_kernel(LaunchViews lv
     wait_all(w, world, PH_AUX, epoch);
   }
   for (int src = 0; src < world; ++src) {
-    const int32_t* idx = world > 1 ? reinterpret_cast<const int32_t*>(v.arena[src] + p.off_idx + par * p.stride_bytes) : my_idx;
-    const float* val = world > 1 ? reinterpret_cast<const float*>(v.arena[src] + p.off_val + par * p.stride_bytes) : v.in;
+    const int32_t* idx = world > 1 ? reinterpret_cast<const int32_t*>(v.arena[src] + p.off_idx + par_off) : my_idx;
+    const float* val = world > 1 ? reinterpret_cast<const float*>(v.arena[src] + p.off_val + par_off) : v.in;
     for (int64_t i = tid; i < p.count; i += stride) {
       int32_t at = idx[i];
       if (at >= 0 && at < n) v.out[at] += p.alpha * val[i];
@@ -902,12 +910,22 @@ Common make_common(CommCtx** ctxs, int n_virtual, int64_t n, uint64_t seed, uint
 
 inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
+// The one-shot kernels (small sum, sparse exchange, Rand-K) have no closing round: a fast rank may start step e + 1
+// while a slower peer still reads what it published in step e.  They therefore alternate between two regions of the
+// arena by epoch parity, and the distance between the regions depends on the ARENA only -- never on the size of a
+// call -- so that launches of different sizes (buckets, different reducers on one arena) cannot make step e + 1's
+// region overlap step e's.
+inline int64_t parity_half_bytes(int64_t arena_bytes) { return (arena_bytes - ARENA_HEADER_BYTES) / 2 / 256 * 256; }
+
 }  // namespace
 
 extern "C" {
 
 int64_t gc_comm_header_bytes() { return ARENA_HEADER_BYTES; }
 int gc_comm_max_world() { return MAXW; }
+
+// Bytes of arena a one-shot kernel needs when each of its parity regions holds `region_bytes`.
+int64_t gc_comm_oneshot_bytes(int64_t region_bytes) { return ARENA_HEADER_BYTES + 2 * align_up(region_bytes, 256) + 512; }
 
 // Bytes of arena needed by the largest fused op on an n-element gradient.
 int64_t gc_comm_required_bytes(int64_t n) {
@@ -1139,8 +1157,8 @@ int gc_fused_small_sum(void** ctxs_, int n_virtual, const float* const* ins, flo
   CommCtx** ctxs = (CommCtx**)ctxs_;
   SmallSumParams p;
   p.off_buf = ARENA_HEADER_BYTES;
-  p.stride_bytes = align_up(n * 4, 256);
-  if (ctxs[0]->world > 1 && p.off_buf + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  p.half_bytes = parity_half_bytes(ctxs[0]->bytes);
+  if (ctxs[0]->world > 1 && align_up(n * 4, 256) > p.half_bytes) return (int)cudaErrorMemoryAllocation;
   p.alpha = alpha;
   const void* kern = (const void*)small_sum_kernel;
   LaunchViews lv;
@@ -1161,10 +1179,11 @@ int gc_fused_sparse(void** ctxs_, int n_virtual, const float* const* vals, float
   SparseParams p;
   p.count = count;
   p.alpha = alpha;
-  p.stride_bytes = align_up(count * 4, 256);
+  const int64_t region = align_up(count * 4, 256);
+  p.half_bytes = parity_half_bytes(ctxs[0]->bytes);
   p.off_idx = ARENA_HEADER_BYTES;
-  p.off_val = p.off_idx + 2 * p.stride_bytes;
-  if (ctxs[0]->world > 1 && p.off_val + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  p.off_val = p.off_idx + region;
+  if (ctxs[0]->world > 1 && 2 * region > p.half_bytes) return (int)cudaErrorMemoryAllocation;
   const void* kern = (const void*)sparse_fused_kernel;
   LaunchViews lv;
   if (fill_views(ctxs, n_virtual, vals, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, idxs, n) != 0)
@@ -1174,23 +1193,27 @@ int gc_fused_sparse(void** ctxs_, int n_virtual, const float* const* vals, float
 }
 
 // One Rand-K (optionally two-scale: bits_hi > 0) reduce step on the window [start, start + k) of the
-// keyed permutation of [0, n).
+// keyed permutation of [0, n).  window (device int64, may be NULL): when given, the window starts at *window instead of
+// `start`, holds min(k, n - *window) coordinates, and the kernel stores the next step's start there (0 after the last
+// window of a pass); every rank of a group must pass its own counter with the same value.
 int gc_fused_randk(void** ctxs_, int n_virtual, const float* const* ins, float* const* outs, int64_t n, uint64_t seed,
                    uint32_t npass, int64_t start, int64_t k, int bits_lo, int bits_hi, int zero_unselected,
-                   uint32_t step, int timeout_ms, int max_blocks, void* cs) {
+                   uint32_t step, int64_t* window, int timeout_ms, int max_blocks, void* cs) {
   CommCtx** ctxs = (CommCtx**)ctxs_;
   RandkParams p;
   p.perm = make_perm_key((uint64_t)n, seed, npass);
   p.start = start;
   p.k = k;
+  p.window = window;
   p.s_lo = (1 << bits_lo) - 1;
   p.s_hi = bits_hi > 0 ? (1 << bits_hi) - 1 : 0;
   p.zero_unselected = zero_unselected;
-  p.stride_bytes = align_up(k * 4, 256);
+  const int64_t region = align_up(k * 4, 256);
+  p.half_bytes = parity_half_bytes(ctxs[0]->bytes);
   p.off_vals = ARENA_HEADER_BYTES;
-  p.off_levels = p.off_vals + p.stride_bytes;
-  p.off_mask = p.off_levels + 2 * p.stride_bytes;
-  if (p.off_mask + 2 * p.stride_bytes > ctxs[0]->bytes) return (int)cudaErrorMemoryAllocation;
+  p.off_levels = p.off_vals + region;
+  p.off_mask = p.off_levels + region;
+  if (3 * region > p.half_bytes) return (int)cudaErrorMemoryAllocation;
   const void* kern = (const void*)randk_fused_kernel;
   LaunchViews lv;
   if (fill_views(ctxs, n_virtual, ins, outs, max_coresident(kern, ctxs[0]->sm_count), max_blocks, &lv, nullptr, n) != 0)

@@ -44,7 +44,8 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // --------------------------------------------------------------------------- Philox fills
 template <int KIND>  // 0 uniform float, 1 normal float, 2 raw u32
-__global__ void philox_fill_kernel(RngKey key, int64_t n, void* __restrict__ out_) {
+__global__ void philox_fill_kernel(RngKey key, const uint32_t* __restrict__ step_offset, int64_t n, void* __restrict__ out_) {
+  if (step_offset != nullptr) key.step += *step_offset;      // a device-resident step counter: advances under graph replay
   int64_t nblk = (n + 3) / 4;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblk; b += stride) {
@@ -326,9 +327,12 @@ __global__ void __launch_bounds__(512) sgd_kernel(float* __restrict__ p, const f
 
 // Transposes of many small row-major matrices in one launch (the [Cout, Cin] weights of 1x1 convolutions
 // -> [Cin, Cout], the K-major operand of the input-gradient GEMM).  Table rows: {src pointer, dst pointer,
-// rows, cols, first tile}; a block moves one 32 x 32 tile through shared memory.
+// rows, cols, first tile, source row pitch, destination row pitch} (pitches in floats); a block moves one 32 x 32
+// tile through shared memory.  With pitches larger than the matrix, one filter tap of a channels-last R x S filter
+// [Cout][tap][Cin] is transposed into tap (R*S - 1 - tap) of [Cin][tap][Cout]: the rotated, channel-swapped filter that
+// turns the input gradient of a stride-1 convolution into a forward convolution of the output gradient.
 namespace {
-constexpr int TR_FIELDS = 5;
+constexpr int TR_FIELDS = 7;
 __global__ void __launch_bounds__(256) batched_transpose_kernel(const int64_t* __restrict__ tab, int n_seg) {
   __shared__ float tile[32][33];
   int lo = 0, hi = n_seg - 1;
@@ -340,17 +344,18 @@ __global__ void __launch_bounds__(256) batched_transpose_kernel(const int64_t* _
   const float* __restrict__ src = reinterpret_cast<const float*>(t[0]);
   float* __restrict__ dst = reinterpret_cast<float*>(t[1]);
   const int rows = (int)t[2], cols = (int)t[3];
+  const int64_t src_ld = t[5], dst_ld = t[6];
   const int tiles_c = (cols + 31) / 32;
   const int local = (int)((int64_t)blockIdx.x - t[4]);
   const int r0 = (local / tiles_c) * 32, c0 = (local % tiles_c) * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
   for (int j = ty; j < 32; j += 8)
-    if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(int64_t)(r0 + j) * cols + c0 + tx];
+    if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(int64_t)(r0 + j) * src_ld + c0 + tx];
   __syncthreads();
 #pragma unroll
   for (int j = ty; j < 32; j += 8)
-    if (c0 + j < cols && r0 + tx < rows) dst[(int64_t)(c0 + j) * rows + r0 + tx] = tile[tx][j];
+    if (c0 + j < cols && r0 + tx < rows) dst[(int64_t)(c0 + j) * dst_ld + r0 + tx] = tile[tx][j];
 }
 }  // namespace
 
@@ -360,14 +365,17 @@ int gc_cuda_abi_version() { return 3; }
 
 int gc_cuda_sm_count() { return sm_count(); }
 
-int gc_cuda_philox_fill(int kind, uint64_t seed, uint32_t stream_id, uint32_t step, int64_t n, void* out, void* cs) {
+// step_offset (device uint32, may be NULL) is added to `step` by the kernel: callers that replay the launch from a CUDA
+// graph keep their step counter in device memory.
+int gc_cuda_philox_fill(int kind, uint64_t seed, uint32_t stream_id, uint32_t step, const uint32_t* step_offset, int64_t n,
+                        void* out, void* cs) {
   if (n <= 0) return 0;
   RngKey key = make_key(seed, stream_id, step);
   int threads = 256, grid = grid_for((n + 3) / 4, threads, 8);
   cudaStream_t st = (cudaStream_t)cs;
-  if (kind == 0) philox_fill_kernel<0><<<grid, threads, 0, st>>>(key, n, out);
-  else if (kind == 1) philox_fill_kernel<1><<<grid, threads, 0, st>>>(key, n, out);
-  else philox_fill_kernel<2><<<grid, threads, 0, st>>>(key, n, out);
+  if (kind == 0) philox_fill_kernel<0><<<grid, threads, 0, st>>>(key, step_offset, n, out);
+  else if (kind == 1) philox_fill_kernel<1><<<grid, threads, 0, st>>>(key, step_offset, n, out);
+  else philox_fill_kernel<2><<<grid, threads, 0, st>>>(key, step_offset, n, out);
   return GC_LAUNCH_CHECK();
 }
 

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from ..ops.bn import bn_act, defer_batch_counters
+from ..ops.bn import defer_batch_counters
 from ..ops.conv import GradLink, conv_bn_act
 from .layers import bn, conv, head_pool, linear
 
@@ -33,8 +33,10 @@ class BasicBlock(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        y = bn_act(self.bn1, self.conv1(x))
-        return bn_act(self.bn2, self.conv2(y), residual=self.shortcut(x))
+        identity = len(self.shortcut) == 0
+        link = GradLink() if identity else None
+        y = conv_bn_act(self.conv1, self.bn1, x, link=link)
+        return conv_bn_act(self.conv2, self.bn2, y, residual=link.residual(x) if identity else self.shortcut(x))
 
 
 class Bottleneck(nn.Module):
@@ -48,12 +50,12 @@ class Bottleneck(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        # 1x1 convolutions: tensor-core GEMM with BN statistics in its epilogue.  In an identity block the gradient of
+        # every convolution: tensor-core kernel with BN statistics in its epilogue.  In an identity block the gradient of
         # the skip connection and conv1's input gradient meet at x: the link lets conv1's GEMM add onto the former.
         identity = len(self.shortcut) == 0
         link = GradLink() if identity else None
         y = conv_bn_act(self.conv1, self.bn1, x, link=link)
-        y = bn_act(self.bn2, self.conv2(y))
+        y = conv_bn_act(self.conv2, self.bn2, y)
         return conv_bn_act(self.conv3, self.bn3, y, residual=link.residual(x) if identity else self.shortcut(x))
 
 
@@ -75,7 +77,7 @@ class ResNet(nn.Module):
         return nn.Sequential(*blocks)
 
     def forward(self, x):
-        x = bn_act(self.bn1, self.conv1(x))
+        x = conv_bn_act(self.conv1, self.bn1, x)
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.linear(head_pool(x, 4))
 

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from ..ops.bn import bn_act
+from ..ops.conv import conv_bn_act
 from .layers import bn, conv, linear
 
 CFG = {
@@ -35,9 +35,10 @@ class VGG(nn.Module):
         i = 0
         while i < len(mods):
             m = mods[i]
-            if isinstance(m, nn.BatchNorm2d) and i + 1 < len(mods) and isinstance(mods[i + 1], nn.ReLU):
-                x = bn_act(m, x)            # BN + ReLU in one pass
-                i += 2
+            if (isinstance(m, nn.Conv2d) and i + 2 < len(mods) and isinstance(mods[i + 1], nn.BatchNorm2d)
+                    and isinstance(mods[i + 2], nn.ReLU)):
+                x = conv_bn_act(m, mods[i + 1], x)      # convolution with BN statistics in its epilogue, BN + ReLU in one pass
+                i += 3
             else:
                 x = m(x)
                 i += 1

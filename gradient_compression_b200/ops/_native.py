@@ -95,7 +95,7 @@ def cuda():
         P = c_void_p
         _declare(lib, "gc_cuda_abi_version", c_int, [])
         _declare(lib, "gc_cuda_sm_count", c_int, [])
-        _declare(lib, "gc_cuda_philox_fill", c_int, [c_int, c_u64, c_u32, c_u32, c_i64, P, P])
+        _declare(lib, "gc_cuda_philox_fill", c_int, [c_int, c_u64, c_u32, c_u32, P, c_i64, P, P])
         _declare(lib, "gc_cuda_absmax_scratch_bytes", c_i64, [])
         _declare(lib, "gc_cuda_absmax", c_int, [P, c_i64, P, P, P])
         _declare(lib, "gc_cuda_quantize_levels", c_int, [P, c_i64, P, c_int, c_int, c_u64, c_u32, c_u32, P, c_int, P])
@@ -131,6 +131,11 @@ def cuda():
         _declare(lib, "gc_cuda_gemm_tn_tf32_supported", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64])
         _declare(lib, "gc_cuda_gemm_tn_tf32", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_config", None, [c_int, c_int])
+        _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P])
+        _declare(lib, "gc_cuda_conv_wgrad_supported", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_conv_wgrad", c_int, [P, P, P] + [c_int] * 8 + [P, P])
+        _declare(lib, "gc_cuda_im2col_small", c_int, [P, P] + [c_int] * 7 + [P, P, c_int, P])
         _declare(lib, "gc_cuda_bn_finalize_partials", c_int, [P, c_int, c_i64, c_int, P, P, P, c_float, c_float, P])
         _declare(lib, "gc_cuda_varpack_workspace_bytes", c_i64, [c_i64])
         _declare(lib, "gc_cuda_varpack_plan", c_int, [P, c_i64, P, P, P, P])
@@ -144,6 +149,7 @@ def cuda():
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
         _declare(lib, "gc_comm_max_world", c_int, [])
         _declare(lib, "gc_comm_required_bytes", c_i64, [c_i64])
+        _declare(lib, "gc_comm_oneshot_bytes", c_i64, [c_i64])
         _declare(lib, "gc_comm_create", c_int, [c_int, c_int, c_i64, PP])
         _declare(lib, "gc_comm_ipc_handle", c_int, [P, P])
         _declare(lib, "gc_comm_open_peers", c_int, [P, P])
@@ -161,7 +167,7 @@ def cuda():
         _declare(lib, "gc_fused_allreduce", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, P])
         _declare(lib, "gc_fused_small_sum", c_int, [PP, c_int, PP, PP, c_i64, c_float, c_int, c_int, P])
         _declare(lib, "gc_fused_randk", c_int, [PP, c_int, PP, PP, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int,
-                                                c_int, c_u32, c_int, c_int, P])
+                                                c_int, c_u32, P, c_int, c_int, P])
         _declare(lib, "gc_fused_sparse", c_int, [PP, c_int, PP, PP, PP, c_i64, c_i64, c_float, c_int, c_int, P])
         _cuda = lib
     return _cuda

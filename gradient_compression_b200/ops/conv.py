@@ -1,18 +1,25 @@
-"""1x1 convolution + batch norm (+ residual) (+ ReLU) with the convolution on the tcgen05 GEMMs.
+"""Convolution + batch norm (+ residual) (+ ReLU) with the convolution on the tcgen05 kernels.
 
-``conv_bn_act(conv, bn, x, residual=None, relu=True)`` is ``relu(bn(conv(x)) + residual)``.  For a 1x1,
-stride-1, ungrouped convolution on channels-last fp32 CUDA tensors the convolution is the GEMM
-``[N*H*W, Cin] x [Cout, Cin]^T`` (``ops.gemm_tf32``: TMA + tcgen05.mma kind::tf32 + TMEM), whose epilogue also
-emits the per-channel sums the batch norm needs -- the normalisation statistics are fused into the producing
-kernel, so the activation is written once and read once (by the apply pass) instead of written, read for the
-statistics and read again.  Backward: fused BN backward kernels; input gradient ``dY x W`` on the same GEMM
-(reading transposed weights that one batched kernel refreshes after every optimiser step, and, in identity
-blocks, adding its result onto the skip connection's gradient: ``GradLink``); weight gradient ``dY^T X`` on the
-split-K GEMM with MN-major operands (``ops.gemm_tn_tf32``).  Every other convolution (3x3, strided, grouped,
-fewer than ``MIN_ROWS`` positions) falls back to ``bn_act(bn, conv(x))`` with cuDNN's convolution.
+``conv_bn_act(conv, bn, x, residual=None, relu=True)`` is ``relu(bn(conv(x)) + residual)`` for an ungrouped
+``nn.Conv2d`` on channels-last fp32 CUDA tensors.  Three forward paths, all TMA + tcgen05.mma kind::tf32 + TMEM:
+
+* ``gemm``  1x1, stride 1: the GEMM ``[N*H*W, Cin] x [Cout, Cin]^T`` (``ops.gemm_tf32``);
+* ``conv``  R x R at stride 1 or 2 with Cin a multiple of 32 (3x3 layers, strided projection shortcuts): implicit GEMM,
+  one shifted 4-D TMA box of the activation per filter tap and 32-channel block, zero fill as padding
+  (``csrc/gc_conv_tc.cu``);
+* ``stem``  few input channels (the 3-channel first layer): a gather kernel writes rows of 32 floats (27 taps + padding),
+  then the GEMM with K = 32.
+
+The epilogue of each emits the per-channel sums the batch norm needs, so the activation is written once and read once
+(by the apply pass).  Backward: fused BN backward kernels; input gradient on the same kernels with the filter rotated
+by 180 degrees and its channel axes swapped (one batched kernel refreshes those copies after every optimiser step;
+in identity blocks the product is added straight onto the skip connection's gradient: ``GradLink``); weight gradient
+``dY^T X`` on the split-K kernel with MN-major operands, per filter tap from shifted boxes.  Input gradients of
+strided convolutions, grouped convolutions and shapes the tilings exclude use cuDNN through ``bn_act(bn, conv(x))``
+or ``aten.convolution_backward``.
 
 The reference builds the same layers from ``nn.Conv2d`` + ``nn.BatchNorm2d`` + ``F.relu`` module calls
-(models/resnet.py:45-76 of the reference).
+(models/resnet.py:45-76, models/vgg.py:96-110 of the reference).
 """
 from __future__ import annotations
 
@@ -25,43 +32,51 @@ from . import _native as nat
 from . import gemm
 from .bn import _cl, _scratch_for, bn_act, count_batch, own_grad, take_owned_grad
 
-# On by default.  Measured on the CIFAR ResNet-50 step (batch 128, one B200, three back-to-back pairs of runs): 8.04 /
-# 8.28 / 8.26 ms with this path against 8.34 / 8.37 / 8.40 ms with cuDNN convolutions everywhere.  GCB200_TC_CONV=0 (or
-# ``ENABLED = False``) keeps every convolution on cuDNN.
+# GCB200_TC_CONV=0 (or ``ENABLED = False``) keeps every convolution on cuDNN.
 ENABLED = os.environ.get("GCB200_TC_CONV", "1") == "1"
 
-
-# GradLink (accumulating input-gradient GEMMs of identity blocks) on / off, for measurements.
+# GradLink (accumulating input-gradient kernels of identity blocks) on / off, for measurements.
 LINK_ENABLED = os.environ.get("GCB200_GRAD_LINK", "1") == "1"
 
-# Weight gradients of these convolutions on the split-K tcgen05 GEMM (off: cuDNN).
+# Weight gradients of these convolutions on the split-K tcgen05 kernel (off: cuDNN).
 WGRAD_ENABLED = os.environ.get("GCB200_TC_WGRAD", "1") == "1"
 
-# Below this many output positions (N*H*W) cuDNN's kernels win by more than the fused statistics return.
-MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "4096"))
+# Convolutions with fewer output positions (N*Ho*Wo) than this stay on cuDNN.
+MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "0"))
+
+# Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem".
+PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem").split(","))
 
 
-class _TransposedWeights:
-    """[Cin, Cout] copies of the 1x1 convolution weights: the K-major operand of the input-gradient GEMM.
+def _taps(w):
+    return w.shape[2] * w.shape[3]
+
+
+class _DgradWeights:
+    """The filter as the input-gradient kernel reads it: ``[Cin, taps * Cout]`` with tap ``t`` holding the transpose of
+    the forward filter's tap ``taps - 1 - t`` (rotation by 180 degrees, channel axes swapped).  For a 1x1 filter that
+    is the plain transpose ``[Cin, Cout]``.
 
     A copy is valid while the weight's version counter and storage are the ones it was made from; the backward of
     a layer redoes a stale copy on the spot.  Kernels that write parameters through raw pointers do not move
     version counters, so ``ops.sgd_step`` marks every copy stale, and ``FlatArena.sgd_step`` -- which knows the
-    parameter list -- then re-transposes all of its registered weights in ONE launch (``refresh``), which is also
+    parameter list -- then redoes all of its registered weights in ONE launch (``refresh``), which is also
     what a captured step graph replays."""
 
     def __init__(self):
-        self.entries = {}          # id(weight) -> [weakref, wt, version, data_ptr]
+        self.entries = {}          # id(weight) -> [weakref, wd, version, data_ptr]
 
     def get(self, w):
         e = self.entries.get(id(w))
         if e is None or e[0]() is not w or e[3] != w.data_ptr() or e[1].device != w.device:
-            e = [weakref.ref(w), torch.empty(w.shape[1], w.shape[0], dtype=torch.float32, device=w.device), -1, w.data_ptr()]
+            e = [weakref.ref(w), torch.empty(w.shape[1], _taps(w) * w.shape[0], dtype=torch.float32, device=w.device), -1,
+                 w.data_ptr()]
             self.entries[id(w)] = e
             if len(self.entries) % 64 == 0:
                 self.entries = {k: v for k, v in self.entries.items() if v[0]() is not None}
         if e[2] != w._version:
-            e[1].copy_(w.detach().reshape(w.shape[0], w.shape[1]).t())
+            cout, cin, r, s = w.shape
+            e[1].view(cin, r, s, cout).copy_(w.detach().flip(2, 3).permute(1, 2, 3, 0))
             e[2] = w._version
         return e[1]
 
@@ -76,18 +91,22 @@ class _TransposedWeights:
         if not mine:
             return
         key = tuple((e[0]().data_ptr(), e[1].data_ptr()) for e in mine)
-        state = getattr(owner, "_transposed_weight_table", None)
+        state = getattr(owner, "_dgrad_weight_table", None)
         if state is None or state[0] != key:
             if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("the table of transposed 1x1 weights changed inside a CUDA graph capture: run one "
+                raise RuntimeError("the table of input-gradient filters changed inside a CUDA graph capture: run one "
                                    "eager step (forward, backward, optimiser) before capturing")
             rows, tiles = [], 0
             for e in mine:
                 w = e[0]()
-                rows.append([w.data_ptr(), e[1].data_ptr(), w.shape[0], w.shape[1], tiles])
-                tiles += ((w.shape[0] + 31) // 32) * ((w.shape[1] + 31) // 32)
+                cout, cin, taps = w.shape[0], w.shape[1], _taps(w)
+                per = ((cout + 31) // 32) * ((cin + 31) // 32)
+                for t in range(taps):       # tap t of [Cout][taps][Cin] -> tap (taps - 1 - t) of [Cin][taps][Cout]
+                    rows.append([w.data_ptr() + 4 * t * cin, e[1].data_ptr() + 4 * (taps - 1 - t) * cout, cout, cin, tiles,
+                                 taps * cin, taps * cout])
+                    tiles += per
             state = (key, torch.tensor(rows, dtype=torch.int64).to(mine[0][1].device), tiles, [e[1] for e in mine])
-            owner._transposed_weight_table = state
+            owner._dgrad_weight_table = state
         _, table, tiles, _ = state
         with torch.cuda.device(table.device):
             nat.check(nat.cuda().gc_cuda_batched_transpose(table.data_ptr(), table.shape[0], tiles, nat.stream_ptr()),
@@ -96,17 +115,18 @@ class _TransposedWeights:
             e[2] = e[0]()._version
 
 
-_transposed = _TransposedWeights()
+_dgrad_weights = _DgradWeights()
 
 
 def weights_written_raw():
     """Called by kernels that rewrite parameters through raw pointers (version counters do not move)."""
-    _transposed.invalidate()
+    _dgrad_weights.invalidate()
 
 
 def refresh_transposed(owner, params):
-    """Called by the owner of a parameter list after it rewrote them: one batched re-transpose."""
-    _transposed.refresh(owner, params)
+    """Called by the owner of a parameter list after it rewrote them: one batched kernel redoes every registered
+    input-gradient filter."""
+    _dgrad_weights.refresh(owner, params)
 
 
 def _as_2d(t):
@@ -114,11 +134,16 @@ def _as_2d(t):
     return t.permute(0, 2, 3, 1).reshape(n * h * w, c)
 
 
+def _w2d(w):
+    """The channels-last filter ``[Cout][R][S][Cin]`` as the matrix ``[Cout, R*S*Cin]`` (no copy)."""
+    return w.permute(0, 2, 3, 1).reshape(w.shape[0], -1)
+
+
 class GradLink:
     """Joins the two gradients that reach the input of a residual block: the identity branch's and the first
-    convolution's.  When that convolution runs on the GEMM, its input-gradient GEMM adds its product straight onto the
-    identity branch's gradient (``accumulate=True``: TMA reduce stores), instead of autograd writing both and summing
-    them in a third pass.  Usage, inside a block's ``forward``::
+    convolution's.  When that convolution runs on the tensor-core kernels, its input-gradient kernel adds its product
+    straight onto the identity branch's gradient (``accumulate=True``: TMA reduce stores), instead of autograd writing
+    both and summing them in a third pass.  Usage, inside a block's ``forward``::
 
         link = GradLink()
         y = conv_bn_act(conv1, bn1, x, link=link)
@@ -130,7 +155,7 @@ class GradLink:
     saving is lost."""
 
     def __init__(self):
-        self.armed = False          # the convolution took the GEMM path and will look for a stashed gradient
+        self.armed = False          # the convolution took a tensor-core path and will look for a stashed gradient
         self.conv_done = False      # its backward already ran (without finding one)
         self.stash, self.stash_owned = None, False
 
@@ -155,28 +180,76 @@ class _StashGrad(torch.autograd.Function):
         return None, None
 
 
-class _Conv1x1BNAct(torch.autograd.Function):
+def _err(device):
+    return gemm._error_flag(device).data_ptr()
+
+
+def conv_forward(x, w, bias=None, stride=1, pad=1, col_partials=None, out=None, accumulate=False):
+    """``conv2d(x, w, bias, stride, pad)`` of a channels-last activation on the implicit-GEMM kernel; ``w`` is the
+    filter in channels-last memory order ``(Cout, Cin, R, R)`` or already a matrix ``[Cout, R*R*Cin]`` together with
+    ``x`` of ``Cin`` channels.  ``col_partials`` ([tiles, 2, Cout]) receives per-tile column sums / sums of squares."""
+    n, cin, h, wd = x.shape
+    w2 = _w2d(w) if w.dim() == 4 else w
+    cout = w2.shape[0]
+    r = int(round((w2.shape[1] // cin) ** 0.5))
+    ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - r) // stride + 1
+    if out is None:
+        assert not accumulate
+        out = torch.empty((n, cout, ho, wo), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+    with torch.cuda.device(x.device):
+        nat.check(nat.cuda().gc_cuda_conv_fwd(x.data_ptr(), w2.data_ptr(), out.data_ptr(), nat.ptr(bias), n, h, wd, cin, cout, r,
+                                              stride, pad, int(bool(accumulate)), nat.ptr(col_partials), _err(x.device),
+                                              nat.stream_ptr()), "conv_fwd")
+    return out
+
+
+def conv_wgrad(dy, x, r, stride, pad):
+    """Weight gradient ``[Cout, R*R*Cin]`` (channels-last filter order) of ``conv2d(x, w, stride, pad)`` given the
+    channels-last output gradient ``dy``."""
+    n, cin, h, wd = x.shape
+    cout = dy.shape[1]
+    dw = torch.zeros(cout, r * r * cin, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        nat.check(nat.cuda().gc_cuda_conv_wgrad(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), n, h, wd, cin, cout, r, stride, pad,
+                                                _err(x.device), nat.stream_ptr()), "conv_wgrad")
+    return dw
+
+
+STEM_K = 32      # row length of the gathered stem operand: R*R*Cin taps padded to one 128-byte row
+
+
+class _ConvBNAct(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu, link):
+    def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu, link,
+                mode, stride, pad):
         x = _cl(x)
-        ctx.link = link
+        ctx.link, ctx.mode, ctx.stride, ctx.pad = link, mode, stride, pad
         n, cin, h, wd = x.shape
-        cout = w.shape[0]
-        m = n * h * wd
+        cout, r = w.shape[0], w.shape[2]
+        ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - r) // stride + 1
+        m = n * ho * wo
         lib, st = nat.cuda(), nat.stream_ptr
-        yconv = torch.empty((n, cout, h, wd), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+        yconv = torch.empty((n, cout, ho, wo), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
         stats = torch.empty(2 * cout, dtype=torch.float32, device=x.device)
-        w2d = w.reshape(cout, cin)
+        gathered = None
         with torch.cuda.device(x.device):
+            tiles = gemm.m_tiles(m)
+            partials = torch.empty(tiles, 2, cout, dtype=torch.float32, device=x.device) if training else None
+            if mode == "gemm":
+                gemm.gemm_tf32(_as_2d(x), w.reshape(cout, cin), bias=cbias, out=_as_2d(yconv), col_partials=partials)
+            elif mode == "conv":
+                conv_forward(x, w, cbias, stride, pad, col_partials=partials, out=yconv)
+            else:
+                gathered = torch.empty(m, STEM_K, dtype=torch.float32, device=x.device)
+                wpad = torch.empty(cout, STEM_K, dtype=torch.float32, device=x.device)
+                nat.check(lib.gc_cuda_im2col_small(x.data_ptr(), gathered.data_ptr(), n, h, wd, cin, r, pad, STEM_K,
+                                                   w.data_ptr(), wpad.data_ptr(), cout, st()), "im2col_small")
+                gemm.gemm_tf32(gathered, wpad, bias=cbias, out=_as_2d(yconv), col_partials=partials)
             if training:
-                tiles = gemm.m_tiles(m)
-                partials = torch.empty(tiles, 2, cout, dtype=torch.float32, device=x.device)
-                gemm.gemm_tf32(_as_2d(x), w2d, bias=cbias, out=_as_2d(yconv), col_partials=partials)
                 nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), tiles, m, cout, stats.data_ptr(),
                                                            nat.ptr(running_mean), nat.ptr(running_var), float(momentum),
                                                            float(eps), st()), "bn_finalize_partials")
             else:
-                gemm.gemm_tf32(_as_2d(x), w2d, bias=cbias, out=_as_2d(yconv))
                 stats[:cout] = running_mean
                 stats[cout:] = torch.rsqrt(running_var + eps)
             res = _cl(residual) if residual is not None else None
@@ -184,16 +257,17 @@ class _Conv1x1BNAct(torch.autograd.Function):
             nat.check(lib.gc_cuda_bn_apply(yconv.data_ptr(), m, cout, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                            nat.ptr(res), int(relu), out.data_ptr(), st()), "bn_apply")
         ctx.relu, ctx.has_res, ctx.has_cbias = bool(relu), residual is not None, cbias is not None
-        ctx.save_for_backward(x, w, yconv, gamma, beta, stats, out if (residual is not None and relu) else None)
+        ctx.save_for_backward(x, w, yconv, gamma, beta, stats, out if (residual is not None and relu) else None, gathered)
         return out
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, yconv, gamma, beta, stats, out = ctx.saved_tensors
+        x, w, yconv, gamma, beta, stats, out, gathered = ctx.saved_tensors
         dy = _cl(dy)
-        n, cout, h, wd = yconv.shape
-        cin = x.shape[1]
-        m = n * h * wd
+        mode, stride, pad = ctx.mode, ctx.stride, ctx.pad
+        n, cout, ho, wo = yconv.shape
+        cin, r = x.shape[1], w.shape[2]
+        m = n * ho * wo
         lib, st = nat.cuda(), nat.stream_ptr
         sums = torch.empty(2 * cout, dtype=torch.float32, device=x.device)
         dconv = torch.empty_like(yconv)
@@ -209,54 +283,91 @@ class _Conv1x1BNAct(torch.autograd.Function):
             dx = None
             link = ctx.link
             if ctx.needs_input_grad[0]:
-                wt = _transposed.get(w)                                     # [Cin, Cout]: K-major for dX = dY x W
                 acc = None
                 if link is not None and link.stash is not None:
                     acc, link.stash = link.stash, None
                     if not (link.stash_owned and acc.shape == x.shape and acc.dtype == torch.float32
                             and acc.is_contiguous(memory_format=torch.channels_last)):
                         acc = acc.contiguous(memory_format=torch.channels_last).clone()     # not ours to write into
-                if acc is not None and gemm.can_accumulate(_as_2d(acc)):
-                    dx = acc                                                # dX = identity-branch gradient + dY x W, added in L2
-                    gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx), accumulate=True)
-                else:
-                    dx = torch.empty_like(x)
-                    gemm.gemm_tf32(_as_2d(dconv), wt, out=_as_2d(dx))
-                    if acc is not None:
+                tc_dgrad = mode == "gemm" or (mode == "conv" and stride == 1 and
+                                              lib.gc_cuda_conv_fwd_supported(n, ho, wo, cout, cin, r, 1, r - 1 - pad))
+                if tc_dgrad:
+                    wd_ = _dgrad_weights.get(w)           # [Cin, taps * Cout]: the K-major operand of dX = dY (*) rot(W)
+                    accumulate = acc is not None and gemm.can_accumulate(_as_2d(acc))
+                    dx = acc if accumulate else torch.empty_like(x)
+                    if mode == "gemm":
+                        gemm.gemm_tf32(_as_2d(dconv), wd_, out=_as_2d(dx), accumulate=accumulate)
+                    else:
+                        conv_forward(dconv, wd_, None, 1, r - 1 - pad, out=dx, accumulate=accumulate)
+                    if acc is not None and not accumulate:
                         dx += acc
+                else:
+                    dx = torch.ops.aten.convolution_backward(dconv, x, w, None, [stride, stride], [pad, pad], [1, 1], False,
+                                                             [0, 0], 1, [True, False, False])[0]
+                    if acc is not None:
+                        dx = dx + acc
             if link is not None:
                 link.conv_done = True
             dw = None
             if ctx.needs_input_grad[1]:
-                if WGRAD_ENABLED and cout % 32 == 0 and cin % 32 == 0:
+                if mode == "gemm" and WGRAD_ENABLED and cout % 32 == 0 and cin % 32 == 0:
                     # dW[Cout, Cin] = dY^T X over all positions: split-K GEMM with MN-major tcgen05 operands
                     dw2d = gemm.gemm_tn_tf32(_as_2d(dconv), _as_2d(x))
                     dw = dw2d.view(cout, cin, 1, 1).contiguous(memory_format=torch.channels_last)
+                elif mode == "conv" and WGRAD_ENABLED and lib.gc_cuda_conv_wgrad_supported(n, x.shape[2], x.shape[3], cin, cout, r,
+                                                                                           stride, pad):
+                    dw = conv_wgrad(dconv, x, r, stride, pad).view(cout, r, r, cin).permute(0, 3, 1, 2)
+                elif mode == "stem" and WGRAD_ENABLED and cout % 32 == 0:
+                    dwp = gemm.gemm_tn_tf32(_as_2d(dconv), gathered)                       # [Cout, STEM_K]
+                    dw = dwp[:, : r * r * cin].reshape(cout, r, r, cin).permute(0, 3, 1, 2)
                 else:
-                    dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [1, 1], [0, 0], [1, 1], False, [0, 0], 1,
-                                                             [False, True, False])[1]
-            dcb = dconv.sum((0, 2, 3)) if ctx.has_cbias else None
-        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None
+                    dw = torch.ops.aten.convolution_backward(dconv, x, w, None, [stride, stride], [pad, pad], [1, 1], False,
+                                                             [0, 0], 1, [False, True, False])[1]
+            # a bias in front of a training-mode batch norm has no effect on the output: its gradient is the sum of
+            # dconv over all positions, which the batch norm's backward makes zero up to rounding
+            dcb = torch.zeros(cout, dtype=torch.float32, device=x.device) if ctx.has_cbias else None
+        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None
 
 
-def _fusable(conv, bn, x):
+def _mode(conv, bn, x):
+    """Which tensor-core path runs ``conv`` on ``x`` ("gemm", "conv", "stem") or None for cuDNN."""
     if not (ENABLED and x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and isinstance(conv, torch.nn.Conv2d)):
-        return False
-    if not torch.backends.cudnn.allow_tf32:       # the GEMM multiplies in TF32: only where TF32 convolutions are allowed
-        return False
-    if conv.kernel_size != (1, 1) or conv.stride != (1, 1) or conv.padding != (0, 0) or conv.groups != 1 or conv.dilation != (1, 1):
-        return False
+        return None
+    if not torch.backends.cudnn.allow_tf32:       # the kernels multiply in TF32: only where TF32 convolutions are allowed
+        return None
+    k, s, p = conv.kernel_size, conv.stride, conv.padding
+    if conv.groups != 1 or conv.dilation != (1, 1) or k[0] != k[1] or s[0] != s[1] or isinstance(p, str) or p[0] != p[1]:
+        return None
+    if conv.padding_mode != "zeros":
+        return None
     if not bn.affine or (not (bn.training or bn.running_mean is None) and torch.is_grad_enabled() and
                          (x.requires_grad or conv.weight.requires_grad)):
-        return False
+        return None
     n, cin, h, w = x.shape
-    if cin % 4 or conv.out_channels % 4 or n * h * w < MIN_ROWS:
-        return False
-    return bool(nat.cuda().gc_cuda_bn_supported(n * h * w, conv.out_channels))
+    r, stride, pad = k[0], s[0], p[0]
+    cout = conv.out_channels
+    ho, wo = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    if ho < 1 or wo < 1 or n * ho * wo < MIN_ROWS or cout % 4:
+        return None
+    lib = nat.cuda()
+    if not lib.gc_cuda_bn_supported(n * ho * wo, cout):
+        return None
+    if r == 1 and stride == 1 and pad == 0:
+        mode = "gemm" if cin % 4 == 0 else None
+    elif (cin * r * r <= STEM_K and stride == 1 and 2 * pad == r - 1 and cout > 16 and not x.requires_grad
+          and conv.weight.is_contiguous(memory_format=torch.channels_last)):
+        mode = "stem"
+    elif conv.weight.is_contiguous(memory_format=torch.channels_last) and lib.gc_cuda_conv_fwd_supported(n, h, w, cin, cout, r,
+                                                                                                          stride, pad):
+        mode = "conv"
+    else:
+        mode = None
+    return mode if mode in PATHS else None
 
 
 def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
-    if not _fusable(conv, bn, x):
+    mode = _mode(conv, bn, x)
+    if mode is None:
         return bn_act(bn, conv(x), residual=residual, relu=relu)
     if link is not None:
         link.armed = LINK_ENABLED and torch.is_grad_enabled() and x.requires_grad
@@ -266,5 +377,6 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
         count_batch(bn)
     rm = bn.running_mean if bn.track_running_stats else None
     rv = bn.running_var if bn.track_running_stats else None
-    return _Conv1x1BNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,
-                               bn.eps, relu, link if (link is not None and link.armed) else None)
+    return _ConvBNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,
+                            bn.eps, relu, link if (link is not None and link.armed) else None, mode, conv.stride[0],
+                            conv.padding[0])

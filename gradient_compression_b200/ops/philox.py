@@ -19,7 +19,7 @@ def stream_id(rank: int, purpose: int) -> int:
     return ((int(rank) & 0xFFFFFF) << 8) | (int(purpose) & 0xFF)
 
 
-def _fill(kind, n, seed, stream, step, device, out=None):
+def _fill(kind, n, seed, stream, step, device, out=None, step_offset=None):
     device = torch.device(device)
     dtype = torch.int32 if kind == "u32" else torch.float32
     if out is None:
@@ -28,9 +28,12 @@ def _fill(kind, n, seed, stream, step, device, out=None):
     seed, stream, step = int(seed) & (2 ** 64 - 1), int(stream) & 0xFFFFFFFF, int(step) & 0xFFFFFFFF
     if out.is_cuda:
         with torch.cuda.device(out.device):
-            nat.check(nat.cuda().gc_cuda_philox_fill(_KIND[kind], seed, stream, step, n, out.data_ptr(),
+            assert step_offset is None or (step_offset.is_cuda and step_offset.dtype == torch.int32)
+            nat.check(nat.cuda().gc_cuda_philox_fill(_KIND[kind], seed, stream, step, nat.ptr(step_offset), n, out.data_ptr(),
                                                      nat.stream_ptr()), "philox_fill")
     else:
+        if step_offset is not None:
+            step = (step + int(step_offset.item())) & 0xFFFFFFFF
         fn = {"uniform": nat.host().gc_host_philox_uniform, "normal": nat.host().gc_host_philox_normal,
               "u32": nat.host().gc_host_philox_u32}[kind]
         fn(seed, stream, step, n, out.data_ptr())
@@ -42,9 +45,11 @@ def uniform(n, seed, stream, step=0, device="cpu", out=None):
     return _fill("uniform", n, seed, stream, step, device, out)
 
 
-def normal(n, seed, stream, step=0, device="cpu", out=None):
-    """n standard normals (Box-Muller on word pairs of each block)."""
-    return _fill("normal", n, seed, stream, step, device, out)
+def normal(n, seed, stream, step=0, device="cpu", out=None, step_offset=None):
+    """n standard normals (Box-Muller on word pairs of each block).  ``step_offset`` (one int32 on ``out``'s device) is
+    added to ``step`` when the fill runs, so a launch replayed from a CUDA graph draws a new stream each time its
+    owner advances the counter."""
+    return _fill("normal", n, seed, stream, step, device, out, step_offset)
 
 
 def u32(n, seed, stream, step=0, device="cpu", out=None):

@@ -123,3 +123,8 @@ class LocalGroup(_ArenaBase):
 
 def required_bytes(n):
     return int(nat.cuda().gc_comm_required_bytes(int(n)))
+
+
+def oneshot_bytes(region_bytes):
+    """Arena size for the one-shot kernels when each of the two parity regions must hold ``region_bytes``."""
+    return int(nat.cuda().gc_comm_oneshot_bytes(int(region_bytes)))

@@ -69,13 +69,16 @@ class FusedOps:
                                                                       self.timeout_ms, self.max_blocks,
                                                                       nat.stream_ptr()))
 
-    def randk(self, ins, outs, seed, npass, start, k, bits_lo, bits_hi=0, zero_unselected=False, step=0):
+    def randk(self, ins, outs, seed, npass, start, k, bits_lo, bits_hi=0, zero_unselected=False, step=0, window=None):
+        """``window`` (one int64 on the device): the kernel takes the window's start from it and advances it, so that
+        a replayed CUDA graph selects new coordinates every step; ``k`` is then the nominal window length K."""
         ins, outs, (ctxs, nv, ia, oa) = self._prep(ins, outs)
+        assert window is None or (window.is_cuda and window.dtype == torch.int64)
         with torch.cuda.device(self.arena.device):
             self._run("fused_randk", nat.cuda().gc_fused_randk(ctxs, nv, ia, oa, ins[0].numel(), int(seed), int(npass),
                                                               int(start), int(k), int(bits_lo), int(bits_hi),
-                                                              int(bool(zero_unselected)), int(step), self.timeout_ms,
-                                                              self.max_blocks, nat.stream_ptr()))
+                                                              int(bool(zero_unselected)), int(step), nat.ptr(window),
+                                                              self.timeout_ms, self.max_blocks, nat.stream_ptr()))
 
     def sparse(self, vals, outs, idxs, alpha):
         vals, outs, (ctxs, nv, ia, oa) = self._prep(vals, outs)
@@ -93,18 +96,42 @@ class FusedOps:
 
 _shared_arena = {}
 
+# One-shot arenas are created at least this large, so that buckets or reducers of different sizes do not regrow them.
+ONESHOT_MIN_BYTES = 8 << 20
 
-def shared_arena(nbytes, device, group=None):
-    """One arena per (device, group), grown collectively when a larger gradient shows up."""
-    key = (str(device), id(group))
+
+def _drain_group(device, group):
+    """Every rank's kernels on the arena have finished: local synchronise, then a barrier over the group."""
+    import torch.distributed as dist
+
+    torch.cuda.synchronize(device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.barrier(group=group)
+
+
+def shared_arena(nbytes, device, group=None, family="twoshot", make=None, drain=None):
+    """One arena per (device, group, kernel family), replaced collectively when a larger one is needed.
+
+    ``family``: the two-shot kernels (QSGD, multi-scale, all-reduce; closing round, whole arena) and the one-shot
+    kernels (small sum, sparse exchange, Rand-K; no closing round, two parity regions) never share an arena, so a
+    rank that has moved on to the next kernel of the other family cannot write where a slower peer still reads.
+    Replacing an arena frees memory that peers have mapped: all ranks reach this call with the same sizes, and the old
+    arena is closed only after every rank's kernels have drained (``drain``: local synchronise + group barrier) --
+    the one-shot kernels have no closing round, so a local synchronise alone would not do.
+    ``make`` / ``drain`` are injection points for tests."""
+    key = (str(device), id(group), family)
     cur = _shared_arena.get(key)
     if cur is None or cur.bytes < nbytes:
         if cur is not None:
-            torch.cuda.synchronize(device)
+            (drain or _drain_group)(device, group)
             cur.close()
-        cur = comm.SymmetricArena(nbytes, device, group)
+        cur = (make or comm.SymmetricArena)(nbytes, device, group)
         _shared_arena[key] = cur
     return cur
+
+
+def _align256(x):
+    return (int(x) + 255) // 256 * 256
 
 
 class FusedEngine:
@@ -113,7 +140,8 @@ class FusedEngine:
     def __init__(self, reducer):
         self.device = reducer._device
         self.group = reducer._group
-        self.ops = None
+        self.ops = None             # FusedOps of the family used last (what status checks look at)
+        self._ops = {}              # family -> FusedOps
         self._n = 0
 
     @classmethod
@@ -122,14 +150,26 @@ class FusedEngine:
             return None
         return cls(reducer)
 
-    def _ensure(self, n):
+    def _ensure(self, n, oneshot_region_bytes=None):
+        """``FusedOps`` on the shared arena of the right family: two-shot kernels on an ``n``-element gradient, or
+        (``oneshot_region_bytes`` given) one-shot kernels whose parity regions hold that many bytes each."""
         # the arena is shared by every reducer of this device / group and may have been regrown by another
         # one since the last call: always go through the registry, never keep a stale handle
-        arena = shared_arena(comm.required_bytes(n), self.device, self.group)
-        if self.ops is None or self.ops.arena is not arena:
-            self.ops = FusedOps(arena)
+        if oneshot_region_bytes is None:
+            family, nbytes = "twoshot", comm.required_bytes(n)
+        else:
+            family, nbytes = "oneshot", max(comm.oneshot_bytes(oneshot_region_bytes), ONESHOT_MIN_BYTES)
+        arena = shared_arena(nbytes, self.device, self.group, family)
+        ops = self._ops.get(family)
+        if ops is None or ops.arena is not arena:
+            ops = self._ops[family] = FusedOps(arena)
+        self.ops = ops
         self._n = max(self._n, n)
-        return self.ops
+        return ops
+
+    def arenas(self):
+        """Every arena this engine has launched on (status words to check, graphs to arm)."""
+        return [o.arena for o in self._ops.values()]
 
     @staticmethod
     def _out_flat(flat, grad_out):
@@ -195,20 +235,21 @@ class FusedEngine:
 
     def randk(self, reducer, flat, grad_out, start, k, npass):
         n = flat.buffer.numel()
-        ops = self._ensure(n)
+        ops = self._ensure(n, 3 * _align256(4 * k))
         dest, tmp = self._out_flat(flat, grad_out)
         lo = reducer._quantization_level
         hi = getattr(reducer, "_higher_quantization_level", 0)
+        window = reducer._device_window(start)
         with reducer._timer("reduce.fused", verbosity=2):
-            ops.randk(flat.buffer, dest, reducer._queue.seed, npass, start, k, lo, hi,
-                      reducer._unselected == "zero", reducer._noise.next_step())
+            ops.randk(flat.buffer, dest, reducer._queue.seed, npass, start, reducer._K if window is not None else k, lo, hi,
+                      reducer._unselected == "zero", reducer._noise.next_step(), window=window)
         self._finish(flat, grad_out, dest, tmp)
         container = 8 if lo < 8 else 32
         return 32 + container * k + (8 * k if hi else 0)
 
     def sparse(self, reducer, flat, grad_out, idx, vals):
         n = flat.buffer.numel()
-        ops = self._ensure(n)
+        ops = self._ensure(n, 2 * _align256(4 * vals.numel()))
         dest, tmp = self._out_flat(flat, grad_out)
         with reducer._timer("reduce.fused", verbosity=2):
             ops.sparse(vals, dest, idx, 1.0 / reducer.n_workers)
@@ -250,15 +291,17 @@ class FusedEngine:
         if reducer.rank_r > lib.gc_cuda_psgd_max_rank():
             return None
         n = flat.buffer.numel()
-        ops = self._ensure(n)
         c = self._psgd_tables(reducer, flat, plan)
+        ops = self._ensure(n, 4 * max(plan["p_total"] + c["v_total"], plan["q_total"], 1))
         dest, tmp = self._out_flat(flat, grad_out)
         g, e = flat.buffer, reducer._memory
         p_total, q_total = plan["p_total"], plan["q_total"]
         with reducer._timer("reduce.prepare.q", verbosity=2):
             if not (reducer.reuse_query and not fresh):
-                philox.normal(q_total, reducer._seed, philox.stream_id(0, philox.PURPOSE_QINIT), reducer._step,
-                              device=g.device, out=reducer.q_memory)
+                # the step counter of the query stream lives on the device (a replayed graph draws a new Q every step)
+                philox.normal(q_total, reducer._seed, philox.stream_id(0, philox.PURPOSE_QINIT), 0,
+                              device=g.device, out=reducer.q_memory, step_offset=reducer._device_step())
+                reducer._step_dev.add_(1)
         st = nat.stream_ptr
         with torch.cuda.device(g.device):
             with reducer._timer("reduce.compute.p", verbosity=2):

@@ -57,6 +57,26 @@ class ProtocolViolation(AssertionError):
     pass
 
 
+def oneshot_schedule(sizes, half=None):
+    """Launches of a one-shot kernel (publish, signal, wait, read everybody's; no closing round) whose buffers have
+    different sizes, with the arena modelled as numbered cells so that overlaps between launches show up.
+
+    ``sizes[i]`` cells are published by launch ``i`` (epoch ``i + 1``) in the region of the epoch's parity.
+    ``half=None``: the regions of a launch lie back to back, ``[parity * size, (parity + 1) * size)`` -- the layout
+    whose parity-1 region moves with the size of the call, so that a larger launch's parity-0 region covers what the
+    previous, smaller launch published (the fault).  ``half=H``: parity ``p`` starts at cell ``p * H`` whatever the
+    size (``gc_fused.cu::parity_half_bytes``)."""
+    schedule = []
+    for i, size in enumerate(sizes):
+        par = (i + 1) & 1
+        first = par * (size if half is None else half)
+        assert half is None or size <= half
+        cells = [f"cell{c}" for c in range(first, first + size)]
+        schedule.append([("write_own", c) for c in cells] + [("signal", "AUX"), ("wait", "AUX")] +
+                        [("read_peers", c) for c in cells])
+    return schedule
+
+
 def _expand(kernel_ops, world, rank, epoch):
     """Micro-actions of one step of one rank: (kind, target rank, name, epoch)."""
     acts = []

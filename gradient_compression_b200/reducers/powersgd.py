@@ -31,7 +31,19 @@ class RankKReducer(Reducer):
         self.q_memory = None
         self._memory = None
         self._step = 0
+        self._step_dev = None     # device copy of the step counter of the query stream (fused path)
         self._layout = None
+
+    def _device_step(self):
+        if self._step_dev is None:
+            self._step_dev = torch.tensor([self._step], dtype=torch.int32, device=self._device)
+        return self._step_dev
+
+    def graph_safe(self):
+        """Replayable from a CUDA graph: the query stream's step counter lives on the device.  With ``reuse_query`` the
+        first step differs from the later ones (it draws Q), so capture must come after it -- which the eager warm-up
+        steps of ``GraphedStep`` guarantee."""
+        return True
 
     # the reference stores the approximation rank in ``self.rank`` (shadowing the worker rank)
     def _plan(self, grad_in):
@@ -118,6 +130,8 @@ class RankKReducer(Reducer):
         return bits
 
     def state_dict(self):
+        if self._step_dev is not None:
+            self._step = int(self._step_dev.item())
         sd = {"step": self._step}
         for k in ("_memory", "p_memory", "q_memory"):
             if getattr(self, k) is not None:
@@ -126,6 +140,8 @@ class RankKReducer(Reducer):
 
     def load_state_dict(self, sd):
         self._step = int(sd["step"])
+        if self._step_dev is not None:
+            self._step_dev.fill_(self._step)
         for k in ("_memory", "p_memory", "q_memory"):
             if k in sd:
                 setattr(self, k, sd[k].to(self._device).clone())

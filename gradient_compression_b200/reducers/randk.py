@@ -50,6 +50,7 @@ class GlobalRandKMaxNormReducer(Reducer):
         self._K = K
         self._unselected = unselected
         self._queue = _IndexQueue(seed, K, reshuffle_each_pass)
+        self._window = None       # device copy of the queue position, advanced by the fused kernel itself
         self._noise = C.NoiseSource(seed, self.rank)
         self._compressor = C.GlobalRandKMaxNormCompressor(self._device, quantization_level, noise=self._noise)
 
@@ -89,12 +90,35 @@ class GlobalRandKMaxNormReducer(Reducer):
             flat.scatter_to(grad_out)
         return bits
 
+    def _device_window(self, start):
+        """The device-resident window start for the fused kernel (None when the permutation is re-keyed every pass: the
+        key is built on the host).  Created from the host queue's position of the current step; from then on the kernel
+        advances it, which is what keeps a replayed CUDA graph walking through the permutation."""
+        if self._queue.reshuffle:
+            return None
+        if self._window is None:
+            import torch
+
+            self._window = torch.tensor([start], dtype=torch.int64, device=self._device)
+        return self._window
+
+    def graph_safe(self):
+        """Replayable from a CUDA graph: every per-step quantity (window start, rounding step) is derived on the device."""
+        return not self._queue.reshuffle
+
+    def _sync_queue_from_device(self):
+        if self._window is not None:
+            self._queue.position = int(self._window.item())      # position of the NEXT window (0 = start of a pass)
+
     def state_dict(self):
+        self._sync_queue_from_device()
         return {"noise": self._noise.state_dict(), "queue": self._queue.state_dict()}
 
     def load_state_dict(self, sd):
         self._noise.load_state_dict(sd["noise"])
         self._queue.load_state_dict(sd["queue"])
+        if self._window is not None:
+            self._window.fill_(self._queue.position)
 
 
 class GlobalRandKMaxNormTwoScaleReducer(GlobalRandKMaxNormReducer):

@@ -125,7 +125,7 @@ def tc_conv():
 @pytest.mark.parametrize("relu", [False, True])
 def test_conv1x1_bn_act_matches_torch(tc_conv, shape, residual, relu):
     """1x1 convolution on the tcgen05 GEMM with BN statistics from its epilogue vs cuDNN conv + torch bn."""
-    from gradient_compression_b200.ops.conv import _fusable, conv_bn_act
+    from gradient_compression_b200.ops.conv import _mode, conv_bn_act
 
     n, cin, h, w, cout = shape
     g = torch.Generator().manual_seed(cin + cout)
@@ -141,7 +141,7 @@ def test_conv1x1_bn_act_matches_torch(tc_conv, shape, residual, relu):
         bn_a.weight.copy_(torch.rand(cout, generator=g) + 0.5)
         bn_a.bias.copy_(torch.randn(cout, generator=g) * 0.1)
     bn_b.load_state_dict(bn_a.state_dict())
-    assert _fusable(conv_a, bn_a, x)
+    assert _mode(conv_a, bn_a, x) == "gemm"
     xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
     ra = r.clone().requires_grad_(True) if residual else None
     rb = r.clone().requires_grad_(True) if residual else None
@@ -208,7 +208,7 @@ def test_input_gradient_follows_weight_updates(tc_conv):
             with torch.no_grad():                        # in-place torch update: the version counter moves
                 for c in convs:
                     c.weight.add_(torch.randn_like(c.weight) * 0.3)
-    assert getattr(arena, "_transposed_weight_table", None) is not None and arena._transposed_weight_table[1].shape[0] == 2
+    assert getattr(arena, "_dgrad_weight_table", None) is not None and arena._dgrad_weight_table[1].shape[0] == 2
 
 
 @pytest.mark.parametrize("owned", [True, False])

@@ -2,6 +2,7 @@
 faults the protocol is designed against."""
 import pytest
 
+from gradient_compression_b200.parallel import protocol_model as pm
 from gradient_compression_b200.parallel.protocol_model import KERNELS, ProtocolViolation, check
 
 
@@ -78,3 +79,43 @@ def test_gemm_pipeline_seeded_faults():
     with pytest.raises(ProtocolViolation):          # accumulator released after one of two epilogue threads arrived
         check_gemm_pipeline(acc_empty_count=1)
     assert check_gemm_pipeline(acc_buffers=1, tiles=3) > 0      # the arithmetic also holds for a single accumulator
+
+
+def test_oneshot_buffers_of_different_sizes_need_a_fixed_parity_distance():
+    """Consecutive one-shot launches of different sizes (buckets, several reducers on one arena): with the parity-1
+    region placed right behind a parity-0 region of the CALL's size, a larger launch overwrites what a slower peer still
+    reads from the previous launch; with the regions a fixed distance apart it cannot."""
+    for sizes in ([1, 2], [2, 2, 1], [1, 3, 1, 2]):
+        with pytest.raises(pm.ProtocolViolation):
+            pm.check(pm.oneshot_schedule(sizes, half=None), world=2)
+        assert pm.check(pm.oneshot_schedule(sizes, half=3), world=2) > 0
+    assert pm.check(pm.oneshot_schedule([1, 2, 1], half=2), world=3) > 0
+
+
+def test_shared_arena_is_drained_before_it_is_replaced():
+    """Replacing a shared arena frees memory that peers have mapped: the old one may only be closed after the drain
+    (local synchronise + group barrier) has run, and kernel families never share an arena."""
+    from gradient_compression_b200.parallel import engine
+
+    log = []
+
+    class FakeArena:
+        def __init__(self, nbytes, device, group):
+            self.bytes = nbytes
+            log.append(("create", nbytes))
+
+        def close(self):
+            log.append(("close", self.bytes))
+
+    def drain(device, group):
+        log.append(("drain",))
+
+    grp = object()
+    a = engine.shared_arena(100, "fake:0", grp, "oneshot", make=FakeArena, drain=drain)
+    assert engine.shared_arena(50, "fake:0", grp, "oneshot", make=FakeArena, drain=drain) is a
+    b = engine.shared_arena(200, "fake:0", grp, "oneshot", make=FakeArena, drain=drain)
+    assert b is not a and log == [("create", 100), ("drain",), ("close", 100), ("create", 200)]
+    c = engine.shared_arena(10, "fake:0", grp, "twoshot", make=FakeArena, drain=drain)
+    assert c is not b and log[-1] == ("create", 10)
+    for fam in ("oneshot", "twoshot"):
+        engine._shared_arena.pop(("fake:0", id(grp), fam))
