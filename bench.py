@@ -52,6 +52,12 @@ def parse_args():
     p.add_argument("--channels-last", type=int, default=1)
     p.add_argument("--cudnn-benchmark", type=int, default=1, help="let cuDNN autotune its convolution algorithms (ours)")
     p.add_argument("--cudnn-benchmark-limit", type=int, default=-1, help="algorithms cuDNN's autotuner tries (0 = all; -1 = torch default)")
+    p.add_argument("--norm-scope", default="global", choices=["global", "bucket"],
+                   help="global: one reduce after backward with one max-norm (the reference); bucket: per-bucket reduces "
+                        "on a side stream while backward runs, each with its own max-norm (ours)")
+    p.add_argument("--bucket-mb", type=float, default=25.0)
+    p.add_argument("--reduce-max-blocks", type=int, default=32, help="grid cap of a fused reduce that overlaps backward (ours)")
+    p.add_argument("--sustained-seconds", type=float, default=3.0, help="0 = skip the sustained measurement")
     p.add_argument("--no-e2e", action="store_true")
     return p.parse_args()
 
@@ -137,6 +143,43 @@ def barrier_sync():
     torch.cuda.synchronize()
 
 
+def measure_sustained(one_step, args, world, rank, local_rank, device):
+    """The same timed region (``args.steps`` steps between CUDA events) repeated until the GPU has been under load for
+    ``args.sustained_seconds``: the median block says what a step costs once clocks have settled under the power cap.
+    ``value`` / ``steps`` of the bench line stay the K-step burst; this is reported beside them."""
+    if args.sustained_seconds <= 0:
+        return None
+    barrier_sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    per_block, t_begin = [], time.perf_counter()
+    while True:
+        s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_ev.record()
+        for i in range(args.steps):
+            one_step(i)
+        e_ev.record()
+        e_ev.synchronize()
+        per_block.append(s_ev.elapsed_time(e_ev) / args.steps)
+        more = torch.tensor([1.0 if time.perf_counter() - t_begin < args.sustained_seconds else 0.0], device=device)
+        if dist.is_initialized():
+            dist.all_reduce(more, op=dist.ReduceOp.MAX)      # every rank runs the same number of blocks
+        if float(more.item()) == 0.0:
+            break
+    seconds = time.perf_counter() - t_begin
+    barrier_sync()
+    clocks = sampler.stop() if rank == 0 else None
+    med = max_over_ranks(statistics.median(per_block), device)
+    out = {"ms_per_step": med, "value": args.batch * world / (med * 1e-3), "unit": "images/s", "blocks": len(per_block),
+           "steps_per_block": args.steps, "seconds": max_over_ranks(seconds, device)}
+    if clocks is not None:
+        out["clocks"] = clocks
+        if clocks.get("sm_mhz"):
+            out["ms_times_sm_mhz"] = med * clocks["sm_mhz"]
+    return out
+
+
 def reducer_config(args):
     return dict(quantization_level=args.bits, higher_quantization_level=args.higher_bits, K=args.K, rank=args.rank,
                 seed=42, backend=args.backend, compression=0.01, quantization_levels=[args.bits, args.higher_bits])
@@ -161,7 +204,13 @@ def run_ours(args, world, rank, local_rank):
                  synthetic_train_size=args.batch * world * steps_needed, synthetic_test_size=args.batch,
                  broadcast_parameters=True, channels_last=bool(args.channels_last))
     opt = FlatSGD(task.arena, lr=0.1, momentum=0.9, weight_decay=5e-4, nesterov=True)
-    reducer = make_reducer(args.reducer, device, None, reducer_config(args))
+    if args.norm_scope == "bucket":
+        from gradient_compression_b200.parallel.bucketed import BucketedReducer
+        reducer = BucketedReducer(task.parameters, args.reducer, device, None, reducer_config(args), bucket_mb=args.bucket_mb,
+                                  max_blocks=args.reduce_max_blocks)
+    else:
+        reducer = make_reducer(args.reducer, device, None, reducer_config(args))
+    # the step evaluates cross-entropy, top-1 and top-5 of the batch on the device, as the reference's step does
     step_fn = GraphedStep(task, reducer, opt, enabled=bool(args.graph))
 
     # device-resident batches for the device-timed loop
@@ -195,6 +244,8 @@ def run_ours(args, world, rank, local_rank):
     clocks = sampler.stop() if rank == 0 else None
     assert torch.isfinite(loss).all(), "loss is not finite"
 
+    sustained = measure_sustained(lambda i: step_fn(dev_batches[i % 4]), args, world, rank, local_rank, device)
+
     e2e = None
     if not args.no_e2e:
         from gradient_compression_b200.train.data import LaggedReadback
@@ -207,26 +258,32 @@ def run_ours(args, world, rank, local_rank):
         t0 = time.perf_counter()
         for _ in range(args.steps):
             batch = next(it)                      # host -> device copy of this step's inputs (issued one step ahead)
-            loss = step_fn(batch)
-            v = reader.push(loss)                 # device -> host read of this step's loss, collected one step later
+            step_fn(batch)
+            v = reader.push(step_fn.metrics_vec)  # device -> host read of this step's loss / top-1 / top-5, collected one step later
             if v is not None:
-                loss_host = v
-        loss_host = reader.drain()[-1]            # the last step's loss is read before the clock stops
+                loss_host = v[0]
+        loss_host = reader.drain()[-1][0]         # the last step's result is read before the clock stops
         barrier_sync()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, device) / args.steps
         e2e = {"value": args.batch * world / (e2e_ms * 1e-3), "unit": "images/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": args.batch * 3 * 32 * 32 * 4 + args.batch * 8, "d2h_bytes_per_step": 4,
+               "h2d_bytes_per_step": args.batch * 3 * 32 * 32 * 4 + args.batch * 8, "d2h_bytes_per_step": 12,
                "last_loss": loss_host,
-               "pipelining": "every step copies one batch host->device (issued two steps ahead on a side stream) and reads one "
-                             "loss device->host (collected one step late); the last loss is read before the clock stops"}
+               "pipelining": "every step copies one batch host->device (issued two steps ahead on a side stream) and reads its "
+                             "cross-entropy, top-1 and top-5 device->host (collected one step late); the last step's are read "
+                             "before the clock stops"}
     from gradient_compression_b200.ops import conv as conv_ops
-    conv_path = ("1x1 (stride 1, >= %d positions): own tcgen05 TF32 GEMM with BN statistics in the epilogue, forward and "
-                 "input gradient; other convolutions and weight gradients: cuDNN" % conv_ops.MIN_ROWS) if conv_ops.ENABLED \
-        else "cuDNN (torch); own tcgen05 GEMM path off (GCB200_TC_CONV=0)"
-    extra = {"graph": step_fn.graphed, "backend": getattr(reducer, "backend", "auto"),
-             "fused": bool(getattr(reducer, "_fused", None)), "channels_last": bool(args.channels_last), "cudnn_benchmark": bool(args.cudnn_benchmark),
-             "conv_path": conv_path, "wire_bits_per_step": getattr(reducer, "last_wire_bits", None)}
-    return dev_ms, launches, clocks, e2e, extra
+    conv_path = ("own tcgen05 TF32 kernels (paths: %s; >= %d output positions) with BN statistics in the epilogue: forward, "
+                 "input gradient (stride 1) and weight gradient; input gradients of strided convolutions: cuDNN"
+                 % (",".join(sorted(conv_ops.PATHS)), conv_ops.MIN_ROWS)) if conv_ops.ENABLED \
+        else "cuDNN (torch); own tcgen05 paths off (GCB200_TC_CONV=0)"
+    first = reducer.reducers[0] if hasattr(reducer, "reducers") else reducer
+    extra = {"graph": step_fn.graphed, "backend": getattr(first, "backend", "auto"), "norm_scope": args.norm_scope,
+             "buckets": len(reducer.buckets) if hasattr(reducer, "buckets") else 1,
+             "fused": bool(getattr(first, "_fused", None)), "channels_last": bool(args.channels_last), "cudnn_benchmark": bool(args.cudnn_benchmark),
+             "conv_path": conv_path, "wire_bits_per_step": getattr(first, "last_wire_bits", None),
+             "step_evaluates": "cross-entropy, top-1, top-5 on the device (as the reference's step)",
+             "capture_error": step_fn.capture_error}
+    return dev_ms, launches, clocks, e2e, extra, sustained
 
 
 # ------------------------------------------------------------------------------------------ reference
@@ -316,6 +373,7 @@ def run_reference(args, world, rank, local_rank):
     barrier_sync()
     dev_ms = max_over_ranks(start.elapsed_time(end), device) / args.steps
     clocks = sampler.stop() if rank == 0 else None
+    sustained = measure_sustained(lambda i: ref_step(dev_batches[i % 4]), args, world, rank, local_rank, device)
 
     e2e = None
     if not args.no_e2e:
@@ -333,7 +391,7 @@ def run_reference(args, world, rank, local_rank):
                "last_loss": metrics["cross_entropy_loss"]}
     extra = {"reduce_ms": timer.totals.get("batch.reduce", 0.0) / max(timer.call_counts.get("batch.reduce", 1), 1) * 1e3,
              "cudnn_allow_tf32": torch.backends.cudnn.allow_tf32, "matmul_allow_tf32": torch.backends.cuda.matmul.allow_tf32}
-    return dev_ms, 0, clocks, e2e, extra
+    return dev_ms, 0, clocks, e2e, extra, sustained
 
 
 def main():
@@ -363,7 +421,11 @@ def main():
         if rank == 0:
             emit(out)
         return
-    dev_ms, launches, clocks, e2e, extra = out
+    sustained = None
+    if len(out) == 6:
+        dev_ms, launches, clocks, e2e, extra, sustained = out
+    else:
+        dev_ms, launches, clocks, e2e, extra = out
     if rank == 0:
         value = args.batch * world / (dev_ms * 1e-3)
         key = (args.model, args.reducer, args.bits if "QSGD" in args.reducer else 0)
@@ -380,7 +442,7 @@ def main():
                        "quantization_level": args.bits, "optimizer": "SGD lr 0.1 momentum 0.9 nesterov wd 5e-4",
                        "l2": "step working set (activations + 94 MB gradient + parameters) far exceeds the 126 MB L2",
                        "published_baseline": "reference logs, 2 GPUs of unnamed hardware, scaled per GPU", **extra},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "sustained": sustained, "gpu_launches": launches,
         }
         emit(line)
     if dist.is_initialized():

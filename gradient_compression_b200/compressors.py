@@ -38,7 +38,9 @@ class NoiseSource:
         return {"seed": self.seed, "rank": self.rank, "step": self.step}
 
     def load_state_dict(self, sd):
-        self.seed, self.rank, self.step = int(sd["seed"]), int(sd["rank"]), int(sd["step"])
+        # the rank stays the live worker's: a state saved by another worker must not make two workers draw the same
+        # rounding-noise stream
+        self.seed, self.step = int(sd["seed"]), int(sd["step"])
 
 
 def _container(bits):

@@ -26,9 +26,12 @@ __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<floa
 // Per-block accumulation of two per-channel sums.  Thread t owns the float4 column (t % vec) and visits
 // rows (t / vec) + k * (BN_THREADS / vec).  Requires C % 4 == 0, vec = C / 4 <= BN_THREADS and
 // BN_THREADS % vec == 0.  F(row-quad data) -> two float4 contributions.
+// acc != NULL: the block's sums are added to acc[0:C] / acc[C:2C] (doubles) with atomics instead of being written to
+// partial_out.
 template <typename F>
 __device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_begin, int64_t row_end, F f,
-                                               float* __restrict__ partial_out /* [2C] for this block */) {
+                                               float* __restrict__ partial_out /* [2C] for this block */,
+                                               double* __restrict__ acc = nullptr) {
   extern __shared__ float smem[];   // 2 * BN_THREADS * 4 floats
   const int vec = C >> 2;
   const int col = threadIdx.x % vec;
@@ -53,9 +56,35 @@ __device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_beg
     __syncthreads();
   }
   if (threadIdx.x < vec) {
-    st4(partial_out + 4 * threadIdx.x, sa[threadIdx.x]);
-    st4(partial_out + C + 4 * threadIdx.x, sb[threadIdx.x]);
+    if (acc != nullptr) {
+      const float4 a4 = sa[threadIdx.x], b4 = sb[threadIdx.x];
+      double* pa = acc + 4 * threadIdx.x;
+      double* pb = acc + C + 4 * threadIdx.x;
+      atomicAdd(pa, (double)a4.x); atomicAdd(pa + 1, (double)a4.y); atomicAdd(pa + 2, (double)a4.z); atomicAdd(pa + 3, (double)a4.w);
+      atomicAdd(pb, (double)b4.x); atomicAdd(pb + 1, (double)b4.y); atomicAdd(pb + 2, (double)b4.z); atomicAdd(pb + 3, (double)b4.w);
+    } else {
+      st4(partial_out + 4 * threadIdx.x, sa[threadIdx.x]);
+      st4(partial_out + C + 4 * threadIdx.x, sb[threadIdx.x]);
+    }
   }
+}
+
+// After block_two_sums(..., acc): the block that draws the last ticket finds every block's contribution in acc, writes
+// the totals as floats and leaves acc and the ticket zeroed for the next launch.
+__device__ __forceinline__ void finish_two_sums(int C, double* __restrict__ acc, unsigned int* __restrict__ ticket,
+                                                float* __restrict__ sums) {
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(ticket, 1u) == gridDim.x - 1u ? 1 : 0;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) {
+    sums[i] = (float)__ldcg(&acc[i]);
+    acc[i] = 0.0;
+  }
+  if (threadIdx.x == 0) *ticket = 0u;
 }
 
 // Combine the per-block partials of 32 consecutive channels (both sums) in double precision.
@@ -164,7 +193,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* 
                                                                    const float* __restrict__ y, int64_t M, int C,
                                                                    int64_t rows_per_block, const float* __restrict__ stats,
                                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                                   int relu, float* __restrict__ partials) {
+                                                                   int relu, float* __restrict__ partials, double* __restrict__ acc,
+                                                                   unsigned int* __restrict__ ticket, float* __restrict__ sums) {
   pdl_wait();
   pdl_launch_dependents();
   int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
@@ -189,7 +219,8 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* 
                    a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
                    b.x = fmaf(d.x, xh.x, b.x); b.y = fmaf(d.y, xh.y, b.y); b.z = fmaf(d.z, xh.z, b.z); b.w = fmaf(d.w, xh.w, b.w);
                  },
-                 partials + (int64_t)blockIdx.x * 2 * C);
+                 partials + (int64_t)blockIdx.x * 2 * C, acc);
+  if (acc != nullptr) finish_two_sums(C, acc, ticket, sums);
 }
 
 __global__ void bn_sums_finalize_kernel(const float* __restrict__ partials, int nparts, int C, float* __restrict__ sums) {
@@ -273,6 +304,8 @@ inline int reduce_grid(int64_t M, int C, int64_t* rows_per_block) {
   return (int)((M + *rows_per_block - 1) / *rows_per_block);
 }
 
+int64_t g_bwd_fused_atomics_limit = 200000;
+
 inline int apply_grid(int64_t nq) {
   int64_t need = (nq + BN_THREADS - 1) / BN_THREADS;
   int64_t cap = (int64_t)bn_sm_count() * 4;
@@ -319,17 +352,28 @@ int gc_cuda_bn_apply(const float* x, int64_t M, int C, const float* stats, const
 }
 
 // sums[0:C] = dbeta, sums[C:2C] = dgamma.  y: saved forward output (needed only when a residual was added).
+// fin_scratch (may be NULL): a zero-initialised buffer of 256 + 2 * C * 8 bytes that every launch leaves zeroed (the one the
+// GEMMs' statistics use).  When given and the grid is small against the tensor (few atomics per block) the blocks add their
+// sums there with atomics and the last one writes `sums`: one launch instead of two.
 int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
-                          const float* gamma, const float* beta, int relu, void* scratch, float* sums, void* cs) {
+                          const float* gamma, const float* beta, int relu, void* scratch, float* sums, void* fin_scratch, void* cs) {
   if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
   int64_t rpb;
   int grid = reduce_grid(M, C, &rpb);
   size_t smem = 2 * BN_THREADS * sizeof(float4);
+  const bool fused = fin_scratch != nullptr && (int64_t)grid * 2 * C <= g_bwd_fused_atomics_limit;
+  double* acc = fused ? reinterpret_cast<double*>(static_cast<uint8_t*>(fin_scratch) + 256) : nullptr;
+  unsigned int* ticket = fused ? static_cast<unsigned int*>(fin_scratch) : nullptr;
   launch_pdl(bn_bwd_reduce_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dy, x, y, M, C, rpb, stats, gamma, beta,
-             relu, (float*)scratch);
-  launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
+             relu, (float*)scratch, acc, ticket, sums);
+  if (!fused)
+    launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
   return (int)cudaGetLastError();
 }
+
+// Above this many atomics per launch (blocks x 2C) the backward reduction keeps its separate finalize kernel: with many
+// blocks on a wide, short activation the atomics would cost more than the second launch.
+void gc_cuda_bn_bwd_fused_limit(int64_t atomics) { g_bwd_fused_atomics_limit = atomics; }
 
 int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
                          const float* gamma, const float* beta, const float* sums, int relu, float* dx, float* dres,

@@ -12,7 +12,7 @@
 //                              kernel on dY with the filter rotated by 180 degrees and its channel axes swapped.
 //                              Batch-norm statistics and bias come from the GEMM epilogue as for the 1x1 case.
 //   weight gradient            dW[Cout, R*S*Cin] += dY[P, Cout]^T * X_shifted[P, Cin] per tap = gemm_tn_tf32_kernel
-//                              whose B operand is a shifted 4-D box of 32 output positions x 32 channels.
+//                              whose B operand is a shifted 4-D box of 64 output positions x 32 channels.
 //   im2col_small_kernel        the 3-channel stem: its rows are 12 bytes apart, which no tensor map can describe,
 //                              so the 27 taps of every position are gathered into rows of 32 floats once and the
 //                              convolution becomes a plain GEMM with K = 32.
@@ -78,7 +78,7 @@ bool fwd_ok(const Shape& s) {
 bool wgrad_ok(const Shape& s) {
   int bw, bh, bn;
   if ((s.Cin & 63) || (s.Cout & 31)) return false;
-  return box_for(BK, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr;
+  return box_for(TBK, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr;
 }
 
 // A[p][k] = x[n, h + r - pad, w + s - pad, c] with k = (r * R + s) * Cin + c (zero outside the image and for
@@ -129,8 +129,9 @@ int gc_cuda_conv_fwd_supported(int N, int H, int W, int Cin, int Cout, int R, in
 
 // y[N*Ho*Wo, Cout] (=, += when accumulate) conv(x[N, H, W, Cin], w[Cout, R*R*Cin]) (+ bias[Cout]); x, w, y 16-byte aligned.
 // col_partials (may be NULL): [ceil(N*Ho*Wo / 128)][2][Cout] per-tile column sums and sums of squares of y.
+// bn_fin (may be NULL): a BnFinHost; the kernel then finishes the batch-norm statistics of y itself.
 int gc_cuda_conv_fwd(const float* x, const float* w, float* y, const float* bias, int N, int H, int W, int Cin, int Cout, int R,
-                     int stride, int pad, int accumulate, float* col_partials, int* error_flag, void* cs) {
+                     int stride, int pad, int accumulate, float* col_partials, int* error_flag, void* cs, const void* bn_fin) {
   Shape s;
   if (!make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) || !fwd_ok(s)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(w) & 15u) || (reinterpret_cast<uintptr_t>(y) & 15u))
@@ -145,16 +146,18 @@ int gc_cuda_conv_fwd(const float* x, const float* w, float* y, const float* bias
     return (int)cudaErrorInvalidValue;
   const ConvA ca = conv_a(s);
   cudaStream_t st = (cudaStream_t)cs;
+  const BnFin fin_dev = bn_fin_from_host(bn_fin);
+  const BnFin* fin = fin_dev.acc != nullptr ? &fin_dev : nullptr;
   switch (tile) {
-    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
-    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
-    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st);
+    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
+    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
+    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
     default: return (int)cudaErrorInvalidValue;
   }
 }
 
 // 1 when the weight gradient of this convolution can run on the tensor cores: Cin a multiple of 64, Cout of 32, and
-// 32 consecutive output positions form one box.
+// 64 consecutive output positions form one box.
 int gc_cuda_conv_wgrad_supported(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
   Shape s;
   return make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) && wgrad_ok(s) ? 1 : 0;
@@ -170,7 +173,7 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
     return (int)cudaErrorInvalidValue;
   const int P = N * s.Ho * s.Wo, No = R * R * Cin;
   int bw, bh, bn;
-  box_for(BK, s.Ho, s.Wo, &bw, &bh, &bn);
+  box_for(TBK, s.Ho, s.Wo, &bw, &bh, &bn);
   int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : 64);      // a tile's columns stay inside one filter tap
   if (gctc::tile_choice && Cin % gctc::tile_choice == 0) tile = gctc::tile_choice;
   CUtensorMap ma, mb, mc;

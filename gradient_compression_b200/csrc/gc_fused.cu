@@ -1003,6 +1003,14 @@ int gc_comm_status(void* ctx, uint32_t* out2, void* cs) {
   return (int)cudaStreamSynchronize((cudaStream_t)cs);
 }
 
+// Enqueue a copy of (status, detail) into pinned host memory on the given stream; does not wait.  The caller reads the
+// words after an event recorded behind the copy has completed.
+int gc_comm_status_async(void* ctx, uint32_t* pinned_out2, void* cs) {
+  CommCtx* c = (CommCtx*)ctx;
+  ArenaHeader* h = (ArenaHeader*)c->local;
+  return (int)cudaMemcpyAsync(pinned_out2, &h->status, 8, cudaMemcpyDeviceToHost, (cudaStream_t)cs);
+}
+
 int gc_comm_clear_status(void* ctx, void* cs) {
   CommCtx* c = (CommCtx*)ctx;
   ArenaHeader* h = (ArenaHeader*)c->local;

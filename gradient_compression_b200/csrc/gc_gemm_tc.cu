@@ -266,11 +266,12 @@ int launch(const float* A, const float* B, float* C, const float* bias, int M, i
 
 template <int BN>
 int launch_persistent(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, cudaStream_t st) {
+                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, cudaStream_t st,
+                      const BnFin* fin) {
   CUtensorMap ma, mb, mc;
   if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0 || make_map(&mc, C, M, N, ldc, BM) != 0)
     return (int)cudaErrorInvalidValue;
-  return launch_persistent_maps<BN>(ma, mb, mc, ConvA{}, bias, M, N, K, accumulate, col_partials, error_flag, st);
+  return launch_persistent_maps<BN>(ma, mb, mc, ConvA{}, bias, M, N, K, accumulate, col_partials, error_flag, st, fin);
 }
 
 template <int BN>
@@ -317,6 +318,9 @@ static int pick_bn(int M, int N) {
 
 int gc_cuda_gemm_tf32_m_tiles(int M) { return (M + BM - 1) / BM; }
 
+// Bytes of the zero-initialised scratch a BnFinHost points to, for outputs of up to max_channels columns.
+int64_t gc_cuda_bn_fin_scratch_bytes(int max_channels) { return 256 + (int64_t)2 * max_channels * 8; }
+
 // For measurements: kernel 0 = choose, 1 = one tile per CTA, 2 = persistent; tile width 0 = choose, else 64 / 128 / 256.
 void gc_cuda_gemm_tf32_config(int kernel, int tile_n) {
   g_kernel_choice = kernel;
@@ -328,18 +332,23 @@ void gc_cuda_gemm_tf32_config(int kernel, int tile_n) {
 // error_flag (device int, may be NULL) is set when a wait ran out.
 // col_partials (may be NULL): [m_tiles][2][N] floats receiving, per 128-row tile, the column sums and sums of
 // squares of C -- the batch-norm statistics of a 1x1 convolution's output without another pass over it.
+// bn_fin (may be NULL): a BnFinHost; the kernel then finishes the batch-norm statistics of C itself (mean and
+// 1 / sqrt(var + eps) into stats[2N], running statistics updated) instead of emitting col_partials.  Persistent kernel only.
 int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, void* cs) {
+                      int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, void* cs,
+                      const void* bn_fin) {
   if (!gc_cuda_gemm_tf32_supported(A, B, M, N, K, lda, ldb)) return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)cs;
-  bool persistent = (g_kernel_choice != 1 || accumulate) && N > 16 && tma_store_ok(C, ldc);
-  if (accumulate && !persistent) return (int)cudaErrorInvalidValue;
+  const BnFin fin_dev = bn_fin_from_host(bn_fin);
+  const BnFin* fin = fin_dev.acc != nullptr ? &fin_dev : nullptr;
+  bool persistent = (g_kernel_choice != 1 || accumulate || fin != nullptr) && N > 16 && tma_store_ok(C, ldc);
+  if ((accumulate || fin != nullptr) && !persistent) return (int)cudaErrorInvalidValue;
   if (persistent) {
     int bn = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, N, K);
     switch (bn) {
-      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
-      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
-      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st);
+      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
+      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
+      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
       default: return (int)cudaErrorInvalidValue;
     }
   }
@@ -351,10 +360,14 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
   }
 }
 
+// For measurements: how the producer warps issue their TMA loads (bit 0: prefetch the tensor maps; bit 1: spread the
+// loads of a stage over several lanes).
+void gc_cuda_tc_tma_mode(int mode) { gctc::tma_mode = mode; }
+
 // For measurements: CTAs per SM the split contraction aims at, and the fewest k-blocks (of 32 rows) a split may get.
 void gc_cuda_gemm_tn_config(int ctas_per_sm, int min_kblocks) {
   gctc::tn_ctas_per_sm = ctas_per_sm > 0 ? ctas_per_sm : 1;
-  gctc::tn_min_kblocks = min_kblocks > 0 ? min_kblocks : 8;
+  gctc::tn_min_kblocks = min_kblocks > 0 ? min_kblocks : 4;
 }
 
 // 1 when C[Mo, No] += A[P, Mo]^T B[P, No] can run on the tensor cores: Mo and No multiples of 32, 16-byte aligned

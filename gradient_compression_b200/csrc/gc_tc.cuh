@@ -22,11 +22,12 @@
 
 // Measurement knobs shared by every translation unit of the library (set through gc_cuda_gemm_tf32_config /
 // gc_cuda_gemm_tn_config): forced tile width (0 = choose), CTAs per SM the split contraction aims at, fewest
-// k-blocks (of 32 rows) a split may get.
+// k-blocks (of 64 rows) a split may get.
 namespace gctc {
 inline int tile_choice = 0;
 inline int tn_ctas_per_sm = 1;
-inline int tn_min_kblocks = 8;
+inline int tn_min_kblocks = 4;
+inline int tma_mode = 1;   // bit 0: prefetch the tensor maps at kernel start; bit 2: epilogue warps sleep between polls while a tile is being accumulated
 }  // namespace gctc
 
 namespace {
@@ -34,7 +35,17 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 32;                       // 32 fp32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;                    // tf32
-constexpr int GEMM_THREADS = 192;
+constexpr int TBK = 64;                      // contraction rows per stage of the split-K (MN-major) kernel: 8 KB TMA boxes
+constexpr int GEMM_THREADS = 192;           // one-tile-per-CTA kernel: producer warp, MMA warp, four epilogue warps
+// The persistent and the split-K kernels have TWO producer warps that take alternate stages of the ring.  One thread
+// needs about 500 cycles per stage (a try_wait that succeeds at once ~170, arrive.expect_tx ~55, the first TMA
+// instruction ~280, each further one ~130: measured on a B200 with clock64), which is 32 bytes per cycle for a 16 KB
+// stage -- half of what the TMA unit of an SM sustains (about 62 B/cycle with 16 KB boxes).  Two issuing threads in
+// different warps bring the ring up to the unit's rate.
+constexpr int PRODUCER_WARPS = 2;
+constexpr int MMA_WARP = PRODUCER_WARPS;     // warp that allocates TMEM and issues tcgen05.mma
+constexpr int FIRST_EPI_WARP = PRODUCER_WARPS + 1;
+constexpr int TN_THREADS = 32 * FIRST_EPI_WARP + 128;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // a wait gives up after two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -71,11 +82,44 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same wait for warps that have nothing to do for a long time (the epilogue warps during a tile's main loop): between
+// polls they sleep, so that their polling does not take issue slots from the single threads that feed the TMA unit and
+// the tensor core on the same SM sub-partitions.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned sleep_ns) {
+  uint32_t addr = smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
+    if ((it & 15u) == 15u) {
+      if (*abort_flag) return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > WAIT_LIMIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
@@ -98,6 +142,47 @@ struct ConvA {
   int w_out;       // output width
   int stride, pad;
 };
+
+// Batch-norm statistics finished inside the GEMM that produces the activation: every CTA keeps per-column sums and sums
+// of squares of its tiles, adds them to `acc` ([2][N] doubles, zero on entry) with atomics when it is done, and the
+// epilogue group that draws the last ticket turns the totals into mean / 1 / sqrt(var + eps) (`stats`, [2N] floats),
+// updates the running statistics and leaves `acc` and `ticket` zeroed for the next launch.  Needs every CTA to stay on
+// one column tile (the launcher makes the grid a multiple of the number of column tiles).  acc == NULL: off.
+struct BnFin {
+  double* acc;
+  unsigned int* ticket;
+  float* stats;
+  float* running_mean;     // may be NULL
+  float* running_var;
+  float momentum, eps;
+};
+
+// What the host passes to ask for it: `scratch` holds the ticket (first 256 bytes) and the totals (2 * N doubles), is
+// zeroed once when allocated (gc_cuda_bn_fin_scratch_bytes) and is left zeroed by every launch that uses it.
+struct BnFinHost {
+  void* scratch;
+  float* stats;
+  float* running_mean;
+  float* running_var;
+  float momentum, eps;
+};
+
+inline BnFin bn_fin_from_host(const void* host_args) {
+  BnFin f{};
+  if (host_args != nullptr) {
+    const BnFinHost* h = static_cast<const BnFinHost*>(host_args);
+    if (h->scratch != nullptr) {
+      f.ticket = static_cast<unsigned int*>(h->scratch);
+      f.acc = reinterpret_cast<double*>(static_cast<uint8_t*>(h->scratch) + 256);
+      f.stats = h->stats;
+      f.running_mean = h->running_mean;
+      f.running_var = h->running_var;
+      f.momentum = h->momentum;
+      f.eps = h->eps;
+    }
+  }
+  return f;
+}
 
 // TMA coordinates {c, w, h, n} of the box that holds output positions p0 .. of filter tap `tap`, channel block `cb`.
 __device__ __forceinline__ void conv_box(const ConvA& ca, int64_t p0, int tap, int cb, int (&co)[4]) {
@@ -190,14 +275,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 
 constexpr int EPI_GROUPS = 2;
-constexpr int PERSISTENT_THREADS = 64 + 128 * EPI_GROUPS;
+constexpr int PERSISTENT_THREADS = 32 * FIRST_EPI_WARP + 128 * EPI_GROUPS;
 
 template <int BN>
 __global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                             const __grid_constant__ CUtensorMap tma_c, const ConvA ca, const float* __restrict__ bias, int M, int N, int K,
                             int tiles_m, int tiles_n, int accumulate, float* __restrict__ col_partials,
-                            int* __restrict__ error_flag) {
+                            int* __restrict__ error_flag, int tma_mode, const BnFin fin) {
   using S = PSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -225,7 +310,7 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -238,30 +323,48 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
   gc::pdl_wait();
   gc::pdl_launch_dependents();
 
-  if (warp == 0) {
+  if (warp < PRODUCER_WARPS) {
+    // producer warp p fills the stages it == p (mod PRODUCER_WARPS) of the ring
     if (lane == 0) {
-      uint32_t it = 0;                                        // k-blocks issued so far, over all tiles
+      if (tma_mode & 1) { tma_prefetch_map(&tma_a); tma_prefetch_map(&tma_b); }
+      uint32_t it = 0;                                        // k-blocks issued so far by all producers, over all tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+        int box[4] = {0, 0, 0, 0};
+        if (ca.taps != 0) conv_box(ca, (int64_t)m0, 0, 0, box);  // pixel of the tile's first position at tap (0, 0)
+        // CTAs that run side by side start their contraction at different k-blocks (the sum does not care about the
+        // order): otherwise all of them ask the same few L2 slices for the same tile of the shared operand at once
+        int kk = (tma_mode & 8) ? (int)((blockIdx.x * 5u) % (unsigned)num_k) : 0;
+        int cb = 0, fr = 0, fs = 0;                             // k-block = (filter tap (fr, fs), 32-channel block cb)
+        if (ca.taps != 0) {
+          const int tap = kk / ca.cblocks;
+          cb = kk - tap * ca.cblocks;
+          fr = tap / ca.fs;
+          fs = tap - fr * ca.fs;
+        }
         for (int k = 0; k < num_k; ++k, ++it) {
-          const int s = (int)(it % S::STAGES);
-          const uint32_t phase = (it / S::STAGES) & 1u;
-          if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) { ok = false; break; }
-          mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
-          if (ca.taps == 0) {
-            tma_load_2d(a_tiles + s * S::A_BYTES, &tma_a, k * BK, m0, &full[s]);
-          } else {                                              // k-block = (filter tap, 32-channel block)
-            int co[4];
-            const int tap = k / ca.cblocks;
-            conv_box(ca, (int64_t)m0, tap, k - tap * ca.cblocks, co);
-            tma_load_4d(a_tiles + s * S::A_BYTES, &tma_a, co[0], co[1], co[2], co[3], &full[s]);
+          if ((int)(it % PRODUCER_WARPS) == warp) {
+            const int s = (int)(it % S::STAGES);
+            const uint32_t phase = (it / S::STAGES) & 1u;
+            if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) { ok = false; break; }
+            mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
+            if (ca.taps == 0)
+              tma_load_2d(a_tiles + s * S::A_BYTES, &tma_a, kk * BK, m0, &full[s]);
+            else
+              tma_load_4d(a_tiles + s * S::A_BYTES, &tma_a, cb * 32, box[1] + fs, box[2] + fr, box[3], &full[s]);
+            tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, kk * BK, n0, &full[s]);
           }
-          tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, k * BK, n0, &full[s]);
+          if (++kk == num_k) {
+            kk = 0; cb = 0; fr = 0; fs = 0;
+          } else if (++cb == ca.cblocks) {                      // (never true for a plain matrix: cblocks == 0)
+            cb = 0;
+            if (++fs == ca.fs) { fs = 0; ++fr; }
+          }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
       uint32_t it = 0, lt = 0;                                // k-blocks consumed, tiles started
@@ -290,7 +393,7 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
     // Two epilogue groups of four warps (TMEM lane quarters warp & 3); group g drains the 32-column slabs
     // g, g + 2, ... of every tile through its own half of the staging ring, with its own named barrier and its
     // own store-issuing thread, so the groups never wait for each other.
-    const int ew = warp - 2;
+    const int ew = warp - FIRST_EPI_WARP;
     const int grp = ew >> 2;
     const int lg = warp & 3;
     const int r = lg * 32 + lane;                              // row of the tile this thread owns
@@ -301,16 +404,20 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
     uint8_t* my_staging = staging + grp * (RING * S::SLAB_BYTES);
     float* my_colsum = colsum;                                 // [4 row quarters][BN][2]; a group only touches its slabs' columns
     uint32_t lt = 0, sc = 0;                                   // tiles drained, slabs staged by this group
+    const bool fin_on = fin.acc != nullptr;
+    const bool want_sums = col_partials != nullptr || fin_on;
+    float run_a = 0.f, run_b = 0.f;                            // fin_on: this thread's column, summed over the CTA's tiles
+    bool drained_all = true;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
       const int mi = t / tiles_n;
       const int m0 = mi * BM, n0 = (t % tiles_n) * BN;
       const uint32_t buf = lt & 1u, aphase = (lt >> 1) & 1u;
-      const bool got = mbar_wait(&acc_full[buf], aphase, &abort_flag);
+      const bool got = (tma_mode & 4) ? mbar_wait_idle(&acc_full[buf], aphase, &abort_flag, 128u) : mbar_wait(&acc_full[buf], aphase, &abort_flag);
       // one thread decides for the group: the TMEM loads are warp-collective and the named barriers below
       // involve all four warps, so either every one of them drains this tile or none does
       if (issuer) epi_go[grp] = (got && abort_flag == 0) ? 1 : 0;
       group_bar(grp);
-      if (!epi_go[grp]) break;
+      if (!epi_go[grp]) { drained_all = false; break; }
       tc_fence_after();
       const uint32_t lane_base = tmem_base + ((uint32_t)(lg * 32) << 16) + buf * (uint32_t)BN;
       const bool full_rows = m0 + BM <= M;
@@ -354,7 +461,7 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");              // one group per slab, empty ones included
         }
-        if (col_partials != nullptr) {
+        if (want_sums) {
           // sum and sum of squares of 32 rows of one column, read back from the staged slab (a row of a slab is
           // one 128-byte line: conflict free); four independent chains each
           const int col = te & 31, quarter = te >> 5;
@@ -384,25 +491,67 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
           my_colsum[(quarter * BN + sl * 32 + col) * 2 + 1] = (q0 + q1) + (q2 + q3);
         }
       }
-      if (col_partials != nullptr) {
+      if (want_sums) {
         group_bar(grp);
+        static_assert((SLABS / EPI_GROUPS) * 32 <= 128, "one column per thread and tile");
         for (int idx = te; idx < (SLABS / EPI_GROUPS) * 32; idx += 128) {       // the columns of this group's slabs
           const int c = (grp + EPI_GROUPS * (idx >> 5)) * 32 + (idx & 31);
           const int gc = n0 + c;
           if (gc < N) {
             float a = (my_colsum[c * 2] + my_colsum[(BN + c) * 2]) + (my_colsum[(2 * BN + c) * 2] + my_colsum[(3 * BN + c) * 2]);
             float b = (my_colsum[c * 2 + 1] + my_colsum[(BN + c) * 2 + 1]) + (my_colsum[(2 * BN + c) * 2 + 1] + my_colsum[(3 * BN + c) * 2 + 1]);
-            col_partials[((int64_t)mi * 2) * N + gc] = a;
-            col_partials[((int64_t)mi * 2 + 1) * N + gc] = b;
+            if (fin_on) {
+              run_a += a;
+              run_b += b;
+            } else {
+              col_partials[((int64_t)mi * 2) * N + gc] = a;
+              col_partials[((int64_t)mi * 2 + 1) * N + gc] = b;
+            }
           }
         }
+      }
+    }
+    if (fin_on && drained_all) {
+      // this CTA's column sums -> the global totals; the group that draws the last of gridDim.x * EPI_GROUPS tickets
+      // finds every contribution in place and finishes the statistics
+      if (te < (SLABS / EPI_GROUPS) * 32) {
+        const int c = (grp + EPI_GROUPS * (te >> 5)) * 32 + (te & 31);
+        const int gc = (int)(blockIdx.x % (unsigned)tiles_n) * BN + c;
+        if (gc < N) {
+          atomicAdd(&fin.acc[gc], (double)run_a);
+          atomicAdd(&fin.acc[N + gc], (double)run_b);
+        }
+      }
+      __threadfence();
+      group_bar(grp);
+      if (issuer) epi_go[grp] = atomicAdd(fin.ticket, 1u) == gridDim.x * (unsigned)EPI_GROUPS - 1u ? 2 : 1;
+      group_bar(grp);
+      if (epi_go[grp] == 2) {
+        __threadfence();
+        const double inv_m = 1.0 / (double)M;
+        for (int c = te; c < N; c += 128) {
+          const double sum = __ldcg(&fin.acc[c]), sq = __ldcg(&fin.acc[N + c]);
+          const double mean = sum * inv_m;
+          double var = sq * inv_m - mean * mean;
+          if (var < 0.0) var = 0.0;
+          fin.stats[c] = (float)mean;
+          fin.stats[N + c] = (float)(1.0 / sqrt(var + (double)fin.eps));
+          if (fin.running_mean != nullptr) {
+            const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+            fin.running_mean[c] = (1.0f - fin.momentum) * fin.running_mean[c] + fin.momentum * (float)mean;
+            fin.running_var[c] = (1.0f - fin.momentum) * fin.running_var[c] + fin.momentum * (float)unbiased;
+          }
+          fin.acc[c] = 0.0;
+          fin.acc[N + c] = 0.0;
+        }
+        if (issuer) *fin.ticket = 0u;
       }
     }
     if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory outlives the stores
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
@@ -422,9 +571,10 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
 // with TMA reduce stores, so C must hold the value to add to (zeros for a plain product).
 template <int BN>
 struct TnSmem {
-  static constexpr int STAGES = (BN <= 64) ? 6 : ((BN <= 128) ? 5 : 3);
-  static constexpr int A_BYTES = BM * BK * 4;
-  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGES = (BN <= 64) ? 4 : ((BN <= 128) ? 3 : 2);
+  static constexpr int CHUNK_BYTES = TBK * 128;             // one TMA box: 32 floats of the output dimension x TBK rows
+  static constexpr int A_BYTES = BM * TBK * 4;
+  static constexpr int B_BYTES = BN * TBK * 4;
   static constexpr int RING_BYTES = STAGES * (A_BYTES + B_BYTES);
   static constexpr int NSLAB = 2;
   static constexpr int SLAB_BYTES = BM * 128;
@@ -438,7 +588,7 @@ struct TnSmem {
 __device__ __forceinline__ uint64_t make_smem_desc_mn(const void* tile) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);      // start address
-  d |= (uint64_t)(4096 >> 4) << 16;                      // leading byte offset: next 32-float chunk of the M / N dimension
+  d |= (uint64_t)((TBK * 128) >> 4) << 16;               // leading byte offset: next 32-float chunk of the M / N dimension
   d |= (uint64_t)(512 >> 4) << 32;                       // stride byte offset: next group of 4 K rows
   d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
   d |= (uint64_t)1 << 61;                                // layout type: SWIZZLE_128B_BASE32B
@@ -450,10 +600,10 @@ __host__ __device__ constexpr uint32_t make_idesc_mn(int n) {
 }
 
 template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(TN_THREADS, 1)
 gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ CUtensorMap tma_c, const ConvA ca, int P, int Mo, int No, int tiles_n, int splits,
-                    int kblocks_per_split, int* __restrict__ error_flag) {
+                    int kblocks_per_split, int* __restrict__ error_flag, int tma_mode) {
   using S = TnSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -471,7 +621,7 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const int split = blockIdx.x % splits;
   const int tile = blockIdx.x / splits;
   const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
-  const int total_k = (P + BK - 1) / BK;
+  const int total_k = (P + TBK - 1) / TBK;
   const int k_begin = split * kblocks_per_split;
   const int k_end = k_begin + kblocks_per_split < total_k ? k_begin + kblocks_per_split : total_k;
   const int num_k = k_end > k_begin ? k_end - k_begin : 0;
@@ -484,7 +634,7 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -494,36 +644,46 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (num_k > 0) {
-    if (warp == 0) {
+    if (warp < PRODUCER_WARPS) {
+      // a stage is BM / 32 + BN / 32 boxes of 32 floats x TBK rows; producer warp p fills the stages k == p (mod PRODUCER_WARPS)
       if (lane == 0) {
-        for (int k = 0; k < num_k; ++k) {
+        if (tma_mode & 1) { tma_prefetch_map(&tma_a); tma_prefetch_map(&tma_b); }
+        int co[4] = {0, 0, 0, 0}, c0 = 0, tap = 0;
+        if (ca.taps != 0) {
+          // weight gradient of an R x S convolution: the columns n0 .. n0 + BN of dW[Cout, taps * Cin] belong to one
+          // filter tap; the TBK output positions of a k-block read that tap's shifted pixels
+          const int cin = ca.cblocks * 32;
+          tap = n0 / cin;
+          c0 = n0 - tap * cin;
+        }
+        // boxes that lie wholly beyond the matrix (Mo < 128: the 64-channel layers; No < BN) are not loaded at all: the
+        // rows and columns of the accumulator they feed are never stored
+        int a_boxes = (Mo - m0 + 31) / 32, b_boxes = ((ca.taps == 0 ? No - n0 : BN) + 31) / 32;
+        a_boxes = a_boxes < BM / 32 ? a_boxes : BM / 32;
+        b_boxes = b_boxes < BN / 32 ? b_boxes : BN / 32;
+        const uint32_t stage_tx = (uint32_t)((a_boxes + b_boxes) * S::CHUNK_BYTES);
+        for (int k = warp; k < num_k; k += PRODUCER_WARPS) {
           const int s = k % S::STAGES;
           const uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
           if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) break;
-          mbar_expect_tx(&full[s], (uint32_t)(S::A_BYTES + S::B_BYTES));
-          // one 4 KB box (32 floats x 32 positions) per 32-float chunk of the output dimensions
+          mbar_expect_tx(&full[s], stage_tx);
+          const int row0 = (k_begin + k) * TBK;
 #pragma unroll
           for (int c = 0; c < BM / 32; ++c)
-            tma_load_2d(a_tiles + s * S::A_BYTES + c * 4096, &tma_a, m0 + c * 32, (k_begin + k) * BK, &full[s]);
+            if (c < a_boxes) tma_load_2d(a_tiles + s * S::A_BYTES + c * S::CHUNK_BYTES, &tma_a, m0 + c * 32, row0, &full[s]);
           if (ca.taps == 0) {
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
-              tma_load_2d(b_tiles + s * S::B_BYTES + c * 4096, &tma_b, n0 + c * 32, (k_begin + k) * BK, &full[s]);
+              if (c < b_boxes) tma_load_2d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, n0 + c * 32, row0, &full[s]);
           } else {
-            // weight gradient of an R x S convolution: the columns n0 .. n0 + BN of dW[Cout, taps * Cin] belong to one
-            // filter tap; the 32 output positions of this k-block read that tap's shifted pixels
-            const int cin = ca.cblocks * 32;
-            const int tap = n0 / cin;
-            int co[4];
-            conv_box(ca, (int64_t)(k_begin + k) * BK, tap, 0, co);
-            const int c0 = n0 - tap * cin;
+            conv_box(ca, (int64_t)row0, tap, 0, co);
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
-              tma_load_4d(b_tiles + s * S::B_BYTES + c * 4096, &tma_b, c0 + c * 32, co[1], co[2], co[3], &full[s]);
+              tma_load_4d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, c0 + c * 32, co[1], co[2], co[3], &full[s]);
           }
         }
       }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
       if (lane == 0) {
         constexpr uint32_t idesc = make_idesc_mn(BN);
         bool ok = true;
@@ -535,7 +695,7 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const uint64_t adesc = make_smem_desc_mn(a_tiles + s * S::A_BYTES);
           const uint64_t bdesc = make_smem_desc_mn(b_tiles + s * S::B_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)     // 8 positions = 8 rows of 128 bytes = 1024 bytes = 64 address units
+          for (int kk = 0; kk < TBK / UMMA_K; ++kk)    // 8 positions = 8 rows of 128 bytes = 1024 bytes = 64 address units
             umma_tf32(tmem_base, adesc + (uint64_t)(kk * 64), bdesc + (uint64_t)(kk * 64), idesc, (k | kk) != 0 ? 1u : 0u);
           umma_commit(&empty[s]);
         }
@@ -544,9 +704,9 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     } else {
       const int lg = warp & 3;
       const int r = lg * 32 + lane;
-      const int te = (warp - 2) * 32 + lane;
+      const int te = (warp - FIRST_EPI_WARP) * 32 + lane;
       const bool issuer = te == 0;
-      const bool got = mbar_wait(acc_ready, 0u, &abort_flag);
+      const bool got = (tma_mode & 4) ? mbar_wait_idle(acc_ready, 0u, &abort_flag, 128u) : mbar_wait(acc_ready, 0u, &abort_flag);
       if (issuer) epi_go = (got && abort_flag == 0) ? 1 : 0;
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (epi_go) {
@@ -584,7 +744,7 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
@@ -642,7 +802,7 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
   if (fn == nullptr) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)P};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)BK};
+  cuuint32_t box[2] = {32, (cuuint32_t)TBK};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -654,7 +814,8 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
 // Launch the persistent kernel on ready-made tensor maps (ca.taps == 0: ma is a 2-D map of A[M, K]).
 template <int BN>
 int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const ConvA& ca, const float* bias,
-                           int M, int N, int K, int accumulate, float* col_partials, int* error_flag, cudaStream_t st) {
+                           int M, int N, int K, int accumulate, float* col_partials, int* error_flag, cudaStream_t st,
+                           const BnFin* fin = nullptr) {
   using S = PSmem<BN>;
   static bool configured = false;
   if (!configured) {
@@ -665,8 +826,14 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
   int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
   int64_t total = (int64_t)tiles_m * tiles_n;
   int64_t grid = total < sm_count() ? total : sm_count();
+  BnFin f{};
+  if (fin != nullptr && fin->acc != nullptr) {
+    if (col_partials != nullptr || tiles_n > grid) return (int)cudaErrorInvalidValue;
+    grid = grid / tiles_n * tiles_n;             // every CTA stays on one column tile
+    f = *fin;
+  }
   gc::launch_pdl(gemm_tf32_persistent_kernel<BN>, dim3((unsigned)grid), dim3(PERSISTENT_THREADS), (size_t)S::TOTAL, st, ma, mb, mc, ca,
-                 bias, M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag);
+                 bias, M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag, gctc::tma_mode, f);
   return (int)cudaGetLastError();
 }
 
@@ -685,14 +852,14 @@ int launch_tn_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
   }
   int tiles_m = (Mo + BM - 1) / BM, tiles_n = (No + BN - 1) / BN;
   int tiles = tiles_m * tiles_n;
-  int total_k = (P + BK - 1) / BK;
+  int total_k = (P + TBK - 1) / TBK;
   int splits = (gctc::tn_ctas_per_sm * sm_count() + tiles - 1) / tiles;
   if (splits > (total_k + gctc::tn_min_kblocks - 1) / gctc::tn_min_kblocks) splits = (total_k + gctc::tn_min_kblocks - 1) / gctc::tn_min_kblocks;
   if (splits < 1) splits = 1;
   int per = (total_k + splits - 1) / splits;
   splits = (total_k + per - 1) / per;
-  gemm_tn_tf32_kernel<BN><<<(unsigned)(tiles * splits), GEMM_THREADS, S::TOTAL, st>>>(ma, mb, mc, ca, P, Mo, No, tiles_n, splits, per,
-                                                                                     error_flag);
+  gemm_tn_tf32_kernel<BN><<<(unsigned)(tiles * splits), TN_THREADS, S::TOTAL, st>>>(ma, mb, mc, ca, P, Mo, No, tiles_n, splits, per,
+                                                                                     error_flag, gctc::tma_mode);
   return (int)cudaGetLastError();
 }
 

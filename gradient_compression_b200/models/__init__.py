@@ -3,7 +3,6 @@
 model_dispatcher.py:58-64)."""
 from .densenet import DenseNet, DenseNet121, DenseNet161, DenseNet169, DenseNet201, densenet_cifar
 from .dpn import DPN, DPN26, DPN92
-from .layers import set_layer_impl
 from .preact_resnet import (PreActResNet, PreActResNet18, PreActResNet34, PreActResNet50, PreActResNet101,
                             PreActResNet152)
 from .resnet import ResNet, ResNet18, ResNet34, ResNet50, ResNet101, ResNet152

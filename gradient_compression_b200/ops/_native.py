@@ -23,6 +23,14 @@ class NativeError(RuntimeError):
     pass
 
 
+class BnFinArgs(ctypes.Structure):
+    """Host-side argument block of the GEMM / convolution kernels that finish batch-norm statistics themselves
+    (``BnFinHost`` in ``csrc/gc_tc.cuh``)."""
+
+    _fields_ = [("scratch", ctypes.c_void_p), ("stats", ctypes.c_void_p), ("running_mean", ctypes.c_void_p),
+                ("running_var", ctypes.c_void_p), ("momentum", ctypes.c_float), ("eps", ctypes.c_float)]
+
+
 def _declare(lib, name, restype, argtypes):
     fn = getattr(lib, name)
     fn.restype = restype
@@ -112,7 +120,8 @@ def cuda():
         _declare(lib, "gc_cuda_bn_supported", c_int, [c_i64, c_int])
         _declare(lib, "gc_cuda_bn_stats", c_int, [P, c_i64, c_int, P, P, P, P, c_float, c_float, P])
         _declare(lib, "gc_cuda_bn_apply", c_int, [P, c_i64, c_int, P, P, P, P, c_int, P, P])
-        _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_fused_limit", None, [c_i64])
         _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
         _declare(lib, "gc_cuda_psgd_max_rank", c_int, [])
         _declare(lib, "gc_cuda_psgd_p", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, c_i64, P])
@@ -125,14 +134,16 @@ def cuda():
         _declare(lib, "gc_cuda_topk_select", c_int, [P, P, P, c_int, c_i64, P, P, P, P])
         _declare(lib, "gc_cuda_batched_transpose", c_int, [P, c_int, c_i64, P])
         _declare(lib, "gc_cuda_gemm_tf32_supported", c_int, [P, P, c_int, c_int, c_int, c_i64, c_i64])
-        _declare(lib, "gc_cuda_gemm_tf32", c_int, [P, P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, c_int, P, P, P])
+        _declare(lib, "gc_cuda_gemm_tf32", c_int, [P, P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, c_int, P, P, P, P])
+        _declare(lib, "gc_cuda_bn_fin_scratch_bytes", c_i64, [c_int])
         _declare(lib, "gc_cuda_gemm_tf32_m_tiles", c_int, [c_int])
         _declare(lib, "gc_cuda_gemm_tn_config", None, [c_int, c_int])
         _declare(lib, "gc_cuda_gemm_tn_tf32_supported", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64])
         _declare(lib, "gc_cuda_gemm_tn_tf32", c_int, [P, P, P, c_int, c_int, c_int, c_i64, c_i64, c_i64, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_config", None, [c_int, c_int])
+        _declare(lib, "gc_cuda_tc_tma_mode", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
-        _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P])
+        _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P, P])
         _declare(lib, "gc_cuda_conv_wgrad_supported", c_int, [c_int] * 8)
         _declare(lib, "gc_cuda_conv_wgrad", c_int, [P, P, P] + [c_int] * 8 + [P, P])
         _declare(lib, "gc_cuda_im2col_small", c_int, [P, P] + [c_int] * 7 + [P, P, c_int, P])
@@ -158,6 +169,7 @@ def cuda():
         _declare(lib, "gc_comm_arena_bytes", c_i64, [P])
         _declare(lib, "gc_comm_set_step_from_device", None, [P, c_int])
         _declare(lib, "gc_comm_status", c_int, [P, P, P])
+        _declare(lib, "gc_comm_status_async", c_int, [P, P, P])
         _declare(lib, "gc_comm_clear_status", c_int, [P, P])
         _declare(lib, "gc_comm_destroy", c_int, [P])
         _declare(lib, "gc_fused_qsgd", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_u64, c_u32, c_int, c_int, P])

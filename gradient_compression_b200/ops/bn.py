@@ -7,6 +7,7 @@ kernels of ``csrc/gc_bn.cu`` on CUDA and with the equivalent torch ops on CPU.  
 """
 from __future__ import annotations
 
+import os
 import weakref
 
 import torch
@@ -80,6 +81,7 @@ def take_owned_grad(t):
     return r is not None and r() is t
 
 _scratch = {}
+FUSED_BWD_FINALIZE = os.environ.get("GCB200_BN_FUSED_BWD_FINALIZE", "0") == "1"
 
 
 def _scratch_for(device, channels):
@@ -90,6 +92,15 @@ def _scratch_for(device, channels):
         cur = torch.empty(max(need, nat.cuda().gc_cuda_bn_scratch_bytes(2048)), dtype=torch.uint8, device=device)
         _scratch[key] = cur
     return cur
+
+
+def _fin_ptr(device, channels):
+    """Scratch that lets the backward reduction finish its sums inside its own launch (None: separate finalize)."""
+    from . import gemm
+
+    if not FUSED_BWD_FINALIZE or channels > gemm.FIN_MAX_CHANNELS:
+        return None
+    return gemm.fin_scratch(device).data_ptr()
 
 
 def _cl(t):
@@ -143,7 +154,7 @@ class _FusedBNAct(torch.autograd.Function):
         with torch.cuda.device(x.device):
             nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), x.data_ptr(), nat.ptr(y), m, c, stats.data_ptr(),
                                                 weight.data_ptr(), bias.data_ptr(), int(ctx.relu),
-                                                _scratch_for(x.device, c).data_ptr(), sums.data_ptr(), st),
+                                                _scratch_for(x.device, c).data_ptr(), sums.data_ptr(), _fin_ptr(x.device, c), st),
                       "bn_bwd_reduce")
             nat.count_launch()
             nat.check(lib.gc_cuda_bn_bwd_apply(dy.data_ptr(), x.data_ptr(), nat.ptr(y), m, c, stats.data_ptr(),

@@ -30,7 +30,7 @@ import torch
 
 from . import _native as nat
 from . import gemm
-from .bn import _cl, _scratch_for, bn_act, count_batch, own_grad, take_owned_grad
+from .bn import _cl, _fin_ptr, _scratch_for, bn_act, count_batch, own_grad, take_owned_grad
 
 # GCB200_TC_CONV=0 (or ``ENABLED = False``) keeps every convolution on cuDNN.
 ENABLED = os.environ.get("GCB200_TC_CONV", "1") == "1"
@@ -43,6 +43,9 @@ WGRAD_ENABLED = os.environ.get("GCB200_TC_WGRAD", "1") == "1"
 
 # Convolutions with fewer output positions (N*Ho*Wo) than this stay on cuDNN.
 MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "0"))
+
+# Batch-norm statistics finished inside the producing kernel (off: per-tile partial sums + a separate finalize kernel).
+FUSED_FINALIZE = os.environ.get("GCB200_BN_FUSED_FINALIZE", "0") == "1"
 
 # Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem".
 PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem").split(","))
@@ -184,10 +187,11 @@ def _err(device):
     return gemm._error_flag(device).data_ptr()
 
 
-def conv_forward(x, w, bias=None, stride=1, pad=1, col_partials=None, out=None, accumulate=False):
+def conv_forward(x, w, bias=None, stride=1, pad=1, col_partials=None, out=None, accumulate=False, bn_fin=None):
     """``conv2d(x, w, bias, stride, pad)`` of a channels-last activation on the implicit-GEMM kernel; ``w`` is the
     filter in channels-last memory order ``(Cout, Cin, R, R)`` or already a matrix ``[Cout, R*R*Cin]`` together with
-    ``x`` of ``Cin`` channels.  ``col_partials`` ([tiles, 2, Cout]) receives per-tile column sums / sums of squares."""
+    ``x`` of ``Cin`` channels.  ``col_partials`` ([tiles, 2, Cout]) receives per-tile column sums / sums of squares; ``bn_fin`` (``gemm.bn_fin_args``)
+    makes the kernel finish the batch-norm statistics itself instead."""
     n, cin, h, wd = x.shape
     w2 = _w2d(w) if w.dim() == 4 else w
     cout = w2.shape[0]
@@ -199,7 +203,7 @@ def conv_forward(x, w, bias=None, stride=1, pad=1, col_partials=None, out=None, 
     with torch.cuda.device(x.device):
         nat.check(nat.cuda().gc_cuda_conv_fwd(x.data_ptr(), w2.data_ptr(), out.data_ptr(), nat.ptr(bias), n, h, wd, cin, cout, r,
                                               stride, pad, int(bool(accumulate)), nat.ptr(col_partials), _err(x.device),
-                                              nat.stream_ptr()), "conv_fwd")
+                                              nat.stream_ptr(), bn_fin[0] if bn_fin is not None else None), "conv_fwd")
     return out
 
 
@@ -233,23 +237,29 @@ class _ConvBNAct(torch.autograd.Function):
         stats = torch.empty(2 * cout, dtype=torch.float32, device=x.device)
         gathered = None
         with torch.cuda.device(x.device):
-            tiles = gemm.m_tiles(m)
-            partials = torch.empty(tiles, 2, cout, dtype=torch.float32, device=x.device) if training else None
+            # training: the kernel that writes yconv also finishes its batch statistics (mean, rstd, running stats)
+            fin = partials = None
+            if training:
+                if FUSED_FINALIZE and cout <= gemm.FIN_MAX_CHANNELS and cout > 16:
+                    fin = gemm.bn_fin_args(x.device, stats, running_mean, running_var, momentum, eps)
+                else:
+                    tiles = gemm.m_tiles(m)
+                    partials = torch.empty(tiles, 2, cout, dtype=torch.float32, device=x.device)
             if mode == "gemm":
-                gemm.gemm_tf32(_as_2d(x), w.reshape(cout, cin), bias=cbias, out=_as_2d(yconv), col_partials=partials)
+                gemm.gemm_tf32(_as_2d(x), w.reshape(cout, cin), bias=cbias, out=_as_2d(yconv), col_partials=partials, bn_fin=fin)
             elif mode == "conv":
-                conv_forward(x, w, cbias, stride, pad, col_partials=partials, out=yconv)
+                conv_forward(x, w, cbias, stride, pad, col_partials=partials, out=yconv, bn_fin=fin)
             else:
                 gathered = torch.empty(m, STEM_K, dtype=torch.float32, device=x.device)
                 wpad = torch.empty(cout, STEM_K, dtype=torch.float32, device=x.device)
                 nat.check(lib.gc_cuda_im2col_small(x.data_ptr(), gathered.data_ptr(), n, h, wd, cin, r, pad, STEM_K,
                                                    w.data_ptr(), wpad.data_ptr(), cout, st()), "im2col_small")
-                gemm.gemm_tf32(gathered, wpad, bias=cbias, out=_as_2d(yconv), col_partials=partials)
-            if training:
-                nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), tiles, m, cout, stats.data_ptr(),
+                gemm.gemm_tf32(gathered, wpad, bias=cbias, out=_as_2d(yconv), col_partials=partials, bn_fin=fin)
+            if partials is not None:
+                nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), partials.shape[0], m, cout, stats.data_ptr(),
                                                            nat.ptr(running_mean), nat.ptr(running_var), float(momentum),
                                                            float(eps), st()), "bn_finalize_partials")
-            else:
+            elif not training:
                 stats[:cout] = running_mean
                 stats[cout:] = torch.rsqrt(running_var + eps)
             res = _cl(residual) if residual is not None else None
@@ -275,7 +285,7 @@ class _ConvBNAct(torch.autograd.Function):
         with torch.cuda.device(x.device):
             nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
                                                 gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),
-                                                _scratch_for(x.device, cout).data_ptr(), sums.data_ptr(), st()), "bn_bwd_reduce")
+                                                _scratch_for(x.device, cout).data_ptr(), sums.data_ptr(), _fin_ptr(x.device, cout), st()), "bn_bwd_reduce")
             nat.count_launch()
             nat.check(lib.gc_cuda_bn_bwd_apply(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
                                                gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),

@@ -40,14 +40,40 @@ def can_accumulate(out):
             and out.data_ptr() % 16 == 0 and out.stride(0) % 4 == 0)
 
 
-def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None, accumulate=False):
+_fin_scratch = {}
+FIN_MAX_CHANNELS = 4096
+
+
+def fin_scratch(device):
+    """The per-device zero-initialised scratch (ticket + double accumulators) of the kernels that finish a reduction
+    inside the producing launch; every such launch leaves it zeroed."""
+    key = (device.type, device.index)
+    if key not in _fin_scratch:
+        n = int(nat.cuda().gc_cuda_bn_fin_scratch_bytes(FIN_MAX_CHANNELS))
+        _fin_scratch[key] = torch.zeros(n, dtype=torch.uint8, device=device)
+    return _fin_scratch[key]
+
+
+def bn_fin_args(device, stats, running_mean, running_var, momentum, eps):
+    """Argument block that makes a GEMM / convolution launch finish the batch-norm statistics of its output itself: mean and
+    1 / sqrt(var + eps) land in ``stats`` ([2N] floats), the running statistics are updated in place.  The kernel's CTAs
+    add their column sums into a per-device scratch with atomics and the last one to finish does the rest, so no
+    separate finalize kernel runs.  Launches that use it must not overlap on the device (one stream)."""
+    import ctypes
+
+    a = nat.BnFinArgs(fin_scratch(device).data_ptr(), stats.data_ptr(), nat.ptr(running_mean), nat.ptr(running_var),
+                      float(momentum), float(eps))
+    return ctypes.byref(a), a
+
+
+def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None, accumulate=False, bn_fin=None):
     """``col_partials`` (optional, fp32 [m_tiles, 2, N]): receives per 128-row tile the column sums and sums of
     squares of the product -- batch-norm statistics of a 1x1 convolution's output for free.
     ``accumulate=True``: ``out += a @ b_nk.T`` with the additions done by TMA reduce stores (in L2), so the old
     contents of ``out`` never travel to an SM."""
     assert not accumulate or out is not None, "accumulate needs the tensor to add to"
     if not supported(a, b_nk) or (accumulate and not can_accumulate(out)):
-        assert col_partials is None, "column statistics need the tensor-core path"
+        assert col_partials is None and bn_fin is None, "column statistics need the tensor-core path"
         y = a @ b_nk.t()
         if bias is not None:
             y = y + bias
@@ -67,7 +93,8 @@ def gemm_tf32(a, b_nk, bias=None, out=None, col_partials=None, accumulate=False)
         nat.check(nat.cuda().gc_cuda_gemm_tf32(a.data_ptr(), b_nk.data_ptr(), out.data_ptr(), nat.ptr(bias), m, n, k,
                                                a.stride(0), b_nk.stride(0), out.stride(0), int(bool(accumulate)),
                                                nat.ptr(col_partials),
-                                               _error_flag(a.device).data_ptr(), nat.stream_ptr()), "gemm_tf32")
+                                               _error_flag(a.device).data_ptr(), nat.stream_ptr(),
+                                               bn_fin[0] if bn_fin is not None else None), "gemm_tf32")
     return out
 
 
@@ -108,7 +135,7 @@ def configure(kernel="auto", tile_n=0):
     nat.cuda().gc_cuda_gemm_tf32_config(KERNELS[kernel], int(tile_n))
 
 
-def configure_tn(ctas_per_sm=1, min_kblocks=8):
+def configure_tn(ctas_per_sm=1, min_kblocks=4):
     """Split-K policy of ``gemm_tn_tf32`` (for measurements)."""
     nat.cuda().gc_cuda_gemm_tn_config(int(ctas_per_sm), int(min_kblocks))
 

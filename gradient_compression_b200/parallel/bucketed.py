@@ -4,7 +4,9 @@ The reference reduces once, after the whole backward, on one flat buffer (traine
 reducer.py:62).  ``BucketedReducer`` cuts the parameter list into buckets (in the order autograd finishes
 them: last layers first), gives every bucket its own reducer instance, and launches a bucket's reduce on a
 side stream as soon as all of its gradients exist -- while backward keeps computing earlier layers on the
-main stream.  ``finish()`` joins the side stream before the optimiser runs.
+main stream.  ``finish()`` joins the side stream before the optimiser runs.  The fork (side stream waits for
+the main stream at the bucket's last gradient) and the join are plain stream dependencies, so the whole
+arrangement can be captured in a CUDA graph and replays as parallel branches.
 
 Semantics: every bucket is an independent instance of the chosen compressor (``norm_scope = "bucket"``):
 QSGD-MaxNorm normalises by the bucket's own global max-norm, which keeps the estimator unbiased and only
@@ -12,7 +14,9 @@ tightens its variance bound (a bucket's max is at most the whole gradient's max)
 reproduces the reference's whole-gradient behaviour exactly.
 
 The fused kernels of all buckets share one symmetric arena and therefore run one after another on the
-side stream; they overlap with backward kernels, not with each other.
+side stream; they overlap with backward kernels, not with each other.  ``max_blocks`` caps the grid of each
+fused launch: the cooperative kernel's blocks spin while they wait for their peers, so they are kept to a
+small share of the SMs and the backward kernels they run beside keep the rest.
 """
 from __future__ import annotations
 
@@ -22,7 +26,7 @@ from ..reducers import make_reducer
 
 
 class BucketedReducer:
-    def __init__(self, params, reducer_name, device, timer=None, config=None, bucket_mb=25.0, overlap=True):
+    def __init__(self, params, reducer_name, device, timer=None, config=None, bucket_mb=25.0, overlap=True, max_blocks=32):
         self.params = list(params)
         self.device = torch.device(device)
         cap = int(bucket_mb * (1 << 20) / 4)
@@ -49,23 +53,36 @@ class BucketedReducer:
                 self._bucket_of[i] = b
         self.overlap = bool(overlap) and self.device.type == "cuda"
         self.stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
+        self.max_blocks = int(max_blocks) if self.overlap else 0
         self._pending = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)
         self._hooks = []
+        self._arena = None
         self.bits = 0
         self.n_workers = self.reducers[0].n_workers
+        self.rank = self.reducers[0].rank
 
     # -- hook-driven mode -------------------------------------------------------------------
     def attach(self):
         """Register post-accumulate-grad hooks: a bucket is reduced the moment its last gradient lands."""
-        for i, p in enumerate(self.params):
-            self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
+        if not self._hooks:
+            for i, p in enumerate(self.params):
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
         return self
 
     def detach(self):
         for h in self._hooks:
             h.remove()
         self._hooks = []
+
+    def bind_arena(self, arena):
+        """Reduce in place inside ``arena``'s flat gradient buffer: autograd hands fresh gradient tensors to the hooks
+        (``arena.detach_grads()`` before backward), a bucket's gradients are copied into their arena slots with one
+        multi-tensor launch on the side stream, reduced there, and ``finish()`` re-attaches the arena views as
+        ``.grad``.  Parameters must be the arena's, in its order."""
+        assert [id(p) for p in arena.params] == [id(p) for p in self.params], "the arena's parameter list, in its order"
+        self._arena = arena
+        return self.attach()
 
     def start_step(self):
         self._pending = [len(idxs) for idxs in self.buckets]
@@ -80,24 +97,49 @@ class BucketedReducer:
                 self._launch(b)
         return hook
 
+    def _reduce_bucket(self, b):
+        idxs = self.buckets[b]
+        if self._arena is not None:
+            views = [self._arena.grad_views[i] for i in idxs]            # physical-order views of the flat buffer
+            logical = [self._arena._logical_grads[i] for i in idxs]
+            src, dst = [], []
+            for i, lg in zip(idxs, logical):
+                g = self.params[i].grad
+                if g is None:
+                    lg.zero_()
+                elif g is not lg:
+                    src.append(g)
+                    dst.append(lg)
+            if src:
+                torch._foreach_copy_(dst, src)
+            grads = views
+        else:
+            grads = [self.params[i].grad for i in idxs]
+        red = self.reducers[b]
+        red.fused_max_blocks = self.max_blocks
+        self.bits += red.reduce(grads, grads)
+
     def _launch(self, b):
-        grads = [self.params[i].grad for i in self.buckets[b]]
         self._launched[b] = True
         if self.overlap:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(self.stream):
-                self.bits += self.reducers[b].reduce(grads, grads)
+                self._reduce_bucket(b)
         else:
-            self.bits += self.reducers[b].reduce(grads, grads)
+            self._reduce_bucket(b)
 
     def finish(self):
-        """Reduce whatever has not been launched (parameters without gradient hooks firing) and join."""
+        """Reduce whatever has not been launched (parameters whose hooks did not fire), join the side stream and, with
+        an arena bound, make the arena views the parameters' ``.grad`` again."""
         for b in range(len(self.buckets)):
             if not self._launched[b]:
-                if all(self.params[i].grad is not None for i in self.buckets[b]):
+                if self._arena is not None or all(self.params[i].grad is not None for i in self.buckets[b]):
                     self._launch(b)
         if self.overlap:
             torch.cuda.current_stream(self.device).wait_stream(self.stream)
+        if self._arena is not None:
+            for p, gv in zip(self._arena.params, self._arena._logical_grads):
+                p.grad = gv
         return self.bits
 
     # -- plain mode (same result, no hooks): reduce(grad_in, grad_out) over all buckets ---------------

@@ -2,7 +2,9 @@
 
 ``FusedOps`` wraps the launches for a ``SymmetricArena`` (one rank per process) or a ``LocalGroup``
 (all ranks in one launch).  ``FusedEngine`` adapts them to the reducers' ``reduce(grad_in, grad_out)``
-contract.
+contract.  The module-level functions at the end are what the reducers call: each returns ``None`` (or
+``False``) when the fused path does not apply, in which case the reducer continues on its collective
+(``dist``) backend; otherwise it performs the whole reduce and returns the reference-accounting bit count.
 """
 from __future__ import annotations
 
@@ -140,6 +142,7 @@ class FusedEngine:
     def __init__(self, reducer):
         self.device = reducer._device
         self.group = reducer._group
+        self._owner = reducer       # its ``fused_max_blocks`` attribute (optional) caps the grid of every launch
         self.ops = None             # FusedOps of the family used last (what status checks look at)
         self._ops = {}              # family -> FusedOps
         self._n = 0
@@ -163,6 +166,7 @@ class FusedEngine:
         ops = self._ops.get(family)
         if ops is None or ops.arena is not arena:
             ops = self._ops[family] = FusedOps(arena)
+        ops.max_blocks = int(getattr(self._owner, "fused_max_blocks", 0) or 0)
         self.ops = ops
         self._n = max(self._n, n)
         return ops
@@ -331,3 +335,49 @@ class FusedEngine:
         bits = 32 * (p_total + q_total + c["v_total"])
         reducer.last_wire_bits = bits
         return bits
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# dispatch from the reducers
+
+def _engine(reducer):
+    eng = getattr(reducer, "_fused", None)
+    if eng is None:
+        eng = FusedEngine.for_reducer(reducer)
+        reducer._fused = eng if eng is not None else False
+    return eng or None
+
+
+def allreduce_mean(reducer, flat, grad_out):
+    eng = _engine(reducer)
+    return eng.allreduce_mean(reducer, flat, grad_out) if eng else False
+
+
+def qsgd_maxnorm(reducer, flat, grad_out):
+    eng = _engine(reducer)
+    return eng.qsgd_maxnorm(reducer, flat, grad_out) if eng else None
+
+
+def qsgd_twoscale(reducer, flat, grad_out):
+    eng = _engine(reducer)
+    return eng.qsgd_twoscale(reducer, flat, grad_out) if eng else None
+
+
+def qsgd_multiscale(reducer, flat, grad_out):
+    eng = _engine(reducer)
+    return eng.qsgd_multiscale(reducer, flat, grad_out) if eng else None
+
+
+def randk(reducer, flat, grad_out, start, k, npass):
+    eng = _engine(reducer)
+    return eng.randk(reducer, flat, grad_out, start, k, npass) if eng else None
+
+
+def powersgd(reducer, flat, grad_out, plan, fresh):
+    eng = _engine(reducer)
+    return eng.powersgd(reducer, flat, grad_out, plan, fresh) if eng else None
+
+
+def sparse(reducer, flat, grad_out, idx, vals):
+    eng = _engine(reducer)
+    return eng.sparse(reducer, flat, grad_out, idx, vals) if eng else False

@@ -18,7 +18,7 @@ class NoneAllReducer(Reducer):
         self.last_wire_bits = bits
         with self._timer("reduce.allreduce", verbosity=2):
             if self._use_fused():
-                from ..parallel import fused
+                from ..parallel import engine as fused
                 if fused.allreduce_mean(self, flat, grad_out):
                     return bits
             self._all_reduce(flat.buffer)

@@ -50,7 +50,7 @@ class QSGDMaxNormTwoScaleReducer(Reducer):
         with self._timer("reduce.flat_pack"):
             flat = TensorBuffer(grad_in)
         if self._use_fused():
-            from ..parallel import fused
+            from ..parallel import engine as fused
             bits = fused.qsgd_twoscale(self, flat, grad_out)
             if bits is not None:
                 return bits
@@ -83,7 +83,7 @@ class QSGDMaxNormMultiScaleReducer(Reducer):
         with self._timer("reduce.flat_pack"):
             flat = TensorBuffer(grad_in)
         if self._use_fused():
-            from ..parallel import fused
+            from ..parallel import engine as fused
             bits = fused.qsgd_multiscale(self, flat, grad_out)
             if bits is not None:
                 return bits

@@ -75,7 +75,7 @@ class RankKReducer(Reducer):
             if self._memory is None:
                 self._memory = torch.zeros_like(flat.buffer)
         if self._use_fused():
-            from ..parallel import fused
+            from ..parallel import engine as fused
             bits = fused.powersgd(self, flat, grad_out, plan, fresh)   # adds the error memory inside its first kernel
             if bits is not None:
                 self._step += 1

@@ -56,7 +56,7 @@ class _MaxNormReducer(Reducer):
                 else:
                     flat.buffer.add_(self._memory)
         if self._use_fused() and not self.error_feedback:
-            from ..parallel import fused
+            from ..parallel import engine as fused
             bits = fused.qsgd_maxnorm(self, flat, grad_out)
             if bits is not None:
                 return bits

@@ -74,7 +74,7 @@ class GlobalRandKMaxNormReducer(Reducer):
         n = flat.buffer.numel()
         start, k, npass = self._queue.next_window(n)
         if self._use_fused():
-            from ..parallel import fused
+            from ..parallel import engine as fused
             bits = fused.randk(self, flat, grad_out, start, k, npass)
             if bits is not None:
                 return bits

@@ -51,7 +51,7 @@ class _TopKBase(Reducer):
         bits = sel.total * (32 + self.position_bits)
         self.last_wire_bits = sel.total * 64
         if self._use_fused():
-            from ..parallel import fused
+            from ..parallel import engine as fused
             if fused.sparse(self, flat, grad_out, idx, vals):
                 return bits
         with self._timer("reduce.gather", verbosity=2):

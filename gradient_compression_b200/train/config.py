@@ -46,6 +46,12 @@ class TrainConfig:
     save_training_state: bool = False
     device: Optional[str] = None
     heartbeat_timeout_s: float = 0.0  # > 0 enables the step watchdog
+    graph: bool = True                # CUDA devices: run the whole step as one callable replayed from a CUDA graph
+    norm_scope: str = "global"        # global: one reduce after backward (the reference) | bucket: per-bucket reduces
+                                      # overlapped with backward, each bucket normalised by its own max-norm
+    bucket_mb: float = 25.0           # bucket size for norm_scope = bucket
+    reduce_max_blocks: int = 32       # grid cap of a fused reduce that runs beside backward kernels
+    on_collective_timeout: str = "raise"   # raise | dist: after a device-side timeout continue on torch.distributed
 
     def as_dict(self):
         return dataclasses.asdict(self)

@@ -152,9 +152,10 @@ class DevicePrefetcher:
 
 
 class LaggedReadback:
-    """Device scalars read on the host one step late: ``push(t)`` starts an asynchronous copy of ``t`` into pinned host
-    memory and returns the value pushed ``lag`` calls earlier (``None`` until there is one), so that reading the loss
-    of every step never stalls the stream that is computing the next one.  ``drain()`` returns what is still pending.
+    """Device scalars (or short vectors) read on the host one step late: ``push(t)`` starts an asynchronous copy of ``t``
+    into pinned host memory and returns the value pushed ``lag`` calls earlier (``None`` until there is one; a float for
+    one element, a list of floats otherwise), so that reading the loss and metrics of every step never stalls the
+    stream that is computing the next one.  ``drain()`` returns what is still pending.
     (The reference reads metrics with ``.item()`` inside the step: model_dispatcher.py:140-164.)"""
 
     def __init__(self, device, lag=1):
@@ -164,11 +165,17 @@ class LaggedReadback:
         self._free = []
 
     def push(self, t):
+        n = t.numel()
         if self._device.type != "cuda":
-            self._pending.append((float(t), None, None))
+            flat = t.detach().reshape(-1).float()
+            self._pending.append((float(flat[0]) if n == 1 else [float(v) for v in flat], None, None))
         else:
-            buf = self._free.pop() if self._free else torch.empty(1, dtype=torch.float32).pin_memory()
-            buf.copy_(t.detach().reshape(1).float(), non_blocking=True)
+            buf = next((b for b in self._free if b.numel() == n), None)
+            if buf is not None:
+                self._free.remove(buf)
+            else:
+                buf = torch.empty(n, dtype=torch.float32).pin_memory()
+            buf.copy_(t.detach().reshape(n).float(), non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(torch.cuda.current_stream(self._device))
             self._pending.append((None, buf, ev))
@@ -181,7 +188,7 @@ class LaggedReadback:
         if buf is None:
             return val
         ev.synchronize()
-        val = float(buf[0])
+        val = float(buf[0]) if buf.numel() == 1 else [float(v) for v in buf]
         self._free.append(buf)
         return val
 

@@ -49,6 +49,10 @@ def initiate_distributed(backend="nccl", timeout_s=1800):
     return True
 
 
+def _global_rank():
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
 def _device_for(config, local_rank):
     if config.device:
         return torch.device(config.device)
@@ -80,7 +84,6 @@ def train(local_rank=0, config=None, logger=None):
             continue
         set_seed(config.seed)
         timer = Timer(verbosity_level=config.log_verbosity, mode=config.timer_mode, quiet=local_rank != 0)
-        reducer = make_reducer(config.reducer, device, timer, cfg_dict)
         bits_communicated = 0
         global_iteration_count = 0
         model_seed = config.seed if config.broadcast_parameters else config.seed + local_rank
@@ -91,10 +94,26 @@ def train(local_rank=0, config=None, logger=None):
         optimizer = FlatSGD(model.arena, lr=config.lr, momentum=config.momentum, weight_decay=config.weight_decay,
                             nesterov=config.nesterov)
         scheduler = CosineSchedule(optimizer, T_max=config.num_epochs, eta_min=0)
+        if config.norm_scope == "bucket":
+            from ..parallel.bucketed import BucketedReducer
+            reducer = BucketedReducer(model.parameters, config.reducer, device, timer, cfg_dict, bucket_mb=config.bucket_mb,
+                                      max_blocks=config.reduce_max_blocks)
+        else:
+            reducer = make_reducer(config.reducer, device, timer, cfg_dict)
+        # CUDA: the whole step (forward, backward, reduce, update, batch metrics) is one callable, replayed from a CUDA
+        # graph when config.graph; the labelled eager path below remains for CPU runs and for per-phase timings
+        step = None
+        if device.type == "cuda" and (config.graph or config.norm_scope == "bucket"):
+            from ..parallel.graph import GraphedStep
+            step = GraphedStep(model, reducer, optimizer, enabled=config.graph,
+                               fallback="dist" if config.on_collective_timeout == "dist" else None)
+        elif config.norm_scope == "bucket":
+            reducer.attach()
         start_epoch = 0
         if resume_state is not None and run == resume_state["run"]:
             _, start_epoch, bits_communicated, best_accuracy = ckpt.restore_training_state(
-                resume_state, model, optimizer, scheduler, reducer)
+                resume_state, model, optimizer, scheduler, reducer,
+                rank_state=ckpt.load_rank_state(config.resume, _global_rank()))
             resume_state = None
 
         for epoch in range(start_epoch, config.num_epochs):
@@ -110,16 +129,26 @@ def train(local_rank=0, config=None, logger=None):
                 if watchdog is not None:
                     watchdog.beat(global_iteration_count)
                 with timer("batch", epoch_frac):
+                    reduce_now = global_iteration_count % config.local_steps == 0
+                    if step is not None and reduce_now:
+                        step(batch)
+                        epoch_metrics.add(step.metrics)
+                        bits_communicated += step.bits_per_step
+                        continue
+                    if config.norm_scope == "bucket" and reduce_now:
+                        reducer.start_step()
                     _, grads, metrics = model.batch_loss_with_gradients(batch)
                     epoch_metrics.add(metrics)
-                    if global_iteration_count % config.local_steps == 0:
+                    if reduce_now:
                         # gradients already live in the flat arena: the reducer works in place, so the
                         # reference's "batch.accumulate" copy into send buffers has nothing left to do
                         with timer("batch.reduce", epoch_frac):
-                            bits_communicated += reducer.reduce(grads, grads)
+                            bits_communicated += reducer.finish() if config.norm_scope == "bucket" else reducer.reduce(grads, grads)
                     with timer("batch.step", epoch_frac, verbosity=2):
                         optimizer.step()
             scheduler.step()
+            if step is not None:
+                step.check()                  # a reduce that timed out on the device surfaces here at the latest
 
             with timer("epoch_metrics.collect", epoch, verbosity=2):
                 epoch_metrics.reduce()
@@ -140,7 +169,12 @@ def train(local_rank=0, config=None, logger=None):
                             best_accuracy["top5"][run] = value
             if local_rank == 0:
                 logger.epoch_update(run, epoch, epoch_metrics, test_stats)
-                if config.save_training_state:
+            if config.save_training_state:
+                if step is not None:
+                    step.sync_host_counters()
+                # the reducer's state (error memories, noise counters) differs per worker: every rank writes its own
+                logger.save_training_state(ckpt.rank_state(reducer, epoch), name=ckpt.rank_state_name(_global_rank()))
+                if local_rank == 0:
                     logger.save_training_state(ckpt.training_state(model, optimizer, scheduler, reducer, run, epoch,
                                                                    bits_communicated, best_accuracy))
         if local_rank == 0:

@@ -69,6 +69,7 @@ class Logger:
         torch.save(model.state_dict(), os.path.join(self._log_path, "model.pt"))
 
     def save_training_state(self, state, name="train_state.pt"):
+        os.makedirs(self._log_path, exist_ok=True)
         torch.save(state, os.path.join(self._log_path, name))
 
     def summary_writer(self, timer, best_accuracy, bits_communicated):

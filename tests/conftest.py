@@ -24,6 +24,16 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+def reference_dir():
+    """Where the reference project's sources are: ``$GRADCOMP_REFERENCE_DIR``, else the copy installed for the benchmark's
+    reference arm under ``baseline/_ref`` of this checkout; None when neither exists (tests that need it skip)."""
+    env = os.environ.get("GRADCOMP_REFERENCE_DIR")
+    if env:
+        return env if os.path.isdir(env) else None
+    local = os.path.join(ROOT, "baseline", "_ref")
+    return local if os.path.exists(os.path.join(local, "reducer.py")) else None
+
+
 def free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -9,7 +9,9 @@ import torch
 
 from gradient_compression_b200 import models
 
-REF = os.environ.get("GRADCOMP_REFERENCE_DIR", "/root/reference")
+from .conftest import reference_dir
+
+REF = reference_dir() or ""
 LIGHT = ["LeNet", "ResNet18", "PreActResNet18", "densenet_cifar", "MobileNet", "MobileNetV2", "SENet18", "PNASNetA",
          "PNASNetB", "EfficientNetB0", "RegNetX_200MF", "RegNetY_400MF", "ShuffleNetG2", "ShuffleNetG3",
          "ShuffleNetV2_x0_5", "ResNeXt29_32x4d", "GoogLeNet", "DPN26", "VGG11"]

@@ -10,7 +10,9 @@ import torch.distributed as dist
 from gradient_compression_b200 import ops, reducers as R
 from gradient_compression_b200.ops import philox
 
-REFERENCE_DIR = os.environ.get("GRADCOMP_REFERENCE_DIR", "/root/reference")
+from .conftest import reference_dir
+
+REFERENCE_DIR = reference_dir() or ""
 SHAPES = [(16, 3, 3, 3), (16,), (32, 16, 3, 3), (32,), (10, 32), (10,)]
 CFG = dict(seed=42, K=50, quantization_level=4, higher_quantization_level=8, quantization_levels=[2, 6, 10],
            compression=0.1, rank=2)

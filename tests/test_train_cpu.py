@@ -153,8 +153,8 @@ def test_resume_continues_where_it_stopped(tmp_path):
     real_save = Logger.save_training_state
 
     def capture(self, state, name="train_state.pt"):
-        if state["epoch"] == 0:
-            real_save(self, state, "epoch0.pt")
+        if state.get("epoch") == 0:
+            real_save(self, state, name.replace("train_state", "epoch0"))
         real_save(self, state, name)
 
     Logger.save_training_state = capture
@@ -180,3 +180,40 @@ def test_trainer_with_device_resident_pipeline(tmp_path):
     lg = train(0, cfg, logger=Logger(cfg.as_dict(), 0, log_path=str(tmp_path / "run")))
     log = np.load(os.path.join(lg.log_path, "log_dict.npy"), allow_pickle=True).item()
     assert np.isfinite(log["train_loss"]).all() and np.isfinite(log["test_loss"]).all()
+
+
+def _resume_body(rank, world, root):
+    """Two workers with error-feedback memories: each must get its OWN memory and noise stream back on resume."""
+    base = dict(runs=1, batch_size=4, architecture="LeNet", reducer="TopKReducer", K=5, data="synthetic",
+                synthetic_train_size=16 * world, synthetic_test_size=8 * world, log_verbosity=0, save_training_state=True,
+                timer_mode="sync", lr=0.01, broadcast_parameters=True)
+    first = TrainConfig(num_epochs=1, log_root=root, **base)
+    train(rank, first, logger=Logger(first.as_dict(), rank, log_path=os.path.join(root, "run")))
+    mine = torch.load(os.path.join(root, "run", f"train_state.rank{rank}.pt"), weights_only=False)
+    other = torch.load(os.path.join(root, "run", f"train_state.rank{1 - rank}.pt"), weights_only=False)
+    mem_mine, mem_other = mine["reducer"]["memory"], other["reducer"]["memory"]
+    assert not torch.equal(mem_mine, mem_other), "workers see different data: their memories differ"
+    # resume: the reducer of this rank must hold this rank's memory, not rank 0's
+    from gradient_compression_b200.reducers import make_reducer
+    from gradient_compression_b200.train import checkpoint as ckpt
+
+    red = make_reducer("TopKReducer", "cpu", None, {"K": 5})
+    state = torch.load(os.path.join(root, "run", "train_state.pt"), weights_only=False)
+    rs = ckpt.load_rank_state(os.path.join(root, "run", "train_state.pt"), rank)
+    assert rs is not None
+    red.load_state_dict((rs if rs["reducer_class"] == "TopKReducer" else state)["reducer"])
+    assert torch.equal(red.state_dict()["memory"], mem_mine)
+
+
+def test_two_rank_resume_restores_each_workers_own_reducer_state(dist_runner, tmp_path):
+    dist_runner(_resume_body, world=2, args=(str(tmp_path),))
+
+
+def test_noise_source_keeps_the_live_rank_on_restore():
+    from gradient_compression_b200.compressors import NoiseSource
+
+    saved = NoiseSource(seed=3, rank=0)
+    saved.step = 17
+    live = NoiseSource(seed=3, rank=1)
+    live.load_state_dict(saved.state_dict())
+    assert live.rank == 1 and live.step == 17 and live.stream(1) != saved.stream(1)
