@@ -22,6 +22,11 @@ using namespace gc;
 namespace {
 
 constexpr int THREADS = 512;
+// Register cap of the dense fused kernels.  A bucketed reducer runs them beside backward kernels; the persistent tcgen05
+// GEMM wants one CTA on every SM (352 threads x 96 registers = 33.8 K of the SM's 64 K) and assigns its tiles
+// statically, so a reducer block that does not fit next to it keeps that SM's GEMM CTA -- and with it the whole GEMM --
+// waiting until the reducer block leaves.  512 threads x 56 registers = 28.7 K fits beside it.
+#define GC_FUSED_MAXNREG 56
 enum Phase : int { PH_READY = 0, PH_DONE = 1, PH_MASK = 2, PH_STAGE = 3, PH_AUX = 4 };
 
 struct Common {
@@ -199,7 +204,7 @@ __device__ __forceinline__ void reduce_scatter_rows(const Ctx& c, int world, int
 }
 
 template <int MW, int SUMB>
-__global__ void __launch_bounds__(THREADS, 2) qsgd_fused_kernel(LaunchViews lv, QsgdParams p) {
+__global__ void __maxnreg__(GC_FUSED_MAXNREG) qsgd_fused_kernel(LaunchViews lv, QsgdParams p) {
   __shared__ float smem[32];
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
@@ -307,7 +312,7 @@ struct TwoScaleParams {
 };
 
 template <int MW, int SUMB>
-__global__ void __launch_bounds__(THREADS, 2) twoscale_fused_kernel(LaunchViews lv, TwoScaleParams p) {
+__global__ void __maxnreg__(GC_FUSED_MAXNREG) twoscale_fused_kernel(LaunchViews lv, TwoScaleParams p) {
   __shared__ float smem[32];
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
@@ -425,7 +430,7 @@ struct MultiScaleParams {
 };
 
 template <int MW, int SUMB>
-__global__ void __launch_bounds__(THREADS, 2) multiscale_fused_kernel(LaunchViews lv, MultiScaleParams p) {
+__global__ void __maxnreg__(GC_FUSED_MAXNREG) multiscale_fused_kernel(LaunchViews lv, MultiScaleParams p) {
   __shared__ float smem[32];
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
@@ -553,7 +558,7 @@ struct AllreduceParams {
   float alpha;   // 1 / W
 };
 
-__global__ void __launch_bounds__(THREADS, 2) allreduce_fused_kernel(LaunchViews lv, AllreduceParams p) {
+__global__ void __maxnreg__(GC_FUSED_MAXNREG) allreduce_fused_kernel(LaunchViews lv, AllreduceParams p) {
   Ctx c = make_ctx(lv);
   const RankView& v = *c.v;
   Waiter w{c.hdr, global_ns() + p.c.timeout_ns};
@@ -887,11 +892,23 @@ int fill_views(CommCtx** ctxs, int n_virtual, const float* const* ins, float* co
   return 0;
 }
 
+// 0: always a cooperative launch (co-residency of the grid is guaranteed by the driver).  1: grids of at most one block
+// per SM are launched as ordinary kernels.  Their blocks still all become resident -- nothing else on the device ever
+// waits for them, so the scheduler places them as soon as the kernels they run beside retire blocks, and every wait is
+// bounded anyway -- but an ordinary launch may overlap with the kernels of other streams, which is what the bucketed
+// reducer wants for the reduces it runs beside backward (a cooperative launch measured as a barrier between them).
+int g_small_grid_plain_launch = 0;
+
 template <typename P>
 int coop_launch(const void* kernel, const LaunchViews& lv, const P& params, cudaStream_t st) {
   void* args[2] = {(void*)&lv, (void*)&params};
   dim3 grid((unsigned)(lv.n_virtual * lv.blocks_per_rank)), block(THREADS);
-  cudaError_t e = cudaLaunchCooperativeKernel(kernel, grid, block, args, 0, st);
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaError_t e;
+  if (g_small_grid_plain_launch && (int)grid.x <= sms) e = cudaLaunchKernel(kernel, grid, block, args, 0, st);
+  else e = cudaLaunchCooperativeKernel(kernel, grid, block, args, 0, st);
   return (int)e;
 }
 
@@ -922,6 +939,7 @@ inline int64_t parity_half_bytes(int64_t arena_bytes) { return (arena_bytes - AR
 extern "C" {
 
 int64_t gc_comm_header_bytes() { return ARENA_HEADER_BYTES; }
+void gc_fused_small_grid_plain_launch(int on) { g_small_grid_plain_launch = on ? 1 : 0; }
 int gc_comm_max_world() { return MAXW; }
 
 // Bytes of arena a one-shot kernel needs when each of its parity regions holds `region_bytes`.

@@ -158,6 +158,7 @@ def cuda():
         _declare(lib, "gc_cuda_augment", c_int, [P, P, c_i64, c_u64, c_u32, c_i64, c_i64, c_int, c_int, c_int, P, P, P, P, P])
         PP = ctypes.POINTER(c_void_p)
         _declare(lib, "gc_comm_header_bytes", c_i64, [])
+        _declare(lib, "gc_fused_small_grid_plain_launch", None, [c_int])
         _declare(lib, "gc_comm_max_world", c_int, [])
         _declare(lib, "gc_comm_required_bytes", c_i64, [c_i64])
         _declare(lib, "gc_comm_oneshot_bytes", c_i64, [c_i64])

@@ -132,6 +132,35 @@ def refresh_transposed(owner, params):
     _dgrad_weights.refresh(owner, params)
 
 
+# Gradient slots: where the weight-gradient kernels add their result when the weight's owner (a ``FlatArena``) has offered
+# the weight's place in its flat gradient buffer.  id(weight) -> (weakref(weight), 2-D view [Cout, R*S*Cin] of the slot).
+_grad_slots = {}
+
+
+def offer_grad_slots(params, slots):
+    """``slots[i]``: the contiguous gradient storage of the 4-D weight ``params[i]`` in its memory order (None: no offer).
+    The split-K weight-gradient kernels then add dW straight into the slot (it must hold the value to add to: zeros at the
+    start of a step) and the layer's autograd node returns no weight gradient, instead of allocating and zeroing a
+    tensor per layer that is copied into the flat buffer afterwards."""
+    for p, slot in zip(params, slots):
+        if slot is None:
+            _grad_slots.pop(id(p), None)
+        elif p.dim() == 4:
+            _grad_slots[id(p)] = (weakref.ref(p), slot.reshape(p.shape[0], -1))
+
+
+def withdraw_grad_slots(params):
+    for p in params:
+        _grad_slots.pop(id(p), None)
+
+
+def _slot_of(w):
+    e = _grad_slots.get(id(w))
+    if e is None or e[0]() is not w or e[1].device != w.device:
+        return None
+    return e[1]
+
+
 def _as_2d(t):
     n, c, h, w = t.shape
     return t.permute(0, 2, 3, 1).reshape(n * h * w, c)
@@ -207,12 +236,12 @@ def conv_forward(x, w, bias=None, stride=1, pad=1, col_partials=None, out=None, 
     return out
 
 
-def conv_wgrad(dy, x, r, stride, pad):
+def conv_wgrad(dy, x, r, stride, pad, out=None):
     """Weight gradient ``[Cout, R*R*Cin]`` (channels-last filter order) of ``conv2d(x, w, stride, pad)`` given the
-    channels-last output gradient ``dy``."""
+    channels-last output gradient ``dy``; added onto ``out`` when given."""
     n, cin, h, wd = x.shape
     cout = dy.shape[1]
-    dw = torch.zeros(cout, r * r * cin, dtype=torch.float32, device=x.device)
+    dw = out if out is not None else torch.zeros(cout, r * r * cin, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         nat.check(nat.cuda().gc_cuda_conv_wgrad(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), n, h, wd, cin, cout, r, stride, pad,
                                                 _err(x.device), nat.stream_ptr()), "conv_wgrad")
@@ -320,13 +349,15 @@ class _ConvBNAct(torch.autograd.Function):
                 link.conv_done = True
             dw = None
             if ctx.needs_input_grad[1]:
+                slot = _slot_of(w) if WGRAD_ENABLED else None       # the owner's gradient storage, or None: return a tensor
                 if mode == "gemm" and WGRAD_ENABLED and cout % 32 == 0 and cin % 32 == 0:
                     # dW[Cout, Cin] = dY^T X over all positions: split-K GEMM with MN-major tcgen05 operands
-                    dw2d = gemm.gemm_tn_tf32(_as_2d(dconv), _as_2d(x))
-                    dw = dw2d.view(cout, cin, 1, 1).contiguous(memory_format=torch.channels_last)
+                    dw2d = gemm.gemm_tn_tf32(_as_2d(dconv), _as_2d(x), out=slot, accumulate=slot is not None)
+                    dw = None if slot is not None else dw2d.view(cout, cin, 1, 1).contiguous(memory_format=torch.channels_last)
                 elif mode == "conv" and WGRAD_ENABLED and lib.gc_cuda_conv_wgrad_supported(n, x.shape[2], x.shape[3], cin, cout, r,
                                                                                            stride, pad):
-                    dw = conv_wgrad(dconv, x, r, stride, pad).view(cout, r, r, cin).permute(0, 3, 1, 2)
+                    dw2d = conv_wgrad(dconv, x, r, stride, pad, out=slot)
+                    dw = None if slot is not None else dw2d.view(cout, r, r, cin).permute(0, 3, 1, 2)
                 elif mode == "stem" and WGRAD_ENABLED and cout % 32 == 0:
                     dwp = gemm.gemm_tn_tf32(_as_2d(dconv), gathered)                       # [Cout, STEM_K]
                     dw = dwp[:, : r * r * cin].reshape(cout, r, r, cin).permute(0, 3, 1, 2)

@@ -44,6 +44,23 @@ class FlatArena:
                 self.grad_views.append(gv)
                 self._logical_grads.append(logical_g)
         self.dense = self.total == self.numel   # no padding holes: the list aliases the flat buffer exactly
+        self._direct = False                    # weight-gradient kernels add straight into flat_grads (see direct_grads)
+
+    def direct_grads(self, on=True):
+        """Offer every 4-D weight's place in ``flat_grads`` to the tensor-core weight-gradient kernels, which then add dW
+        there and hand autograd nothing for that weight: no per-layer gradient tensor, no zero fill of it, no copy into the
+        flat buffer.  The buffer is zeroed at the start of every step (``detach_grads`` / ``zero_grad``).  Gradient hooks
+        do not fire for such weights, so reducers that are driven by hooks must not turn this on."""
+        if not self.flat_grads.is_cuda:
+            return self
+        from ..ops import conv
+
+        self._direct = bool(on)
+        if on:
+            conv.offer_grad_slots(self.params, [gv if p.dim() == 4 else None for p, gv in zip(self.params, self.grad_views)])
+        else:
+            conv.withdraw_grad_slots(self.params)
+        return self
 
     @staticmethod
     def _views(segment, p):
@@ -66,6 +83,8 @@ class FlatArena:
 
     def detach_grads(self):
         """Let autograd allocate fresh gradients in the next backward (no accumulate-into-view kernels)."""
+        if self._direct:
+            self.flat_grads.zero_()           # the weight-gradient kernels add onto their slots
         for p in self.params:
             p.grad = None
 
@@ -74,9 +93,12 @@ class FlatArena:
         re-attach the views.  Together with ``detach_grads`` this replaces one memset plus one in-place
         add per parameter tensor (161 launches for ResNet-50) by a single launch."""
         src, dst = [], []
+        from ..ops import conv
+
         for p, gv in zip(self.params, self._logical_grads):
             if p.grad is None:
-                gv.zero_()
+                if not (self._direct and conv._slot_of(p) is not None):       # else: the kernels already put it there
+                    gv.zero_()
             elif p.grad is not gv:
                 src.append(p.grad)
                 dst.append(gv)

@@ -20,20 +20,32 @@ small share of the SMs and the backward kernels they run beside keep the rest.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..reducers import make_reducer
 
 
 class BucketedReducer:
-    def __init__(self, params, reducer_name, device, timer=None, config=None, bucket_mb=25.0, overlap=True, max_blocks=32):
+    def __init__(self, params, reducer_name, device, timer=None, config=None, bucket_mb=25.0, overlap=True, max_blocks=32,
+                 tail_mb=2.0):
         self.params = list(params)
         self.device = torch.device(device)
         cap = int(bucket_mb * (1 << 20) / 4)
-        # buckets in reverse parameter order (gradients of the last layers are ready first), each a
+        # The bucket that is reduced last holds the first parameters (their gradients are the last to exist) and its
+        # reduce is the only one that nothing can hide: it is kept small (``tail_mb``) and gets the whole GPU.
+        tail_cap, n_tail, acc = int(tail_mb * (1 << 20) / 4), 0, 0
+        if tail_cap > 0 and sum(p.numel() for p in self.params) > cap:
+            for p in self.params[:-1]:
+                if acc + p.numel() > tail_cap:
+                    break
+                acc += p.numel()
+                n_tail += 1
+        # the other buckets in reverse parameter order (gradients of the last layers are ready first), each a
         # contiguous range of the parameter list so that it aliases a slice of a flat arena
         self.buckets, cur, cur_n = [], [], 0
-        for idx in reversed(range(len(self.params))):
+        for idx in reversed(range(n_tail, len(self.params))):
             cur.append(idx)
             cur_n += self.params[idx].numel()
             if cur_n >= cap:
@@ -41,12 +53,17 @@ class BucketedReducer:
                 cur, cur_n = [], 0
         if cur:
             self.buckets.append(sorted(cur))
+        if n_tail:
+            self.buckets.append(list(range(n_tail)))
         cfg = dict(config or {})
         self.reducers = []
         for b, _ in enumerate(self.buckets):
             c = dict(cfg)
             c["seed"] = int(cfg.get("seed", 0)) * 1000003 + b          # independent noise / index streams per bucket
             self.reducers.append(make_reducer(reducer_name, device, timer, c))
+        largest = max(sum(self.params[i].numel() for i in idxs) for idxs in self.buckets)
+        for r in self.reducers:
+            r.fused_arena_elements = largest       # all buckets share one arena: size it once, for the largest of them
         self._bucket_of = {}
         for b, idxs in enumerate(self.buckets):
             for i in idxs:
@@ -54,6 +71,10 @@ class BucketedReducer:
         self.overlap = bool(overlap) and self.device.type == "cuda"
         self.stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
         self.max_blocks = int(max_blocks) if self.overlap else 0
+        if self.overlap and os.environ.get("GCB200_BUCKET_PLAIN_LAUNCH", "1") == "1":
+            from ..ops import _native as nat
+
+            nat.cuda().gc_fused_small_grid_plain_launch(1)     # small grids as ordinary launches: they may overlap backward
         self._pending = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)
         self._hooks = []
@@ -116,7 +137,8 @@ class BucketedReducer:
         else:
             grads = [self.params[i].grad for i in idxs]
         red = self.reducers[b]
-        red.fused_max_blocks = self.max_blocks
+        # every bucket but the last runs beside backward kernels on a capped grid; the last one has the GPU to itself
+        red.fused_max_blocks = self.max_blocks if b + 1 < len(self.buckets) else 0
         self.bits += red.reduce(grads, grads)
 
     def _launch(self, b):

@@ -159,7 +159,9 @@ class FusedEngine:
         # the arena is shared by every reducer of this device / group and may have been regrown by another
         # one since the last call: always go through the registry, never keep a stale handle
         if oneshot_region_bytes is None:
-            family, nbytes = "twoshot", comm.required_bytes(n)
+            # an owner that knows its largest gradient (a bucketed reducer: its largest bucket) says so, and the arena is
+            # sized once instead of being replaced when a larger bucket shows up
+            family, nbytes = "twoshot", comm.required_bytes(max(n, int(getattr(self._owner, "fused_arena_elements", 0) or 0)))
         else:
             family, nbytes = "oneshot", max(comm.oneshot_bytes(oneshot_region_bytes), ONESHOT_MIN_BYTES)
         arena = shared_arena(nbytes, self.device, self.group, family)

@@ -104,7 +104,10 @@ class GraphedStep:
         self.capture_error = None
         self._bucketed = hasattr(reducer, "buckets")
         if self._bucketed:
-            reducer.bind_arena(task.arena)
+            reducer.bind_arena(task.arena)       # driven by gradient hooks: every weight gradient must reach autograd
+            task.arena.direct_grads(False)
+        else:
+            task.arena.direct_grads(True)        # weight-gradient kernels add straight into the flat gradient buffer
         self._status = _StatusMirror(task._device) if (check_status and task._device.type == "cuda") else None
 
     # -- the reducers behind this step -------------------------------------------------------

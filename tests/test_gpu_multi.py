@@ -94,3 +94,66 @@ def test_fused_reducers_across_gpus(dist_runner, world):
         pytest.skip(f"needs {world} GPUs")
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dist_runner(_body, world=world, backend="nccl")
+
+
+def _bucketed_body(rank, world):
+    """Per-bucket fused reduces on a side stream, captured in a CUDA graph and replayed: every bucket of every replay must
+    equal the CPU oracle of an independent QSGD instance with that bucket's seed and the Philox step the device derives."""
+    from gradient_compression_b200.ops import _native as nat
+    from gradient_compression_b200.parallel.bucketed import BucketedReducer
+    from tests.test_gpu_fused import _oracle_qsgd
+
+    dev = torch.device("cuda", rank)
+    sizes = [70001, 130, 50000, 9000, 64]
+    params = [torch.nn.Parameter(torch.zeros(s, device=dev)) for s in sizes]
+    for p in params:
+        p.grad = torch.zeros_like(p)
+    srcs = [[torch.randn(s, generator=torch.Generator().manual_seed(500 + 10 * r + i)) * (1e-3 * (r + 1))
+             for i, s in enumerate(sizes)] for r in range(world)]
+    mine = [t.to(dev) for t in srcs[rank]]
+    br = BucketedReducer(params, "QSGDMaxNormReducer", dev, None, {"quantization_level": 4, "seed": 3, "backend": "fused"},
+                         bucket_mb=0.2, max_blocks=8, tail_mb=0)
+    assert br.buckets == [[2, 3, 4], [0, 1]]
+    nb = len(br.buckets)
+
+    def run_once():
+        for p, s in zip(params, mine):
+            p.grad.copy_(s)
+        br.start_step()
+        for b in range(nb):
+            br._launch(b)
+        br.finish()
+
+    def check(step_of_bucket, what):
+        torch.cuda.synchronize()
+        for j, idxs in enumerate(br.buckets):
+            got = torch.cat([params[i].grad.reshape(-1) for i in idxs]).cpu()
+            xs = [torch.cat([srcs[r][i] for i in idxs]) for r in range(world)]
+            want = _oracle_qsgd(xs, 4, 3 * 1000003 + j, step_of_bucket(j))
+            assert torch.equal(got, want), f"{what}, bucket {j}"
+
+    run_once()                                   # eager: maps the arenas; every bucket's host-side step is 0
+    check(lambda j: 0, "eager")
+    arenas = []
+    for r in br.reducers:
+        arenas += [a for a in r._fused.arenas() if a not in arenas]
+    for a in arenas:
+        for c in a.ctxs:
+            nat.cuda().gc_comm_set_step_from_device(c.handle, 1)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_once()                               # host-side steps (now 1) are frozen into the graph; the device adds its launch count
+    for replay in range(3):
+        graph.replay()
+        check(lambda j: 1 + nb + replay * nb + j, f"replay {replay}")
+    for r in br.reducers:
+        r._fused.ops.check()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_bucketed_graphed_reduce_across_gpus(dist_runner, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist_runner(_bucketed_body, world=world, backend="nccl")
