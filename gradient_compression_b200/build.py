@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "_lib")
 
 HOST_SOURCES = ["host_oracle.cpp"]
-CUDA_SOURCES = ["gc_kernels.cu", "gc_fused.cu", "gc_noalloc.cu", "gc_bn.cu", "gc_powersgd.cu", "gc_topk.cu", "gc_gemm_tc.cu", "gc_conv_tc.cu", "gc_varpack.cu", "gc_augment.cu"]
+CUDA_SOURCES = ["gc_kernels.cu", "gc_fused.cu", "gc_noalloc.cu", "gc_bn.cu", "gc_head.cu", "gc_powersgd.cu", "gc_topk.cu", "gc_gemm_tc.cu", "gc_conv_tc.cu", "gc_varpack.cu", "gc_augment.cu"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

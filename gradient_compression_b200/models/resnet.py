@@ -7,6 +7,7 @@ import torch.nn as nn
 
 from ..ops.bn import defer_batch_counters
 from ..ops.conv import GradLink, conv_bn_act
+from ..ops.head import head_loss
 from .layers import bn, conv, head_pool, linear
 
 
@@ -76,10 +77,20 @@ class ResNet(nn.Module):
             self.in_planes = planes * block.expansion
         return nn.Sequential(*blocks)
 
-    def forward(self, x):
+    def features(self, x):
         x = conv_bn_act(self.conv1, self.bn1, x)
-        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
-        return self.linear(head_pool(x, 4))
+        return self.layer4(self.layer3(self.layer2(self.layer1(x))))
+
+    def forward(self, x):
+        return self.linear(head_pool(self.features(x), 4))
+
+    def forward_loss(self, x, labels):
+        """``(loss, logits, [cross-entropy, top-1, top-5])``: pooling, the linear layer, the loss and the batch metrics in
+        one kernel when the final map is 4 x 4 (``F.avg_pool2d(out, 4)`` then covers it whole, models/resnet.py:106)."""
+        f = self.features(x)
+        if f.shape[2] == 4 and f.shape[3] == 4:
+            return head_loss(f, self.linear, labels)
+        return head_loss(head_pool(f, 4)[:, :, None, None], self.linear, labels)
 
 
 def ResNet18():

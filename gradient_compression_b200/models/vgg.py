@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch.nn as nn
 
 from ..ops.conv import conv_bn_act
+from ..ops.head import head_loss
 from .layers import bn, conv, linear
 
 CFG = {
@@ -31,6 +32,17 @@ class VGG(nn.Module):
         self.classifier = linear(512, 10)
 
     def forward(self, x):
+        return self.classifier(self._features(x).flatten(1))
+
+    def forward_loss(self, x, labels):
+        """``(loss, logits, [cross-entropy, top-1, top-5])`` with the linear layer, the loss and the batch metrics in one kernel
+        (the feature map is 1 x 1 after the fifth max-pool: models/vgg.py:88,109 of the reference)."""
+        f = self._features(x)
+        if f.shape[2] * f.shape[3] != 1:
+            f = f.flatten(1)[:, :, None, None]
+        return head_loss(f, self.classifier, labels)
+
+    def _features(self, x):
         mods = list(self.features)
         i = 0
         while i < len(mods):
@@ -42,7 +54,7 @@ class VGG(nn.Module):
             else:
                 x = m(x)
                 i += 1
-        return self.classifier(x.flatten(1))
+        return x
 
 
 def VGG11():

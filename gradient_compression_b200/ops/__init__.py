@@ -1,8 +1,9 @@
 """Native ops: every function dispatches on the tensor's device -- CPU tensors run the C++ oracle,
 CUDA tensors run the hand-written sm_100a kernel.  There is no PyTorch fallback on a GPU."""
-from . import _native, bn, conv, gemm, linalg, packing, philox, quant, topk
+from . import _native, bn, conv, gemm, head, linalg, packing, philox, quant, topk
 from .bn import bn_act
 from .conv import conv_bn_act
+from .head import head_loss
 from ._native import NativeError, launches
 from .linalg import gram_schmidt_, topk_abs_indices
 from .packing import bytepack, byteunpack, varpack, varunpack

@@ -123,6 +123,10 @@ def cuda():
         _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P, P])
         _declare(lib, "gc_cuda_bn_bwd_fused_limit", None, [c_i64])
         _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_head_supported", c_int, [c_int, c_int, c_int, c_int])
+        _declare(lib, "gc_cuda_head_scratch_bytes", c_i64, [c_int])
+        _declare(lib, "gc_cuda_head_forward", c_int, [P, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P, P, P])
+        _declare(lib, "gc_cuda_head_backward", c_int, [P, P, P, P, c_int, c_int, c_int, c_int, P, P, P, P])
         _declare(lib, "gc_cuda_psgd_max_rank", c_int, [])
         _declare(lib, "gc_cuda_psgd_p", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, c_i64, P])
         _declare(lib, "gc_cuda_psgd_gs", c_int, [P, P, c_int, c_float, P])

@@ -128,8 +128,7 @@ class GraphedStep:
         task.arena.detach_grads()
         if self._bucketed:
             self.reducer.start_step()
-        pred = task._model(x)
-        loss = task._criterion(pred, y)
+        loss, pred, m = task.forward_loss(x, y)
         loss.backward()
         if self._bucketed:
             self.bits_per_step = self.reducer.finish()          # joins the side stream; gradients are back in the arena
@@ -139,7 +138,8 @@ class GraphedStep:
         self.opt.step()
         loss = loss.detach()
         if self.evaluate:
-            m = task.evaluate_predictions(pred.detach(), y, loss)
+            if m is None:                         # no fused head: cross-entropy is the loss, top-1 / top-5 from torch ops
+                m = task.evaluate_predictions(pred.detach(), y, loss)
             self.metrics = {k: (v if torch.is_tensor(v) else torch.as_tensor(v)) for k, v in m.items()}
             # the three scalars side by side: one device-to-host copy reads a step's result
             self.metrics_vec = torch.stack([self.metrics[k].reshape(()).float() for k in

@@ -129,16 +129,31 @@ class CIFAR:
         else:
             self._model.zero_grad()
 
+    def forward_loss(self, imgs, labels):
+        """``(loss, logits, metrics)`` of a batch, the metrics as device scalars.  Models with a fused head (pooling, linear
+        layer, cross-entropy and top-1 / top-5 in one kernel: ``ops.head``) provide all three at once; for the others the
+        loss comes from the criterion and the metrics from ``evaluate_predictions``."""
+        fused = getattr(self._model, "forward_loss", None)
+        if fused is not None and labels.dtype == torch.int64:
+            loss, prediction, m = fused(imgs, labels)
+            metrics = {"cross_entropy_loss": m[0], "top1_accuracy": m[1], "top5_accuracy": m[2]}
+            return loss, prediction, metrics
+        prediction = self._model(imgs)
+        loss = self._criterion(prediction, labels)
+        return loss, prediction, None
+
     def batch_loss_with_gradients(self, batch):
         self.zero_grad()
         imgs, labels = batch
         with self._timer("batch.forward", float(self._epoch)):
-            prediction = self._model(imgs)
-            loss = self._criterion(prediction, labels)
+            loss, prediction, metrics = self.forward_loss(imgs, labels)
         with self._timer("batch.backward", float(self._epoch)):
             loss.backward()
         with self._timer("batch.evaluate", float(self._epoch)):
-            metrics = self.evaluate_predictions(prediction.detach(), labels, loss.detach())
+            if metrics is None:
+                metrics = self.evaluate_predictions(prediction.detach(), labels, loss.detach())
+            elif self._sync_metrics:
+                metrics = {k: v.item() for k, v in metrics.items()}
         grads = self.arena.grads() if self.arena is not None else [p.grad for p in self.parameters]
         return loss.detach(), grads, metrics
 

@@ -213,3 +213,42 @@ def test_bytepack_gpu_matches_host():
     w_host, w_dev = packing.bytepack(src), packing.bytepack(src.cuda())
     assert torch.equal(w_dev.cpu(), w_host)
     assert torch.equal(packing.byteunpack(w_dev, src.numel()).cpu(), src)
+
+
+@pytest.mark.parametrize("n,c,hw,k,bias", [(128, 2048, 4, 10, True), (128, 512, 1, 10, True), (7, 64, 3, 32, False), (33, 1024, 2, 10, True)])
+def test_head_kernels_match_torch(n, c, hw, k, bias):
+    """Average pool + linear + cross-entropy + top-1 / top-5 in one kernel, and its backward, against torch ops in fp32."""
+    import torch.nn.functional as F
+
+    from gradient_compression_b200.ops import head
+
+    g = torch.Generator().manual_seed(n + c + k)
+    feat = torch.randn(n, c, hw, hw, generator=g).cuda().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    ref_feat = feat.detach().clone(memory_format=torch.preserve_format).requires_grad_(True)
+    lin = torch.nn.Linear(c, k, bias=bias).cuda()
+    ref_lin = torch.nn.Linear(c, k, bias=bias).cuda()
+    ref_lin.load_state_dict(lin.state_dict())
+    labels = torch.randint(0, k, (n,), generator=g).cuda()
+    assert head.supported(feat, lin.weight, labels)
+    loss, logits, met = head.head_loss(feat, lin, labels)
+    (loss * 1.5).backward()
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        rl = ref_lin(ref_feat.mean((2, 3)))
+        rloss = F.cross_entropy(rl, labels)
+        (rloss * 1.5).backward()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    assert torch.allclose(logits, rl, rtol=1e-4, atol=1e-4)
+    assert float(loss) == pytest.approx(float(rloss), rel=1e-5)
+    top = rl.topk(min(5, k), 1)[1].eq(labels.view(-1, 1))
+    assert float(met[0]) == pytest.approx(float(rloss), rel=1e-5)
+    assert float(met[1]) == pytest.approx(float(top[:, 0].float().mean()), abs=1e-6)
+    assert float(met[2]) == pytest.approx(float(top.any(1).float().mean()), abs=1e-6)
+    assert torch.allclose(feat.grad, ref_feat.grad, rtol=1e-4, atol=1e-7)
+    assert torch.allclose(lin.weight.grad, ref_lin.weight.grad, rtol=1e-4, atol=1e-6)
+    if bias:
+        assert torch.allclose(lin.bias.grad, ref_lin.bias.grad, rtol=1e-4, atol=1e-6)
+    loss2, _, met2 = head.head_loss(feat.detach(), lin, labels)        # the ticket was reset: a second call gives the same
+    assert float(loss2) == float(loss) and torch.equal(met2, met)

@@ -189,6 +189,7 @@ def _resume_body(rank, world, root):
                 timer_mode="sync", lr=0.01, broadcast_parameters=True)
     first = TrainConfig(num_epochs=1, log_root=root, **base)
     train(rank, first, logger=Logger(first.as_dict(), rank, log_path=os.path.join(root, "run")))
+    torch.distributed.barrier()                  # every rank has written its files
     mine = torch.load(os.path.join(root, "run", f"train_state.rank{rank}.pt"), weights_only=False)
     other = torch.load(os.path.join(root, "run", f"train_state.rank{1 - rank}.pt"), weights_only=False)
     mem_mine, mem_other = mine["reducer"]["memory"], other["reducer"]["memory"]
