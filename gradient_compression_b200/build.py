@@ -93,8 +93,11 @@ def host_lib_path():
     return os.path.join(LIBDIR, "libgcb200_host.so")
 
 
-def cuda_lib_path():
-    return os.path.join(LIBDIR, "libgcb200_cuda.so")
+def cuda_lib_path(debug_bounds=False):
+    """``debug_bounds``: the build with -DGC_DEBUG_BOUNDS (computed gather / scatter indices checked before use, a failing
+    one recorded in the arena's status word instead of being followed); loaded instead of the regular library when
+    ``GCB200_DEBUG_BOUNDS=1``."""
+    return os.path.join(LIBDIR, "libgcb200_cuda_dbg.so" if debug_bounds else "libgcb200_cuda.so")
 
 
 def build_host(force=False, verbose=False):
@@ -136,12 +139,12 @@ def nvcc_path():
     return cand if os.path.exists(cand) else None
 
 
-def _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose):
+def _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose, defines=()):
     """One ``nvcc -c`` per source, all at once: the sources are independent translation units."""
     from concurrent.futures import ThreadPoolExecutor
 
     os.makedirs(objdir, exist_ok=True)
-    flags = NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-I", CSRC]
+    flags = NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-I", CSRC] + [f"-D{d}" for d in defines]
     if ptxas_info:
         flags = ["-Xptxas", "-v"] + flags
 
@@ -157,34 +160,36 @@ def _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose):
         return list(pool.map(one, srcs))
 
 
-def build_cuda(force=False, verbose=False, ptxas_info=False):
+def build_cuda(force=False, verbose=False, ptxas_info=False, debug_bounds=False):
     os.makedirs(LIBDIR, exist_ok=True)
     srcs = _sources(CUDA_SOURCES)
     nvcc = nvcc_path()
+    lib = cuda_lib_path(debug_bounds)
+    defines = ("GC_DEBUG_BOUNDS",) if debug_bounds else ()
     # what decides the result: compiler, flags and sources (the stamp also covers every header)
     recipe = [nvcc or "nvcc"] + NVCC_ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
-                                           "-I", CSRC, "-o", cuda_lib_path()] + srcs
+                                           "-I", CSRC, "-o", lib] + [f"-D{d}" for d in defines] + srcs
     digest = _digest(srcs, _flags_only(recipe))
-    if not force and not _stale(cuda_lib_path(), digest):
-        return cuda_lib_path()
+    if not force and not _stale(lib, digest):
+        return lib
     if nvcc is None:
-        raise RuntimeError("nvcc not found: cannot build libgcb200_cuda.so")
+        raise RuntimeError(f"nvcc not found: cannot build {os.path.basename(lib)}")
     with _BuildLock():
-        if force or _stale(cuda_lib_path(), digest):
-            objdir = os.path.join(LIBDIR, "obj")
+        if force or _stale(lib, digest):
+            objdir = os.path.join(LIBDIR, "obj_dbg" if debug_bounds else "obj")
             objs = []
             try:
-                objs = _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose)
-                link = [nvcc] + NVCC_ARCH + ["-shared", "-Xcompiler", "-fPIC", "-o", cuda_lib_path()] + objs
+                objs = _compile_cuda_objects(nvcc, srcs, objdir, ptxas_info, verbose, defines)
+                link = [nvcc] + NVCC_ARCH + ["-shared", "-Xcompiler", "-fPIC", "-o", lib] + objs
                 if verbose:
                     print(" ".join(link))
-                _compile(link, cuda_lib_path())
+                _compile(link, lib)
             finally:
                 for o in objs:
                     if os.path.exists(o):
                         os.remove(o)
-            _finish(cuda_lib_path(), digest)
-    return cuda_lib_path()
+            _finish(lib, digest)
+    return lib
 
 
 def build_all(force=False, verbose=False):
@@ -194,6 +199,9 @@ def build_all(force=False, verbose=False):
 if __name__ == "__main__":
     if "--sanitize" in sys.argv:
         print(build_host_sanitized(verbose=True))
+        sys.exit(0)
+    if "--debug-bounds" in sys.argv:
+        print(build_cuda("--force" in sys.argv, verbose=True, debug_bounds=True))
         sys.exit(0)
     force = "--force" in sys.argv
     print(build_host(force, verbose=True))

@@ -74,7 +74,21 @@ struct Waiter {
     atomicExch(&hdr->abort, 1u);
     __threadfence();
   }
+  // An index that would have gone outside its tensor: the access is not made; the first such index is kept beside
+  // STATUS_BOUNDS for the host (the launch carries on: other elements are unaffected).
+  __device__ __forceinline__ void out_of_bounds(long long index) {
+    if (atomicCAS(&hdr->status, 0u, (uint32_t)STATUS_BOUNDS) == 0u) hdr->status_detail = (uint32_t)index;
+  }
 };
+
+// Debug build (-DGC_DEBUG_BOUNDS, `python -m gradient_compression_b200.build --debug-bounds`): every computed index of the
+// gather / scatter paths is checked before use; a failing one is recorded (Waiter::out_of_bounds) and its access skipped.
+// The regular build keeps only the checks on indices that come from user data (the sparse exchange's index lists).
+#if defined(GC_DEBUG_BOUNDS)
+#define GC_INDEX_OK(w, i, n) (((i) >= 0 && (long long)(i) < (long long)(n)) ? true : ((w).out_of_bounds((long long)(i)), false))
+#else
+#define GC_INDEX_OK(w, i, n) true
+#endif
 
 // Per-rank grid barrier (generation counting, works for any block count per launch).
 __device__ __forceinline__ void grid_barrier(Waiter& w, int nblocks, int phase) {

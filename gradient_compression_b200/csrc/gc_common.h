@@ -160,8 +160,7 @@ enum : uint32_t {
 enum : int {
   STATUS_OK = 0,
   STATUS_TIMEOUT = 1,      // a bounded wait on a peer flag ran out
-  STATUS_BAD_ARG = 2,
-  STATUS_BOUNDS = 3,       // debug bounds check failed; index recorded next to the status
+  STATUS_BOUNDS = 3,       // an index outside its tensor was met (and not followed); the first one is recorded next to the status
 };
 
 }  // namespace gc

@@ -699,7 +699,8 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
   // gather the K selected coordinates first (the dense pass below may overwrite them in place)
   float m = 0.0f;
   for (int64_t i = tid; i < k; i += stride) {
-    float x = v.in[perm_eval(p.perm, (uint64_t)(start + i))];
+    const uint64_t at = perm_eval(p.perm, (uint64_t)(start + i));
+    float x = GC_INDEX_OK(w, at, n) ? v.in[at] : 0.0f;
     vals[i] = x;
     m = fmaxf(m, abs_for_max(x));
   }
@@ -782,7 +783,8 @@ __global__ void __launch_bounds__(THREADS) randk_fused_kernel(LaunchViews lv, Ra
     for (int src = 0; src < MAXW; ++src)
       if (src < world) acc += reinterpret_cast<const int32_t*>(v.arena[src] + p.off_levels + par_off)[i];
     bool hi = two && vals[i] != 0.0f;
-    v.out[perm_eval(p.perm, (uint64_t)(start + i))] = mul_rn(hi ? dq_hi : dq_lo, (float)acc);
+    const uint64_t at = perm_eval(p.perm, (uint64_t)(start + i));
+    if (GC_INDEX_OK(w, at, n)) v.out[at] = mul_rn(hi ? dq_hi : dq_lo, (float)acc);
   }
 }
 
@@ -832,6 +834,7 @@ __global__ void __launch_bounds__(THREADS, 2) sparse_fused_kernel(LaunchViews lv
     for (int64_t i = tid; i < p.count; i += stride) {
       int32_t at = idx[i];
       if (at >= 0 && at < n) v.out[at] += p.alpha * val[i];
+      else w.out_of_bounds(at);                 // an index list from outside this library: reported, never followed
     }
     if (src + 1 < world) grid_barrier(w, c.nblocks, 0x71);
   }
@@ -1027,6 +1030,15 @@ int gc_comm_status_async(void* ctx, uint32_t* pinned_out2, void* cs) {
   CommCtx* c = (CommCtx*)ctx;
   ArenaHeader* h = (ArenaHeader*)c->local;
   return (int)cudaMemcpyAsync(pinned_out2, &h->status, 8, cudaMemcpyDeviceToHost, (cudaStream_t)cs);
+}
+
+// 1 when this library was built with the debug bounds checks.
+int gc_comm_debug_bounds() {
+#if defined(GC_DEBUG_BOUNDS)
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 int gc_comm_clear_status(void* ctx, void* cs) {

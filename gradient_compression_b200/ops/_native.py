@@ -90,9 +90,10 @@ def cuda():
     """The CUDA kernel library.  Raises when it cannot be loaded: there is no eager fallback."""
     global _cuda
     if _cuda is None:
-        path = _build.cuda_lib_path()
+        debug = os.environ.get("GCB200_DEBUG_BOUNDS") == "1"      # the build whose gather / scatter indices are checked
+        path = _build.cuda_lib_path(debug)
         try:
-            path = _build.build_cuda()  # no-op when up to date
+            path = _build.build_cuda(debug_bounds=debug)  # no-op when up to date
         except Exception as exc:
             if not os.path.exists(path):
                 raise NativeError(f"libgcb200_cuda.so is missing and could not be built: {exc}") from exc
@@ -176,6 +177,7 @@ def cuda():
         _declare(lib, "gc_comm_status", c_int, [P, P, P])
         _declare(lib, "gc_comm_status_async", c_int, [P, P, P])
         _declare(lib, "gc_comm_clear_status", c_int, [P, P])
+        _declare(lib, "gc_comm_debug_bounds", c_int, [])
         _declare(lib, "gc_comm_destroy", c_int, [P])
         _declare(lib, "gc_fused_qsgd", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_u64, c_u32, c_int, c_int, P])
         _declare(lib, "gc_fused_twoscale", c_int, [PP, c_int, PP, PP, c_i64, c_int, c_int, c_u64, c_u32, c_int,

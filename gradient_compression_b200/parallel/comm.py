@@ -16,7 +16,7 @@ import torch.distributed as dist
 
 from ..ops import _native as nat
 
-STATUS_OK, STATUS_TIMEOUT, STATUS_BAD_ARG, STATUS_BOUNDS = 0, 1, 2, 3
+STATUS_OK, STATUS_TIMEOUT, STATUS_BOUNDS = 0, 1, 3
 
 
 class CollectiveTimeout(RuntimeError):
@@ -26,6 +26,15 @@ class CollectiveTimeout(RuntimeError):
         super().__init__(f"rank {rank}: fused collective timed out in phase 0x{phase:x} waiting for "
                          f"{'a local block' if peer == 0xfffe else f'rank {peer}'}")
         self.rank, self.phase, self.peer = rank, phase, peer
+
+
+class IndexOutOfBounds(RuntimeError):
+    """A kernel met an index outside its tensor (an index list handed to the sparse exchange, or -- in the debug-bounds
+    build -- any computed gather / scatter index).  The access was skipped; ``index`` is the first such value."""
+
+    def __init__(self, rank, index):
+        super().__init__(f"rank {rank}: index {index} is outside the tensor; the access was skipped")
+        self.rank, self.index = rank, index
 
 
 def _ck(err, what):
@@ -71,15 +80,24 @@ class _ArenaBase:
         return ctx_arr, n, in_arr, out_arr
 
     def check(self):
-        """Raise ``CollectiveTimeout`` if a kernel recorded a failure; synchronises the stream."""
+        """Raise ``CollectiveTimeout`` / ``IndexOutOfBounds`` if a kernel recorded a failure; synchronises the stream.  Every
+        rank's status word is read and cleared before the first failure is raised, so the next launch starts clean."""
+        first = None
         for c in self.ctxs:
             status, detail = c.status()
+            if status == STATUS_OK:
+                continue
+            c.clear_status()
+            if first is not None:
+                continue
             if status == STATUS_TIMEOUT:
-                c.clear_status()
-                raise CollectiveTimeout(c.rank, detail >> 16, detail & 0xFFFF)
-            if status != STATUS_OK:
-                c.clear_status()
-                raise nat.NativeError(f"fused kernel reported status {status} (detail {detail})")
+                first = CollectiveTimeout(c.rank, detail >> 16, detail & 0xFFFF)
+            elif status == STATUS_BOUNDS:
+                first = IndexOutOfBounds(c.rank, detail - (1 << 32) if detail >= (1 << 31) else detail)
+            else:
+                first = nat.NativeError(f"fused kernel reported status {status} (detail {detail})")
+        if first is not None:
+            raise first
 
     def close(self):
         for c in self.ctxs:

@@ -224,3 +224,105 @@ def test_bounded_wait_reports_timeout_and_context_survives():
         assert float(ops.absmax(x)) > 0        # the CUDA context is alive
     finally:
         grp.close()
+
+
+def test_out_of_range_index_is_reported_and_never_followed():
+    """An index list with entries outside the tensor (what a buggy caller could hand to the sparse exchange): the kernel
+    skips those entries, applies the others, and the host gets STATUS_BOUNDS with the first bad index."""
+    from gradient_compression_b200.parallel import comm
+
+    n, count, world = 5003, 64, 2
+    grp, fo = _group(world, n)
+    try:
+        g = torch.Generator().manual_seed(9)
+        idxs = [torch.randperm(n, generator=g)[:count].to(torch.int32) for _ in range(world)]
+        idxs[1][5] = n + 11                        # outside: must be skipped, not written
+        idxs[1][6] = -3
+        vals = [torch.randn(count, generator=g) for _ in range(world)]
+        canary = torch.full((n + 64,), 7.0, device="cuda")
+        outs = [canary[:n], torch.full((n,), 7.0, device="cuda")]
+        fo.sparse([v.cuda() for v in vals], outs, [i.cuda() for i in idxs], 1.0 / world)
+        with pytest.raises(comm.IndexOutOfBounds) as e:
+            fo.check()
+        assert e.value.index in (n + 11, -3)
+        expect = torch.zeros(n)
+        for r, (i, v) in enumerate(zip(idxs, vals)):
+            keep = (i >= 0) & (i < n)
+            expect[i[keep].long()] += (1.0 / world) * v[keep]
+        assert torch.equal(outs[0].cpu(), expect) and torch.equal(outs[1].cpu(), expect)
+        assert float(canary[n:].min()) == 7.0 and float(canary[n:].max()) == 7.0      # nothing beyond the tensor was touched
+        fo.sparse([v.cuda() for v in vals], outs, [i.clamp(0, n - 1).cuda() for i in idxs], 1.0 / world)
+        fo.check()                                 # the status was cleared: a clean launch reports nothing
+    finally:
+        grp.close()
+
+
+def test_debug_bounds_build_runs_the_same_kernels():
+    """The -DGC_DEBUG_BOUNDS build (every computed gather / scatter index checked before use) in a process of its own:
+    Rand-K on an emulated group gives the regular build's result and reports no index, and a bad index handed to the
+    sparse exchange is reported there too."""
+    import subprocess
+    import sys
+
+    code = r'''
+import torch
+from gradient_compression_b200.ops import _native as nat
+from gradient_compression_b200.parallel import comm
+from gradient_compression_b200.parallel.engine import FusedOps
+assert nat.cuda().gc_comm_debug_bounds() == 1
+n, world = 40003, 2
+grp = comm.LocalGroup(world, comm.required_bytes(n))
+fo = FusedOps(grp, timeout_ms=5000)
+xs = [torch.randn(n, generator=torch.Generator().manual_seed(r)).cuda() for r in range(world)]
+outs = [torch.empty(n, device="cuda") for _ in range(world)]
+fo.randk(xs, outs, 5, 0, n - 700, 1000, 8, 0, False, 0)     # a window that ends at the edge of the tensor
+fo.check()
+print("RANDK", float(outs[0].double().sum()), float(outs[1].double().abs().sum()))
+idx = [torch.arange(10, dtype=torch.int32).cuda(), torch.tensor([1, 2, n + 1] + [3] * 7, dtype=torch.int32).cuda()]
+try:
+    fo.sparse([torch.ones(10).cuda()] * 2, outs, idx, 0.5)
+    fo.check()
+    print("NO ERROR")
+except comm.IndexOutOfBounds as e:
+    print("BOUNDS", e.index)
+grp.close()
+'''
+    import os
+
+    def run(debug):
+        env = dict(os.environ, GCB200_DEBUG_BOUNDS="1" if debug else "0")
+        src = code if debug else code.replace("== 1", "== 0")
+        out = subprocess.run([sys.executable, "-c", src], env=env, capture_output=True, text=True, timeout=600,
+                             cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert out.returncode == 0, out.stderr[-2000:]
+        return [l for l in out.stdout.splitlines() if l.startswith(("RANDK", "BOUNDS", "NO ERROR"))]
+
+    dbg, rel = run(True), run(False)
+    assert dbg == rel and dbg[1] == f"BOUNDS {40003 + 1}", (dbg, rel)
+
+
+@pytest.mark.parametrize("world,bits", [(1, 8), (2, 4), (4, 2), (8, 8)])
+def test_fused_qsgd_against_a_plain_pytorch_restatement(world, bits):
+    """An oracle that shares no code with the kernels: inputs whose levels |x| / norm * s are whole numbers leave the
+    stochastic rounding nothing to round (its probability is 0), so the result must be the plain mean of the inputs --
+    written here with torch ops only, without the quantiser or the Philox stream of the native library."""
+    n = 30011
+    s = (1 << bits) - 1
+    grp, fo = _group(world, n)
+    try:
+        g = torch.Generator().manual_seed(world * 100 + bits)
+        xs = [torch.randint(-s, s + 1, (n,), generator=g).float() for _ in range(world)]
+        xs[0][17] = float(s)                               # the max-norm is exactly s: level = |x|
+        scale = 0.03125                                    # a power of two keeps every quotient exact
+        ins = [(x * scale).cuda() for x in xs]
+        outs = [torch.empty(n, device="cuda") for _ in range(world)]
+        fo.qsgd(ins, outs, bits, 1234, 5)
+        fo.check()
+        levels = torch.stack(xs).sum(0)                    # sum of the signed integer levels
+        norm = torch.tensor(s * scale)
+        expect = levels * (norm / (s * world))             # dequantise: norm / (s W) * sum of levels, in fp32
+        for o in outs:
+            assert torch.allclose(o.cpu(), expect, rtol=2e-7, atol=0.0)
+            assert torch.allclose(o.cpu(), torch.stack(xs).sum(0) * scale / world, rtol=1e-6, atol=0.0)
+    finally:
+        grp.close()
