@@ -190,6 +190,100 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
   }
 }
 
+// Taps of a stride-2 convolution that reach input pixels of parity `par` along one axis: r = par + pad - 2 d for d = 0, 1, ...
+// while 0 <= r < R.  Returns their count; the d-th tap reads the output gradient at offset +d.
+static int class_taps(int par, int pad, int R) {
+  int count = 0;
+  for (int d = 0;; ++d) {
+    const int r = par + pad - 2 * d;
+    if (r < 0) break;
+    if (r < R) ++count;
+    else if (count == 0) continue;     // (r >= R before the first valid tap: keep looking at smaller r)
+  }
+  return count;
+}
+
+// The first offset d of that list (taps with r >= R are skipped from the front).
+static int class_first(int par, int pad, int R) {
+  for (int d = 0;; ++d) {
+    const int r = par + pad - 2 * d;
+    if (r < 0) return 0;
+    if (r < R) return d;
+  }
+}
+
+// 1 when the input gradient of this stride-2 convolution can run on the tensor cores: H and W even, Cout (the contraction)
+// a multiple of 32, Cin a multiple of 4 and >= 32, 128 consecutive pixels of the half-resolution grid form one box, and
+// every parity class starts its taps at offset 0 (true for R = 1, pad 0 and R = 3, pad 1).
+int gc_cuda_conv_dgrad_s2_supported(int N, int H, int W, int Cin, int Cout, int R, int pad) {
+  Shape s;
+  if ((H & 1) || (W & 1) || !make_shape(N, H, W, Cin, Cout, R, 2, pad, &s) || s.Ho != H / 2 || s.Wo != W / 2) return 0;
+  if ((Cout & 31) || (Cin & 3) || Cin < 32) return 0;
+  for (int par = 0; par < 2; ++par)
+    if (class_first(par, pad, R) != 0) return 0;
+  int bw, bh, bn;
+  return box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr ? 1 : 0;
+}
+
+// Floats of the per-class filter copies the kernel reads (see gc_cuda_conv_dgrad_s2): R * R * Cin * Cout.
+// dx[N, H, W, Cin] = input gradient of conv2d(x, w, stride 2, pad) given dy[N, H/2, W/2, Cout].  One launch per parity class
+// (ph, pw) of input pixels: the pixels (2i + ph, 2j + pw) receive a stride-1 convolution of dy with the taps
+// r = ph + pad - 2 fr, s = pw + pad - 2 fs, and are written through a 4-D store map over that strided sub-grid of dx.
+// wd: the filter copies class after class in the order (0,0), (0,1), (1,0), (1,1); class c is the matrix
+// [Cin, th * tw * Cout] with wd_c[ci][fr][fs][co] = w[co][ph + pad - 2 fr][pw + pad - 2 fs][ci].  Classes without taps
+// (a 1x1 filter reaches only the even pixels) are zero: dx is cleared first when there is one.
+int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, int H, int W, int Cin, int Cout, int R, int pad,
+                          int* error_flag, void* cs) {
+  if (!gc_cuda_conv_dgrad_s2_supported(N, H, W, Cin, Cout, R, pad)) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(wd) & 15u) || (reinterpret_cast<uintptr_t>(dx) & 15u))
+    return (int)cudaErrorInvalidValue;
+  cudaStream_t st = (cudaStream_t)cs;
+  const int Ho = H / 2, Wo = W / 2, M = N * Ho * Wo;
+  bool any_empty = false;
+  for (int c = 0; c < 4; ++c) any_empty |= class_taps(c >> 1, pad, R) * class_taps(c & 1, pad, R) == 0;
+  if (any_empty) {
+    cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)N * H * W * Cin * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  Shape sy{N, Ho, Wo, Cout, Cin, 1, 1, 0, Ho, Wo};          // the class problem reads dy at stride 1, no padding
+  int bw, bh, bn;
+  box_for(BM, Ho, Wo, &bw, &bh, &bn);
+  EncodeTiledFn fn = encode_fn();
+  int64_t w_off = 0;
+  for (int c = 0; c < 4; ++c) {
+    const int ph = c >> 1, pw = c & 1;
+    const int th = class_taps(ph, pad, R), tw = class_taps(pw, pad, R);
+    if (th * tw == 0) continue;
+    const int K = th * tw * Cout;
+    const int tile = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, Cin, K);
+    CUtensorMap ma, mb, mc;
+    if (make_map_nhwc(&ma, dy, sy, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0 || make_map(&mb, wd + w_off, Cin, K, K, tile) != 0)
+      return (int)cudaErrorInvalidValue;
+    {   // pixels (2i + ph, 2j + pw) of dx as the 4-D tensor {Cin, W/2, H/2, N}
+      cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)N};
+      cuuint64_t strides[3] = {(cuuint64_t)2 * Cin * 4, (cuuint64_t)2 * W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+      cuuint32_t box[4] = {32, (cuuint32_t)bw, (cuuint32_t)bh, (cuuint32_t)bn};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      if (fn(&mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)(dx + ((int64_t)ph * W + pw) * Cin), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return (int)cudaErrorInvalidValue;
+    }
+    const ConvA ca{th * tw, tw, Cout / 32, Ho * Wo, Wo, 1, 0};
+    const ConvC cc{Ho * Wo, Wo};
+    int err;
+    switch (tile) {
+      case 64: err = launch_persistent_maps<64>(ma, mb, mc, ca, nullptr, M, Cin, K, 0, nullptr, error_flag, st, nullptr, &cc); break;
+      case 128: err = launch_persistent_maps<128>(ma, mb, mc, ca, nullptr, M, Cin, K, 0, nullptr, error_flag, st, nullptr, &cc); break;
+      case 256: err = launch_persistent_maps<256>(ma, mb, mc, ca, nullptr, M, Cin, K, 0, nullptr, error_flag, st, nullptr, &cc); break;
+      default: err = (int)cudaErrorInvalidValue;
+    }
+    if (err != 0) return err;
+    w_off += (int64_t)Cin * K;
+  }
+  return 0;
+}
+
 // Rows of Kp = 32-float-padded filter taps for a stride-1 convolution with few input channels (the 3-channel stem):
 // A[N*H*W, Kp] from x[N, H, W, Cin], and (when wpad is given) the filter w[Cout, R*R*Cin] padded to wpad[Cout, Kp].
 int gc_cuda_im2col_small(const float* x, float* A, int N, int H, int W, int Cin, int R, int pad, int Kp, const float* w,

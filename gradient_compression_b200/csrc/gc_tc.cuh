@@ -143,6 +143,14 @@ struct ConvA {
   int stride, pad;
 };
 
+// Where the rows of the OUTPUT go when it is not a matrix but a strided sub-grid of an NHWC tensor read through a 4-D map
+// {C, W', H', N} (the input gradient of a stride-2 convolution: one launch per parity class of input pixels): row
+// p = (n, i, j) of the result is stored at coordinates (column, j, i, n).  hw == 0: a plain 2-D matrix.
+struct ConvC {
+  int hw;          // rows per image (H' * W'), 0 = plain matrix
+  int w;           // W'
+};
+
 // Batch-norm statistics finished inside the GEMM that produces the activation: every CTA keeps per-column sums and sums
 // of squares of its tiles, adds them to `acc` ([2][N] doubles, zero on entry) with atomics when it is done, and the
 // epilogue group that draws the last ticket turns the totals into mean / 1 / sqrt(var + eps) (`stats`, [2N] floats),
@@ -282,7 +290,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                             const __grid_constant__ CUtensorMap tma_c, const ConvA ca, const float* __restrict__ bias, int M, int N, int K,
                             int tiles_m, int tiles_n, int accumulate, float* __restrict__ col_partials,
-                            int* __restrict__ error_flag, int tma_mode, const BnFin fin) {
+                            int* __restrict__ error_flag, int tma_mode, const BnFin fin, const ConvC cc) {
   using S = PSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -450,7 +458,13 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
         group_bar(grp);
         if (issuer) {
           if (n0 + sl * 32 < N) {
-            if (accumulate)                      // C += tile: the add happens in L2, C is never read by the SM
+            if (cc.hw != 0) {                    // rows = pixels (n, i, j) of a strided sub-grid: 4-D store map
+              const int img = m0 / cc.hw, rem = m0 - img * cc.hw;
+              const int i0 = rem / cc.w, j0 = rem - i0 * cc.w;
+              asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                           ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(j0), "r"(i0), "r"(img)
+                           : "memory");
+            } else if (accumulate)               // C += tile: the add happens in L2, C is never read by the SM
               asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                            ::"l"(&tma_c), "r"(smem_u32(slab)), "r"(n0 + sl * 32), "r"(m0)
                            : "memory");
@@ -815,7 +829,7 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
 template <int BN>
 int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const ConvA& ca, const float* bias,
                            int M, int N, int K, int accumulate, float* col_partials, int* error_flag, cudaStream_t st,
-                           const BnFin* fin = nullptr) {
+                           const BnFin* fin = nullptr, const ConvC* cc = nullptr) {
   using S = PSmem<BN>;
   static bool configured = false;
   if (!configured) {
@@ -833,7 +847,7 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
     f = *fin;
   }
   gc::launch_pdl(gemm_tf32_persistent_kernel<BN>, dim3((unsigned)grid), dim3(PERSISTENT_THREADS), (size_t)S::TOTAL, st, ma, mb, mc, ca,
-                 bias, M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag, gctc::tma_mode, f);
+                 bias, M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag, gctc::tma_mode, f, cc != nullptr ? *cc : ConvC{0, 0});
   return (int)cudaGetLastError();
 }
 

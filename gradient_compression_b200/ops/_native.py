@@ -149,6 +149,8 @@ def cuda():
         _declare(lib, "gc_cuda_tc_tma_mode", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
         _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P, P])
+        _declare(lib, "gc_cuda_conv_dgrad_s2_supported", c_int, [c_int] * 7)
+        _declare(lib, "gc_cuda_conv_dgrad_s2", c_int, [P, P, P] + [c_int] * 7 + [P, P])
         _declare(lib, "gc_cuda_conv_wgrad_supported", c_int, [c_int] * 8)
         _declare(lib, "gc_cuda_conv_wgrad", c_int, [P, P, P] + [c_int] * 8 + [P, P])
         _declare(lib, "gc_cuda_im2col_small", c_int, [P, P] + [c_int] * 7 + [P, P, c_int, P])

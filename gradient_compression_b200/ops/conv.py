@@ -14,9 +14,10 @@ The epilogue of each emits the per-channel sums the batch norm needs, so the act
 (by the apply pass).  Backward: fused BN backward kernels; input gradient on the same kernels with the filter rotated
 by 180 degrees and its channel axes swapped (one batched kernel refreshes those copies after every optimiser step;
 in identity blocks the product is added straight onto the skip connection's gradient: ``GradLink``); weight gradient
-``dY^T X`` on the split-K kernel with MN-major operands, per filter tap from shifted boxes.  Input gradients of
-strided convolutions, grouped convolutions and shapes the tilings exclude use cuDNN through ``bn_act(bn, conv(x))``
-or ``aten.convolution_backward``.
+``dY^T X`` on the split-K kernel with MN-major operands, per filter tap from shifted boxes.  The input gradient of a
+stride-2 convolution is four launches of the forward kernel, one per parity class of input pixels, each writing its
+pixels through a strided 4-D store map.  Grouped convolutions and shapes the tilings exclude use cuDNN through
+``bn_act(bn, conv(x))`` or ``aten.convolution_backward``.
 
 The reference builds the same layers from ``nn.Conv2d`` + ``nn.BatchNorm2d`` + ``F.relu`` module calls
 (models/resnet.py:45-76, models/vgg.py:96-110 of the reference).
@@ -47,18 +48,31 @@ MIN_ROWS = int(os.environ.get("GCB200_TC_CONV_MIN_ROWS", "0"))
 # Batch-norm statistics finished inside the producing kernel (off: per-tile partial sums + a separate finalize kernel).
 FUSED_FINALIZE = os.environ.get("GCB200_BN_FUSED_FINALIZE", "0") == "1"
 
-# Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem".
-PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem").split(","))
+# Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem", "dgrad_s2" (own input gradient of
+# stride-2 convolutions; without it cuDNN computes those).
+PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem,dgrad_s2").split(","))
 
 
 def _taps(w):
     return w.shape[2] * w.shape[3]
 
 
+def _s2_classes(r, pad):
+    """Parity classes (ph, pw) of the input pixels of a stride-2 convolution, in the order the kernel walks them, each with
+    the filter taps that reach it: ``(taps_h, taps_w)`` where tap d of an axis is filter index ``par + pad - 2 d``."""
+    def axis(par):
+        return [par + pad - 2 * d for d in range(r + pad + 1) if 0 <= par + pad - 2 * d < r]
+
+    return [(ph, pw, axis(ph), axis(pw)) for ph in (0, 1) for pw in (0, 1)]
+
+
 class _DgradWeights:
-    """The filter as the input-gradient kernel reads it: ``[Cin, taps * Cout]`` with tap ``t`` holding the transpose of
-    the forward filter's tap ``taps - 1 - t`` (rotation by 180 degrees, channel axes swapped).  For a 1x1 filter that
-    is the plain transpose ``[Cin, Cout]``.
+    """The filter as the input-gradient kernels read it.
+
+    Stride 1: ``[Cin, taps * Cout]`` with tap ``t`` holding the transpose of the forward filter's tap ``taps - 1 - t``
+    (rotation by 180 degrees, channel axes swapped); for a 1x1 filter that is the plain transpose ``[Cin, Cout]``.
+    Stride 2: one such matrix per parity class of input pixels, back to back, class ``(ph, pw)`` holding
+    ``[Cin][fr][fs][Cout] = w[Cout][ph + pad - 2 fr][pw + pad - 2 fs][Cin]`` (``csrc/gc_conv_tc.cu``).
 
     A copy is valid while the weight's version counter and storage are the ones it was made from; the backward of
     a layer redoes a stale copy on the spot.  Kernels that write parameters through raw pointers do not move
@@ -67,19 +81,29 @@ class _DgradWeights:
     what a captured step graph replays."""
 
     def __init__(self):
-        self.entries = {}          # id(weight) -> [weakref, wd, version, data_ptr]
+        self.entries = {}          # (id(weight), stride) -> [weakref, wd, version, data_ptr, stride, pad]
 
-    def get(self, w):
-        e = self.entries.get(id(w))
+    def get(self, w, stride=1, pad=None):
+        key = (id(w), stride)
+        e = self.entries.get(key)
         if e is None or e[0]() is not w or e[3] != w.data_ptr() or e[1].device != w.device:
-            e = [weakref.ref(w), torch.empty(w.shape[1], _taps(w) * w.shape[0], dtype=torch.float32, device=w.device), -1,
-                 w.data_ptr()]
-            self.entries[id(w)] = e
+            shape = (w.shape[1], _taps(w) * w.shape[0]) if stride == 1 else (_taps(w) * w.shape[0] * w.shape[1],)
+            e = [weakref.ref(w), torch.empty(shape, dtype=torch.float32, device=w.device), -1, w.data_ptr(), stride, pad]
+            self.entries[key] = e
             if len(self.entries) % 64 == 0:
                 self.entries = {k: v for k, v in self.entries.items() if v[0]() is not None}
         if e[2] != w._version:
             cout, cin, r, s = w.shape
-            e[1].view(cin, r, s, cout).copy_(w.detach().flip(2, 3).permute(1, 2, 3, 0))
+            if stride == 1:
+                e[1].view(cin, r, s, cout).copy_(w.detach().flip(2, 3).permute(1, 2, 3, 0))
+            else:
+                off = 0
+                for _, _, th, tw in _s2_classes(r, pad):
+                    if th and tw:
+                        n = cin * len(th) * len(tw) * cout
+                        sub = w.detach()[:, :, th][:, :, :, tw]                       # [Cout, Cin, th, tw]
+                        e[1][off: off + n].view(cin, len(th), len(tw), cout).copy_(sub.permute(1, 2, 3, 0))
+                        off += n
             e[2] = w._version
         return e[1]
 
@@ -87,10 +111,35 @@ class _DgradWeights:
         for e in self.entries.values():
             e[2] = -1
 
+    @staticmethod
+    def _rows(e, tiles):
+        """Table rows {src, dst, rows, cols, first tile, src pitch, dst pitch} of the batched transpose for one entry."""
+        w = e[0]()
+        cout, cin, r, taps = w.shape[0], w.shape[1], w.shape[2], _taps(w)
+        per = ((cout + 31) // 32) * ((cin + 31) // 32)
+        rows = []
+        if e[4] == 1:
+            for t in range(taps):       # tap t of [Cout][taps][Cin] -> tap (taps - 1 - t) of [Cin][taps][Cout]
+                rows.append([w.data_ptr() + 4 * t * cin, e[1].data_ptr() + 4 * (taps - 1 - t) * cout, cout, cin, tiles,
+                             taps * cin, taps * cout])
+                tiles += per
+        else:
+            off = 0
+            for _, _, th, tw in _s2_classes(r, e[5]):
+                nt = len(th) * len(tw)
+                for a, fr in enumerate(th):
+                    for b, fs in enumerate(tw):      # filter tap (fr, fs) -> tap (a, b) of this class's [Cin][th][tw][Cout]
+                        rows.append([w.data_ptr() + 4 * (fr * w.shape[3] + fs) * cin, e[1].data_ptr() + 4 * (off + (a * len(tw) + b) * cout),
+                                     cout, cin, tiles, taps * cin, nt * cout])
+                        tiles += per
+                off += cin * nt * cout
+        return rows, tiles
+
     def refresh(self, owner, params):
         """One launch for every registered weight among ``params``; the pointer table and the buffers it names are
         kept on ``owner`` so that they live as long as a graph that replays the launch."""
-        mine = [e for e in (self.entries.get(id(p)) for p in params) if e is not None and e[0]() is not None and e[0]().is_cuda]
+        mine = [e for p in params for e in (self.entries.get((id(p), 1)), self.entries.get((id(p), 2)))
+                if e is not None and e[0]() is not None and e[0]().is_cuda]
         if not mine:
             return
         key = tuple((e[0]().data_ptr(), e[1].data_ptr()) for e in mine)
@@ -101,13 +150,8 @@ class _DgradWeights:
                                    "eager step (forward, backward, optimiser) before capturing")
             rows, tiles = [], 0
             for e in mine:
-                w = e[0]()
-                cout, cin, taps = w.shape[0], w.shape[1], _taps(w)
-                per = ((cout + 31) // 32) * ((cin + 31) // 32)
-                for t in range(taps):       # tap t of [Cout][taps][Cin] -> tap (taps - 1 - t) of [Cin][taps][Cout]
-                    rows.append([w.data_ptr() + 4 * t * cin, e[1].data_ptr() + 4 * (taps - 1 - t) * cout, cout, cin, tiles,
-                                 taps * cin, taps * cout])
-                    tiles += per
+                more, tiles = self._rows(e, tiles)
+                rows += more
             state = (key, torch.tensor(rows, dtype=torch.int64).to(mine[0][1].device), tiles, [e[1] for e in mine])
             owner._dgrad_weight_table = state
         _, table, tiles, _ = state
@@ -339,6 +383,16 @@ class _ConvBNAct(torch.autograd.Function):
                     else:
                         conv_forward(dconv, wd_, None, 1, r - 1 - pad, out=dx, accumulate=accumulate)
                     if acc is not None and not accumulate:
+                        dx += acc
+                elif (mode == "conv" and stride == 2 and "dgrad_s2" in PATHS
+                      and lib.gc_cuda_conv_dgrad_s2_supported(n, x.shape[2], x.shape[3], cin, cout, r, pad)):
+                    # one launch per parity class of input pixels, each a stride-1 convolution of dY written through a
+                    # strided 4-D store map
+                    dx = torch.empty_like(x)
+                    nat.check(lib.gc_cuda_conv_dgrad_s2(dconv.data_ptr(), _dgrad_weights.get(w, 2, pad).data_ptr(), dx.data_ptr(), n,
+                                                        x.shape[2], x.shape[3], cin, cout, r, pad, _err(x.device), st()),
+                              "conv_dgrad_s2")
+                    if acc is not None:
                         dx += acc
                 else:
                     dx = torch.ops.aten.convolution_backward(dconv, x, w, None, [stride, stride], [pad, pad], [1, 1], False,

@@ -143,6 +143,7 @@ def test_dgrad_filter_refresh_kernel_matches_torch():
           for c_out, c_in, r in [(64, 64, 3), (96, 40, 1), (128, 64, 3), (32, 256, 1)]]
     table = conv._DgradWeights()
     expect = [table.get(w).clone() for w in ws]            # torch path (flip + permute)
+    expect2 = [table.get(w, 2, (w.shape[2] - 1) // 2).clone() for w in ws]       # stride-2 layout: one matrix per parity class
     for e in table.entries.values():
         e[1].zero_()
     table.invalidate()
@@ -152,8 +153,30 @@ def test_dgrad_filter_refresh_kernel_matches_torch():
 
     table.refresh(Owner(), ws)
     torch.cuda.synchronize()
-    for w, want in zip(ws, expect):
-        assert torch.equal(table.entries[id(w)][1], want)
+    for w, want, want2 in zip(ws, expect, expect2):
+        assert torch.equal(table.entries[(id(w), 1)][1], want)
+        assert torch.equal(table.entries[(id(w), 2)][1], want2)
+
+
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[6] == 2] + [(3, 8, 8, 64, 96, 3, 2, 1), (5, 4, 4, 128, 64, 1, 2, 0)])
+def test_conv_stride2_input_gradient_exact_on_small_integers(shape):
+    """Four launches, one per parity class of input pixels, each storing through a strided 4-D map."""
+    from gradient_compression_b200.ops import conv, gemm
+
+    n, h, w, cin, cout, r, stride, pad = shape
+    g = torch.Generator().manual_seed(sum(shape) + 4)
+    x = _cl(_ints((n, cin, h, w), g).cuda())
+    wt = _cl(_ints((cout, cin, r, r), g, -2, 3).cuda())
+    dy = _cl(_ints((n, cout, h // 2, w // 2), g).cuda())
+    lib = conv.nat.cuda()
+    assert lib.gc_cuda_conv_dgrad_s2_supported(n, h, w, cin, cout, r, pad)
+    ref = _conv_backward64(dy, x, wt, 2, pad, 0)
+    wd = conv._dgrad_weights.get(wt, 2, pad)
+    dx = torch.full_like(x, 7.0)
+    conv.nat.check(lib.gc_cuda_conv_dgrad_s2(dy.data_ptr(), wd.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, pad,
+                                             gemm._error_flag(x.device).data_ptr(), conv.nat.stream_ptr()), "conv_dgrad_s2")
+    gemm.check()
+    _same(dx, ref)
 
 
 @pytest.mark.parametrize("shape", [s for s in SHAPES if s[3] % 64 == 0])
