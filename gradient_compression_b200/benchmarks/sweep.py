@@ -75,6 +75,7 @@ def main(argv=None):
     ap.add_argument("--e2e", action="store_true", help="also take bench.py's end-to-end measurement (slower)")
     ap.add_argument("--sustained-seconds", type=float, default=0.0)
     ap.add_argument("--one-gpu-json", default=None, help="an earlier sweep at one GPU: adds the exposed reduce time per row")
+    ap.add_argument("--only", nargs="+", default=None, help="keep the rows whose label contains one of these strings")
     ap.add_argument("--out", default=os.path.join(ROOT, "profiles", "bench_matrix"))
     args = ap.parse_args(argv)
     extra = ["--sustained-seconds", str(args.sustained_seconds)] + ([] if args.e2e else ["--no-e2e"])
@@ -87,6 +88,8 @@ def main(argv=None):
     rows, port = [], 29600
     for group in args.group:
         for model, reducer, flags, label in ROWS[group]:
+            if args.only and not any(o in label for o in args.only):
+                continue
             row = {"group": group, "model": model, "reducer": reducer, "label": label, "gpus": args.gpus}
             for impl in args.arms:                       # the reference first, this library right after it
                 port += 1
