@@ -26,7 +26,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--sweep", action="store_true", help="also time the forward kernel at every tile width")
     ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--no-split", action="store_true", help="never split the contraction of the forward / input-gradient kernel")
     args = ap.parse_args()
+    if args.no_split:
+        gemm.configure_split(1)
     torch.backends.cudnn.benchmark = True
     cl = torch.channels_last
     flush = torch.zeros(64 << 20, device="cuda")
@@ -43,6 +46,18 @@ def main():
         parts = torch.empty(gemm.m_tiles(m), 2, cout, device="cuda")
         row["fwd_us"] = round(_median_us(lambda: conv.conv_forward(x, w, None, stride, pad, col_partials=parts, out=out), flush), 1)
         row["fwd_cudnn_us"] = round(_median_us(lambda: F.conv2d(x, w, None, stride, pad), flush), 1)
+        splits = conv.nat.cuda().gc_cuda_conv_fwd_splits(n, hw, hw, cin, cout, r, stride, pad)
+        if splits > 1 and not args.no_split:
+            # what the layer runs instead: split contraction, then the statistics in a pass of their own
+            from ..ops import bn
+            stats = torch.empty(2 * cout, device="cuda")
+            scratch = bn._scratch_for(x.device, cout)
+
+            def split_fwd():
+                conv.conv_forward(x, w, None, stride, pad, out=out)
+                conv.nat.cuda().gc_cuda_bn_stats(out.data_ptr(), m, cout, scratch.data_ptr(), stats.data_ptr(), None, None, 0.1, 1e-5,
+                                                 conv.nat.stream_ptr())
+            row["fwd_split_plus_stats_us"] = round(_median_us(split_fwd, flush), 1)
         if args.sweep:
             sw = {}
             for tile_n in (64, 128, 256):

@@ -139,21 +139,40 @@ int gc_cuda_conv_fwd(const float* x, const float* w, float* y, const float* bias
   const int M = N * s.Ho * s.Wo, K = R * R * Cin;
   int bw, bh, bn;
   box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn);
-  const int tile = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, Cout, K);
+  cudaStream_t st = (cudaStream_t)cs;
+  const BnFin fin_dev = bn_fin_from_host(bn_fin);
+  const BnFin* fin = fin_dev.acc != nullptr ? &fin_dev : nullptr;
+  int tile = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, Cout, K), splits = 1;
+  if (col_partials == nullptr && fin == nullptr)       // few output tiles and a long contraction: split it over the idle SMs
+    plan_persistent(M, Cout, K, accumulate ? 0.0 : zero_cycles((int64_t)M * Cout), &tile, &splits);
   CUtensorMap ma, mb, mc;
   if (make_map_nhwc(&ma, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0 || make_map(&mb, w, Cout, K, K, tile) != 0 ||
       make_map(&mc, y, M, Cout, Cout, BM) != 0)
     return (int)cudaErrorInvalidValue;
   const ConvA ca = conv_a(s);
-  cudaStream_t st = (cudaStream_t)cs;
-  const BnFin fin_dev = bn_fin_from_host(bn_fin);
-  const BnFin* fin = fin_dev.acc != nullptr ? &fin_dev : nullptr;
+  if (splits > 1 && !accumulate) {
+    cudaError_t e = cudaMemsetAsync(y, 0, (size_t)M * Cout * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int acc = (accumulate || splits > 1) ? 1 : 0;
   switch (tile) {
-    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
-    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
-    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, bias, M, Cout, K, accumulate, col_partials, error_flag, st, fin);
+    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, bias, M, Cout, K, acc, col_partials, error_flag, st, fin, nullptr, splits);
+    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, bias, M, Cout, K, acc, col_partials, error_flag, st, fin, nullptr, splits);
+    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, bias, M, Cout, K, acc, col_partials, error_flag, st, fin, nullptr, splits);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+// Contraction splits gc_cuda_conv_fwd would use for this shape if the caller gave up the in-kernel column statistics and
+// computed them in a pass of its own over y (whose modelled cost is charged to the split plan).  1: keep the statistics in
+// the kernel.
+int gc_cuda_conv_fwd_splits(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
+  Shape s;
+  if (!make_shape(N, H, W, Cin, Cout, R, stride, pad, &s) || !fwd_ok(s)) return 1;
+  const int M = N * s.Ho * s.Wo;
+  int tile, splits;
+  plan_persistent(M, Cout, R * R * Cin, zero_cycles((int64_t)M * Cout) + stats_pass_cycles((int64_t)M * Cout), &tile, &splits);
+  return splits;
 }
 
 // 1 when the weight gradient of this convolution can run on the tensor cores: Cin a multiple of 64, Cout of 32, and

@@ -267,11 +267,16 @@ int launch(const float* A, const float* B, float* C, const float* bias, int M, i
 template <int BN>
 int launch_persistent(const float* A, const float* B, float* C, const float* bias, int M, int N, int K, int64_t lda,
                       int64_t ldb, int64_t ldc, int accumulate, float* col_partials, int* error_flag, cudaStream_t st,
-                      const BnFin* fin) {
+                      const BnFin* fin, int splits) {
   CUtensorMap ma, mb, mc;
   if (make_map(&ma, A, M, K, lda, BM) != 0 || make_map(&mb, B, N, K, ldb, BN) != 0 || make_map(&mc, C, M, N, ldc, BM) != 0)
     return (int)cudaErrorInvalidValue;
-  return launch_persistent_maps<BN>(ma, mb, mc, ConvA{}, bias, M, N, K, accumulate, col_partials, error_flag, st, fin);
+  if (splits > 1 && !accumulate) {
+    cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch_persistent_maps<BN>(ma, mb, mc, ConvA{}, bias, M, N, K, (accumulate || splits > 1) ? 1 : 0, col_partials, error_flag,
+                                    st, fin, nullptr, splits);
 }
 
 template <int BN>
@@ -344,11 +349,13 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
   bool persistent = (g_kernel_choice != 1 || accumulate || fin != nullptr) && N > 16 && tma_store_ok(C, ldc);
   if ((accumulate || fin != nullptr) && !persistent) return (int)cudaErrorInvalidValue;
   if (persistent) {
-    int bn = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, N, K);
+    int bn = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, N, K), splits = 1;
+    if (col_partials == nullptr && fin == nullptr)
+      plan_persistent(M, N, K, accumulate ? 0.0 : zero_cycles((int64_t)M * N), &bn, &splits);
     switch (bn) {
-      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
-      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
-      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin);
+      case 64: return launch_persistent<64>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin, splits);
+      case 128: return launch_persistent<128>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin, splits);
+      case 256: return launch_persistent<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, col_partials, error_flag, st, fin, splits);
       default: return (int)cudaErrorInvalidValue;
     }
   }
@@ -359,6 +366,18 @@ int gc_cuda_gemm_tf32(const float* A, const float* B, float* C, const float* bia
     default: return launch<256>(A, B, C, bias, M, N, K, lda, ldb, ldc, col_partials, error_flag, st);
   }
 }
+
+// Contraction splits gc_cuda_gemm_tf32 would use for C[M, N] over K if the caller computed the column statistics in a
+// pass of its own over C instead of asking for col_partials (that pass is charged to the split plan).  1: do not split.
+int gc_cuda_gemm_tf32_splits(int M, int N, int K) {
+  if (N <= 16) return 1;
+  int bn, splits;
+  plan_persistent(M, N, K, zero_cycles((int64_t)M * N) + stats_pass_cycles((int64_t)M * N), &bn, &splits);
+  return splits;
+}
+
+// For measurements: contraction splits of the persistent kernel (0 = modelled, 1 = never, n = n wherever a product allows it).
+void gc_cuda_tc_split_config(int splits) { gctc::split_choice = splits; }
 
 // For measurements: how the producer warps issue their TMA loads (bit 0: prefetch the tensor maps; bit 1: spread the
 // loads of a stage over several lanes).

@@ -27,6 +27,7 @@ namespace gctc {
 inline int tile_choice = 0;
 inline int tn_ctas_per_sm = 1;
 inline int tn_min_kblocks = 4;
+inline int split_choice = 0;   // contraction splits of the persistent kernel: 0 = modelled, 1 = never, n = n where a product allows it
 inline int tma_mode = 1;   // bit 0: prefetch the tensor maps at kernel start; bit 2: epilogue warps sleep between polls while a tile is being accumulated
 }  // namespace gctc
 
@@ -289,7 +290,7 @@ template <int BN>
 __global__ void __launch_bounds__(PERSISTENT_THREADS, 1)
 gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                             const __grid_constant__ CUtensorMap tma_c, const ConvA ca, const float* __restrict__ bias, int M, int N, int K,
-                            int tiles_m, int tiles_n, int accumulate, float* __restrict__ col_partials,
+                            int tiles_m, int tiles_n, int splits, int accumulate, float* __restrict__ col_partials,
                             int* __restrict__ error_flag, int tma_mode, const BnFin fin, const ConvC cc) {
   using S = PSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -308,7 +309,10 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k = (K + BK - 1) / BK;
-  const int total_tiles = tiles_m * tiles_n;
+  // work item = (output tile, split of the contraction); the splits of one tile are neighbours in the list, so they run
+  // at the same time on different SMs and add their partial tiles in L2 (the host passes accumulate = 1 and a zeroed C)
+  const int total_items = tiles_m * tiles_n * splits;
+  const int kps = (num_k + splits - 1) / splits;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -337,13 +341,13 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
       if (tma_mode & 1) { tma_prefetch_map(&tma_a); tma_prefetch_map(&tma_b); }
       uint32_t it = 0;                                        // k-blocks issued so far by all producers, over all tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
+        const int tile = t / splits, sp = t - tile * splits;
+        const int kbeg = sp * kps, kend = min(num_k, kbeg + kps);
+        const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
         int box[4] = {0, 0, 0, 0};
         if (ca.taps != 0) conv_box(ca, (int64_t)m0, 0, 0, box);  // pixel of the tile's first position at tap (0, 0)
-        // CTAs that run side by side start their contraction at different k-blocks (the sum does not care about the
-        // order): otherwise all of them ask the same few L2 slices for the same tile of the shared operand at once
-        int kk = (tma_mode & 8) ? (int)((blockIdx.x * 5u) % (unsigned)num_k) : 0;
+        int kk = kbeg;
         int cb = 0, fr = 0, fs = 0;                             // k-block = (filter tap (fr, fs), 32-channel block cb)
         if (ca.taps != 0) {
           const int tap = kk / ca.cblocks;
@@ -351,7 +355,7 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
           fr = tap / ca.fs;
           fs = tap - fr * ca.fs;
         }
-        for (int k = 0; k < num_k; ++k, ++it) {
+        for (int k = kbeg; k < kend; ++k, ++it) {
           if ((int)(it % PRODUCER_WARPS) == warp) {
             const int s = (int)(it % S::STAGES);
             const uint32_t phase = (it / S::STAGES) & 1u;
@@ -363,9 +367,8 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
               tma_load_4d(a_tiles + s * S::A_BYTES, &tma_a, cb * 32, box[1] + fs, box[2] + fr, box[3], &full[s]);
             tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, kk * BK, n0, &full[s]);
           }
-          if (++kk == num_k) {
-            kk = 0; cb = 0; fr = 0; fs = 0;
-          } else if (++cb == ca.cblocks) {                      // (never true for a plain matrix: cblocks == 0)
+          ++kk;
+          if (++cb == ca.cblocks) {                             // (never true for a plain matrix: cblocks == 0)
             cb = 0;
             if (++fs == ca.fs) { fs = 0; ++fr; }
           }
@@ -377,12 +380,14 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
       constexpr uint32_t idesc = make_idesc(BN);
       uint32_t it = 0, lt = 0;                                // k-blocks consumed, tiles started
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+      for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x, ++lt) {
+        const int sp = t % splits;
+        const int nk = min(num_k, (sp + 1) * kps) - sp * kps;
         const uint32_t buf = lt & 1u, aphase = (lt >> 1) & 1u;
         if (!mbar_wait(&acc_empty[buf], aphase ^ 1u, &abort_flag)) break;      // first use of a buffer passes at once
         tc_fence_after();
         const uint32_t tmem_c = tmem_base + buf * (uint32_t)BN;
-        for (int k = 0; k < num_k; ++k, ++it) {
+        for (int k = 0; k < nk; ++k, ++it) {
           const int s = (int)(it % S::STAGES);
           const uint32_t phase = (it / S::STAGES) & 1u;
           if (!mbar_wait(&full[s], phase, &abort_flag)) { ok = false; break; }
@@ -416,9 +421,11 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
     const bool want_sums = col_partials != nullptr || fin_on;
     float run_a = 0.f, run_b = 0.f;                            // fin_on: this thread's column, summed over the CTA's tiles
     bool drained_all = true;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
-      const int mi = t / tiles_n;
-      const int m0 = mi * BM, n0 = (t % tiles_n) * BN;
+    for (int t = blockIdx.x; t < total_items; t += gridDim.x, ++lt) {
+      const int tile = t / splits;
+      const bool add_bias = bias != nullptr && t == tile * splits;      // the first split of a tile carries the bias
+      const int mi = tile / tiles_n;
+      const int m0 = mi * BM, n0 = (tile % tiles_n) * BN;
       const uint32_t buf = lt & 1u, aphase = (lt >> 1) & 1u;
       const bool got = (tma_mode & 4) ? mbar_wait_idle(&acc_full[buf], aphase, &abort_flag, 128u) : mbar_wait(&acc_full[buf], aphase, &abort_flag);
       // one thread decides for the group: the TMEM loads are warp-collective and the named barriers below
@@ -447,7 +454,7 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
         for (int c = 0; c < 8; ++c) {
           const uint32_t* src = c < 4 ? &ra[c * 4] : &rb[(c - 4) * 4];
           float4 o = make_float4(__uint_as_float(src[0]), __uint_as_float(src[1]), __uint_as_float(src[2]), __uint_as_float(src[3]));
-          if (bias != nullptr) {
+          if (add_bias) {
             int col = n0 + sl * 32 + c * 4;
             o.x += col < N ? bias[col] : 0.f; o.y += col + 1 < N ? bias[col + 1] : 0.f;
             o.z += col + 2 < N ? bias[col + 2] : 0.f; o.w += col + 3 < N ? bias[col + 3] : 0.f;
@@ -829,7 +836,7 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
 template <int BN>
 int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const ConvA& ca, const float* bias,
                            int M, int N, int K, int accumulate, float* col_partials, int* error_flag, cudaStream_t st,
-                           const BnFin* fin = nullptr, const ConvC* cc = nullptr) {
+                           const BnFin* fin = nullptr, const ConvC* cc = nullptr, int splits = 1) {
   using S = PSmem<BN>;
   static bool configured = false;
   if (!configured) {
@@ -838,7 +845,12 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
     configured = true;
   }
   int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  int64_t total = (int64_t)tiles_m * tiles_n;
+  if (splits < 1 || splits > (K + BK - 1) / BK) return (int)cudaErrorInvalidValue;
+  // a split contraction adds partial tiles into C: the caller zeroed C (or wants C += ...), and nothing that needs the
+  // finished values (column statistics) or a store map without a reduce form can ride along
+  if (splits > 1 && (!accumulate || col_partials != nullptr || (fin != nullptr && fin->acc != nullptr) || cc != nullptr))
+    return (int)cudaErrorInvalidValue;
+  int64_t total = (int64_t)tiles_m * tiles_n * splits;
   int64_t grid = total < sm_count() ? total : sm_count();
   BnFin f{};
   if (fin != nullptr && fin->acc != nullptr) {
@@ -847,7 +859,8 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
     f = *fin;
   }
   gc::launch_pdl(gemm_tf32_persistent_kernel<BN>, dim3((unsigned)grid), dim3(PERSISTENT_THREADS), (size_t)S::TOTAL, st, ma, mb, mc, ca,
-                 bias, M, N, K, tiles_m, tiles_n, accumulate, col_partials, error_flag, gctc::tma_mode, f, cc != nullptr ? *cc : ConvC{0, 0});
+                 bias, M, N, K, tiles_m, tiles_n, splits, accumulate, col_partials, error_flag, gctc::tma_mode, f,
+                 cc != nullptr ? *cc : ConvC{0, 0});
   return (int)cudaGetLastError();
 }
 
@@ -902,5 +915,43 @@ int pick_bn_persistent(int M, int N, int K) {
   return best;
 }
 
+// Modelled cycles of zeroing `elements` floats with a memset node, and of one more pass over them for column statistics.
+inline double zero_cycles(int64_t elements) { return 3000.0 + (double)elements * 4.0 / 3000.0; }
+inline double stats_pass_cycles(int64_t elements) { return 8000.0 + (double)elements * 4.0 / 2000.0; }
+
+// Tile width and number of contraction splits for a product whose output may be built from partial tiles (no column
+// statistics wanted, plain 2-D output).  Modelled cycles of the slowest CTA: a k-block costs the issuing thread about
+// 200 cycles of waiting and committing plus the larger of four MMA issues and their tensor time (420 / 500 / 720 cycles
+// for 64 / 128 / 256 columns, measured with clock64 inside the kernel), a work item about 2500 cycles of fill and
+// drain.  extra_split_cycles: what a caller pays elsewhere when the product is split (zeroing C, a separate pass for the
+// statistics).  Returns splits = 1 with pick_bn_persistent's width when splitting does not pay.
+inline void plan_persistent(int M, int N, int K, double extra_split_cycles, int* bn_out, int* splits_out) {
+  *bn_out = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, N, K);
+  *splits_out = 1;
+  if (gctc::split_choice == 1) return;
+  const int sms = sm_count();
+  const int num_k = (K + BK - 1) / BK;
+  const int64_t mt = (M + BM - 1) / BM;
+  auto cycles = [&](int bn, int splits) {
+    const double stage = bn == 64 ? 420.0 : (bn == 128 ? 500.0 : 720.0);
+    const int64_t items = mt * ((N + bn - 1) / bn) * splits;
+    const int64_t waves = (items + sms - 1) / sms;
+    return (double)waves * ((double)((num_k + splits - 1) / splits) * stage + 2500.0) + (splits > 1 ? extra_split_cycles : 0.0);
+  };
+  double best = cycles(*bn_out, 1);
+  const int cand[3] = {256, 128, 64};
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    if ((bn == 256 && N <= 128) || (bn == 128 && N <= 64)) continue;
+    if (gctc::tile_choice && bn != gctc::tile_choice) continue;
+    for (int splits = 2; splits <= 16; ++splits) {
+      const int per = (num_k + splits - 1) / splits;
+      if (per < 6 || (splits - 1) * per >= num_k) continue;      // every split non-empty and long enough to fill the ring
+      if (gctc::split_choice > 1 && splits != gctc::split_choice) continue;
+      const double c = cycles(bn, splits);
+      if (c < best * 0.93 || (gctc::split_choice > 1 && *splits_out == 1)) { best = c; *bn_out = bn; *splits_out = splits; }
+    }
+  }
+}
 
 }  // namespace

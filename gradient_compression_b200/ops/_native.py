@@ -148,6 +148,9 @@ def cuda():
         _declare(lib, "gc_cuda_gemm_tf32_config", None, [c_int, c_int])
         _declare(lib, "gc_cuda_tc_tma_mode", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_conv_fwd_splits", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_gemm_tf32_splits", c_int, [c_int] * 3)
+        _declare(lib, "gc_cuda_tc_split_config", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P, P])
         _declare(lib, "gc_cuda_conv_dgrad_s2_supported", c_int, [c_int] * 7)
         _declare(lib, "gc_cuda_conv_dgrad_s2", c_int, [P, P, P] + [c_int] * 7 + [P, P])

@@ -292,6 +292,25 @@ def conv_wgrad(dy, x, r, stride, pad, out=None):
     return dw
 
 
+_SPLIT_PLAN = {}
+
+
+def _split_forward(lib, mode, n, h, wd, cin, cout, r, stride, pad, m):
+    """True when the forward kernel of this layer should run as a split contraction and leave the batch statistics to a
+    separate pass (the kernels' own cost model decides; cached per shape)."""
+    key = (mode, n, h, wd, cin, cout, r, stride, pad)
+    hit = _SPLIT_PLAN.get(key)
+    if hit is None:
+        if mode == "gemm":
+            hit = lib.gc_cuda_gemm_tf32_splits(m, cout, cin) > 1
+        elif mode == "conv":
+            hit = lib.gc_cuda_conv_fwd_splits(n, h, wd, cin, cout, r, stride, pad) > 1
+        else:
+            hit = False
+        _SPLIT_PLAN[key] = hit
+    return hit
+
+
 STEM_K = 32      # row length of the gathered stem operand: R*R*Cin taps padded to one 128-byte row
 
 
@@ -315,7 +334,7 @@ class _ConvBNAct(torch.autograd.Function):
             if training:
                 if FUSED_FINALIZE and cout <= gemm.FIN_MAX_CHANNELS and cout > 16:
                     fin = gemm.bn_fin_args(x.device, stats, running_mean, running_var, momentum, eps)
-                else:
+                elif not _split_forward(lib, mode, n, h, wd, cin, cout, r, stride, pad, m):
                     tiles = gemm.m_tiles(m)
                     partials = torch.empty(tiles, 2, cout, dtype=torch.float32, device=x.device)
             if mode == "gemm":
@@ -332,6 +351,13 @@ class _ConvBNAct(torch.autograd.Function):
                 nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), partials.shape[0], m, cout, stats.data_ptr(),
                                                            nat.ptr(running_mean), nat.ptr(running_var), float(momentum),
                                                            float(eps), st()), "bn_finalize_partials")
+            elif training and fin is None:
+                # the convolution ran as a split contraction (few output tiles, long filters): its statistics take a pass
+                # of their own over the small output
+                nat.check(lib.gc_cuda_bn_stats(yconv.data_ptr(), m, cout, _scratch_for(x.device, cout).data_ptr(), stats.data_ptr(),
+                                               nat.ptr(running_mean), nat.ptr(running_var), float(momentum), float(eps), st()),
+                          "bn_stats")
+                nat.count_launch()
             elif not training:
                 stats[:cout] = running_mean
                 stats[cout:] = torch.rsqrt(running_var + eps)

@@ -135,6 +135,12 @@ def configure(kernel="auto", tile_n=0):
     nat.cuda().gc_cuda_gemm_tf32_config(KERNELS[kernel], int(tile_n))
 
 
+def configure_split(splits=0):
+    """Contraction splits of the persistent kernel where a product allows them (no statistics, plain 2-D output):
+    0 = the kernels' cost model decides, 1 = never, n = n -- for measurements and tests."""
+    nat.cuda().gc_cuda_tc_split_config(int(splits))
+
+
 def configure_tn(ctas_per_sm=1, min_kblocks=4):
     """Split-K policy of ``gemm_tn_tf32`` (for measurements)."""
     nat.cuda().gc_cuda_gemm_tn_config(int(ctas_per_sm), int(min_kblocks))

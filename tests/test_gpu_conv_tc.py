@@ -112,6 +112,54 @@ def test_conv_forward_every_tile_width(tile_n):
     _same(out, ref)
 
 
+@pytest.mark.parametrize("splits", [1, 2, 3, 5])
+@pytest.mark.parametrize("shape", [(32, 4, 4, 512, 512, 3, 1, 1), (9, 8, 8, 256, 256, 3, 1, 1), (16, 8, 8, 512, 512, 3, 2, 1),
+                                   (8, 16, 16, 512, 1024, 1, 2, 0)])
+def test_conv_forward_split_contraction(shape, splits):
+    """The same convolution with its contraction cut into `splits` work items per output tile (partial tiles added in L2
+    onto a zeroed output; the bias rides on the first split only) and onto an output that already holds values."""
+    from gradient_compression_b200.ops import conv, gemm
+
+    n, h, w, cin, cout, r, stride, pad = shape
+    g = torch.Generator().manual_seed(sum(shape) + splits)
+    x = _cl(_ints((n, cin, h, w), g).cuda())
+    wt = _cl(_ints((cout, cin, r, r), g, -2, 3).cuda())
+    bias = _ints((cout,), g).cuda()
+    ref = _conv64(x, wt, bias, stride, pad)
+    gemm.configure_split(splits)
+    try:
+        out = conv.conv_forward(x, wt, bias, stride, pad)
+        prior = _cl(_ints(tuple(ref.shape), g).cuda())
+        acc = conv.conv_forward(x, wt, bias, stride, pad, out=prior.clone(memory_format=torch.preserve_format), accumulate=True)
+    finally:
+        gemm.configure_split(0)
+    gemm.check()
+    _same(out, ref)
+    _same(acc, ref + prior)
+
+
+@pytest.mark.parametrize("splits", [0, 2, 4])
+@pytest.mark.parametrize("m,n,k,ldc", [(2048, 512, 2048, 512), (2048, 2048, 512, 2048), (1000, 96, 1024, 128), (512, 256, 4096, 256)])
+def test_gemm_split_contraction(m, n, k, ldc, splits):
+    from gradient_compression_b200.ops import gemm
+
+    g = torch.Generator().manual_seed(m + n + k + splits)
+    a = _ints((m, k), g).cuda()
+    b = _ints((n, k), g, -2, 3).cuda()
+    bias = _ints((n,), g).cuda()
+    buf = torch.full((m, ldc), 7.0, device="cuda")
+    ref = (a.double() @ b.double().t() + bias.double()).float()
+    gemm.configure_split(splits)
+    try:
+        gemm.gemm_tf32(a, b, bias=bias, out=buf[:, :n])
+    finally:
+        gemm.configure_split(0)
+    gemm.check()
+    _same(buf[:, :n], ref)
+    if ldc > n:
+        assert float((buf[:, n:] - 7.0).abs().max()) == 0.0      # the zeroing of a split output stays inside its columns
+
+
 @pytest.mark.parametrize("shape", [s for s in SHAPES if s[6] == 1])
 def test_conv_input_gradient_exact_on_small_integers(shape):
     """dX = forward kernel on dY with the rotated, channel-swapped filter; also accumulating onto a tensor."""
@@ -228,7 +276,8 @@ def _block(cin, cout, r, stride, bias):
 @pytest.mark.parametrize("cin,cout,r,stride,hw,bias,res", [
     (64, 64, 3, 1, 32, False, False), (64, 128, 3, 1, 16, True, False), (128, 128, 3, 2, 16, False, False),
     (3, 64, 3, 1, 32, False, False), (3, 64, 3, 1, 32, True, False), (256, 512, 1, 2, 16, False, False),
-    (256, 256, 3, 1, 8, False, True), (512, 512, 3, 1, 2, True, False), (256, 64, 1, 1, 8, False, False)])
+    (256, 256, 3, 1, 8, False, True), (512, 512, 3, 1, 2, True, False), (256, 64, 1, 1, 8, False, False),
+    (512, 512, 3, 1, 4, False, True), (2048, 512, 1, 1, 4, False, False)])
 def test_conv_bn_act_matches_unfused_modules(cin, cout, r, stride, hw, bias, res):
     """The fused layer (tensor-core convolution + epilogue statistics + BN apply, and its backward) against the same
     modules run one after the other in fp32."""

@@ -87,7 +87,19 @@ def _batch(seed, n=32):
 def test_bucketed_overlapped_step_equals_plain_step_for_an_exact_reducer():
     """Buckets reduced on a side stream while backward runs, captured in the step graph: with an exact reducer (mean over
     one worker) and the parameters held still (learning rate 0) the reduced gradient of every replay must be the plain
-    eager step's, up to the rounding of the split-K weight gradients (their partial tiles add up in no fixed order)."""
+    eager step's, up to the rounding of the split-K weight gradients (their partial tiles add up in no fixed order).  The
+    forward and input-gradient contractions run unsplit here: split three or more ways they too would add up in no fixed
+    order, and ReLU masks that flip on that noise would drown the comparison."""
+    from gradient_compression_b200.ops import gemm
+
+    gemm.configure_split(1)
+    try:
+        _overlapped_equals_plain()
+    finally:
+        gemm.configure_split(0)
+
+
+def _overlapped_equals_plain():
     task_a, plain = _setup(False, "NoneAllReducer")
     task_b, bucketed = _bucketed_setup(True, "NoneAllReducer")
     assert len(bucketed.reducer.buckets) > 3
