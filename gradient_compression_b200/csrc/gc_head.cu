@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_fwd_kernel(const float* __r
                                                                 float* __restrict__ pooled, float* __restrict__ logits,
                                                                 float* __restrict__ dlogits, float* __restrict__ per_sample,
                                                                 unsigned int* __restrict__ ticket, float* __restrict__ out3) {
-  __shared__ float sp[HEAD_MAX_CHANNELS];
+  __shared__ __align__(16) float sp[HEAD_MAX_CHANNELS];
   __shared__ float slog[HEAD_MAX_CLASSES];
   __shared__ int last;
   const int n = blockIdx.x;
@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_fwd_kernel(const float* __r
   const float inv_pos = 1.0f / (float)positions;
   for (int q = threadIdx.x; q < (C >> 2); q += HEAD_THREADS) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
     for (int p = 0; p < positions; ++p) {
       const float4 v = *reinterpret_cast<const float4*>(xn + (int64_t)p * C + 4 * q);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
@@ -51,7 +52,12 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_fwd_kernel(const float* __r
   for (int k = warp; k < K; k += HEAD_THREADS / 32) {
     float acc = 0.f;
     const float* wk = W + (int64_t)k * C;
-    for (int c = lane; c < C; c += 32) acc = fmaf(sp[c], wk[c], acc);
+#pragma unroll 4
+    for (int c = lane * 4; c < C; c += 128) {                // C is a multiple of 4: whole quads, several loads in flight
+      const float4 wv = *reinterpret_cast<const float4*>(wk + c);
+      const float4 pv = *reinterpret_cast<const float4*>(sp + c);
+      acc = fmaf(pv.x, wv.x, acc); acc = fmaf(pv.y, wv.y, acc); acc = fmaf(pv.z, wv.z, acc); acc = fmaf(pv.w, wv.w, acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) {
       acc += bias != nullptr ? bias[k] : 0.f;
@@ -110,32 +116,46 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_bwd_dx_kernel(const float* 
   for (int p = 0; p < positions; ++p) *reinterpret_cast<float4*>(dn + (int64_t)p * C) = acc;
 }
 
+// One block per 32 channels: warp w sums the samples w, w + 8, ... for its lane's channel and all classes, the eight partial
+// sums meet in shared memory.
+constexpr int HEAD_DW_CHANNELS = 32;
+
 __global__ void __launch_bounds__(HEAD_THREADS) head_bwd_dw_kernel(const float* __restrict__ dlogits, const float* __restrict__ pooled,
                                                                    const float* __restrict__ g, int N, int C, int K,
                                                                    float* __restrict__ dW, float* __restrict__ db) {
-  extern __shared__ float sdl[];                 // dlogits [N, K]
+  extern __shared__ float sdl[];                 // dlogits [N, K], then partial sums [8 warps][K][32 channels]
+  float* part = sdl + N * K;
   for (int i = threadIdx.x; i < N * K; i += HEAD_THREADS) sdl[i] = dlogits[i];
   __syncthreads();
   const float gs = g != nullptr ? *g : 1.f;
-  const int c = blockIdx.x * HEAD_THREADS + threadIdx.x;
-  if (c < C) {
-    float acc[HEAD_MAX_CLASSES];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * HEAD_DW_CHANNELS + lane;
+  float acc[HEAD_MAX_CLASSES];
 #pragma unroll
-    for (int k = 0; k < HEAD_MAX_CLASSES; ++k) acc[k] = 0.f;
-    for (int n = 0; n < N; ++n) {
+  for (int k = 0; k < HEAD_MAX_CLASSES; ++k) acc[k] = 0.f;
+  if (c < C) {
+    for (int n = warp; n < N; n += HEAD_THREADS / 32) {
       const float pv = pooled[(int64_t)n * C + c];
 #pragma unroll
       for (int k = 0; k < HEAD_MAX_CLASSES; ++k)
         if (k < K) acc[k] = fmaf(sdl[n * K + k], pv, acc[k]);
     }
+  }
 #pragma unroll
-    for (int k = 0; k < HEAD_MAX_CLASSES; ++k)
-      if (k < K) dW[(int64_t)k * C + c] = acc[k] * gs;
+  for (int k = 0; k < HEAD_MAX_CLASSES; ++k)
+    if (k < K) part[(warp * K + k) * HEAD_DW_CHANNELS + lane] = acc[k];
+  __syncthreads();
+  for (int i = threadIdx.x; i < K * HEAD_DW_CHANNELS; i += HEAD_THREADS) {
+    const int k = i / HEAD_DW_CHANNELS, cc = blockIdx.x * HEAD_DW_CHANNELS + (i % HEAD_DW_CHANNELS);
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < HEAD_THREADS / 32; ++w) sum += part[(w * K + k) * HEAD_DW_CHANNELS + (i % HEAD_DW_CHANNELS)];   // fixed order
+    if (cc < C) dW[(int64_t)k * C + cc] = sum * gs;
   }
   if (blockIdx.x == 0 && threadIdx.x < K && db != nullptr) {
-    float acc = 0.f;
-    for (int n = 0; n < N; ++n) acc += sdl[n * K + threadIdx.x];
-    db[threadIdx.x] = acc * gs;
+    float sum = 0.f;
+    for (int n = 0; n < N; ++n) sum += sdl[n * K + threadIdx.x];
+    db[threadIdx.x] = sum * gs;
   }
 }
 
@@ -147,7 +167,7 @@ extern "C" {
 // backward kernel's shared memory.
 int gc_cuda_head_supported(int N, int positions, int C, int K) {
   return N >= 1 && positions >= 1 && C >= 4 && (C & 3) == 0 && C <= HEAD_MAX_CHANNELS && K >= 1 && K <= HEAD_MAX_CLASSES &&
-         (int64_t)N * K * 4 <= 96 * 1024 ? 1 : 0;
+         (int64_t)N * K * 4 + (HEAD_THREADS / 32) * K * HEAD_DW_CHANNELS * 4 <= 96 * 1024 ? 1 : 0;
 }
 
 // Bytes of the zero-initialised scratch (ticket + per-sample values) for batches of up to max_batch samples.
@@ -180,8 +200,9 @@ int gc_cuda_head_backward(const float* dlogits, const float* pooled, const float
       cudaFuncSetAttribute(head_bwd_dw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
       configured = true;
     }
-    head_bwd_dw_kernel<<<(unsigned)((C + HEAD_THREADS - 1) / HEAD_THREADS), HEAD_THREADS, (size_t)N * K * 4, st>>>(dlogits, pooled, g, N, C, K,
-                                                                                                            dW, db);
+    const size_t smem = (size_t)N * K * 4 + (size_t)(HEAD_THREADS / 32) * K * HEAD_DW_CHANNELS * 4;
+    head_bwd_dw_kernel<<<(unsigned)((C + HEAD_DW_CHANNELS - 1) / HEAD_DW_CHANNELS), HEAD_THREADS, smem, st>>>(dlogits, pooled, g, N, C, K,
+                                                                                                        dW, db);
   }
   return (int)cudaGetLastError();
 }

@@ -20,8 +20,8 @@ def _projection(cin, cout, stride):
 class _Projection(nn.Sequential):
     """1x1 convolution + batch norm of a shortcut; children are named "0" and "1" as in the reference."""
 
-    def forward(self, x):
-        return conv_bn_act(self[0], self[1], x, relu=False)
+    def forward(self, x, donate=None):
+        return conv_bn_act(self[0], self[1], x, relu=False, donate=donate)
 
 
 class BasicBlock(nn.Module):
@@ -35,9 +35,9 @@ class BasicBlock(nn.Module):
 
     def forward(self, x):
         identity = len(self.shortcut) == 0
-        link = GradLink() if identity else None
+        link = GradLink()
         y = conv_bn_act(self.conv1, self.bn1, x, link=link)
-        return conv_bn_act(self.conv2, self.bn2, y, residual=link.residual(x) if identity else self.shortcut(x))
+        return conv_bn_act(self.conv2, self.bn2, y, residual=link.residual(x) if identity else self.shortcut(x, donate=link))
 
 
 class Bottleneck(nn.Module):
@@ -51,13 +51,14 @@ class Bottleneck(nn.Module):
         self.shortcut = _projection(in_planes, planes * self.expansion, stride)
 
     def forward(self, x):
-        # every convolution: tensor-core kernel with BN statistics in its epilogue.  In an identity block the gradient of
-        # the skip connection and conv1's input gradient meet at x: the link lets conv1's GEMM add onto the former.
+        # every convolution: tensor-core kernel with BN statistics in its epilogue.  Two gradients meet at x: conv1's input
+        # gradient and the skip connection's (identity block) or the projection shortcut's; the link lets conv1's GEMM add
+        # onto the other one instead of autograd summing them in a pass of its own.
         identity = len(self.shortcut) == 0
-        link = GradLink() if identity else None
+        link = GradLink()
         y = conv_bn_act(self.conv1, self.bn1, x, link=link)
         y = conv_bn_act(self.conv2, self.bn2, y)
-        return conv_bn_act(self.conv3, self.bn3, y, residual=link.residual(x) if identity else self.shortcut(x))
+        return conv_bn_act(self.conv3, self.bn3, y, residual=link.residual(x) if identity else self.shortcut(x, donate=link))
 
 
 class ResNet(nn.Module):

@@ -317,9 +317,9 @@ STEM_K = 32      # row length of the gathered stem operand: R*R*Cin taps padded 
 class _ConvBNAct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu, link,
-                mode, stride, pad):
+                mode, stride, pad, donate=None):
         x = _cl(x)
-        ctx.link, ctx.mode, ctx.stride, ctx.pad = link, mode, stride, pad
+        ctx.link, ctx.mode, ctx.stride, ctx.pad, ctx.donate = link, mode, stride, pad, donate
         n, cin, h, wd = x.shape
         cout, r = w.shape[0], w.shape[2]
         ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - r) // stride + 1
@@ -427,6 +427,11 @@ class _ConvBNAct(torch.autograd.Function):
                         dx = dx + acc
             if link is not None:
                 link.conv_done = True
+            donate = ctx.donate
+            if donate is not None and dx is not None and not donate.conv_done and donate.stash is None:
+                # this layer shares its input with the link's convolution, whose backward runs later: hand the gradient
+                # over instead of returning it, so that that kernel adds onto it (autograd would sum the two in a pass)
+                donate.stash, donate.stash_owned, dx = dx, True, None
             dw = None
             if ctx.needs_input_grad[1]:
                 slot = _slot_of(w) if WGRAD_ENABLED else None       # the owner's gradient storage, or None: return a tensor
@@ -447,7 +452,7 @@ class _ConvBNAct(torch.autograd.Function):
             # a bias in front of a training-mode batch norm has no effect on the output: its gradient is the sum of
             # dconv over all positions, which the batch norm's backward makes zero up to rounding
             dcb = torch.zeros(cout, dtype=torch.float32, device=x.device) if ctx.has_cbias else None
-        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None
+        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None, None
 
 
 def _mode(conv, bn, x):
@@ -486,7 +491,11 @@ def _mode(conv, bn, x):
     return mode if mode in PATHS else None
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None, donate=None):
+    """``act(bn(conv(x)) + residual)`` on the tensor-core kernels where the layer qualifies (cuDNN + the fused BN kernels
+    otherwise).  ``link``: see ``GradLink``.  ``donate``: the ``GradLink`` of an earlier-created layer that reads the same
+    ``x`` (a block's first convolution, when this layer is the projection shortcut): this layer's input gradient is then
+    handed to that layer's input-gradient kernel to add onto."""
     mode = _mode(conv, bn, x)
     if mode is None:
         return bn_act(bn, conv(x), residual=residual, relu=relu)
@@ -500,4 +509,4 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None):
     rv = bn.running_var if bn.track_running_stats else None
     return _ConvBNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,
                             bn.eps, relu, link if (link is not None and link.armed) else None, mode, conv.stride[0],
-                            conv.padding[0])
+                            conv.padding[0], donate if (donate is not None and donate.armed) else None)

@@ -34,6 +34,8 @@ def supported(features, weight, labels):
             and labels.dtype == torch.int64):
         return False
     n, c, h, w = features.shape
+    if weight.data_ptr() % 16 or not weight.is_contiguous():      # the kernels read W in 16-byte quads
+        return False
     return bool(nat.cuda().gc_cuda_head_supported(n, h * w, c, weight.shape[0]))
 
 

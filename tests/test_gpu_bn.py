@@ -248,6 +248,34 @@ def test_identity_block_gradient_link(tc_conv, owned):
     assert float((gw_l - gw_p).norm() / gw_p.norm()) < 1e-6
 
 
+@pytest.mark.parametrize("stride", [1, 2])
+def test_projection_block_hands_its_input_gradient_to_the_first_convolution(tc_conv, stride):
+    """x feeds conv1 and the projection shortcut.  The shortcut's backward runs first and donates its input gradient to
+    conv1's input-gradient kernel, which adds onto it; the result must equal autograd's own sum of the two."""
+    from gradient_compression_b200.models.resnet import Bottleneck
+    from gradient_compression_b200.ops import conv as convmod
+
+    cl = torch.channels_last
+    torch.manual_seed(5 + stride)
+    block = Bottleneck(64, 32, stride).cuda().to(memory_format=cl)
+    x0 = torch.randn(8, 64, 16, 16, device="cuda").contiguous(memory_format=cl)
+    grads = []
+    for enabled in (True, False):
+        convmod.LINK_ENABLED = enabled
+        try:
+            block.zero_grad(set_to_none=True)
+            x = (x0 * 1.0).requires_grad_(True)
+            x.retain_grad()
+            out = block(x)
+            torch.manual_seed(9)
+            out.backward(torch.randn_like(out))
+        finally:
+            convmod.LINK_ENABLED = True
+        grads.append((x.grad.clone(), block.conv1.weight.grad.clone(), block.shortcut[0].weight.grad.clone()))
+    for a, b in zip(*grads):
+        assert float((a - b).norm() / b.norm()) < 1e-5
+
+
 def test_batch_counters_are_batched_but_exact():
     """``num_batches_tracked`` of every batch norm of a zoo model moves by one per training forward (one multi-tensor
     launch at the end of the forward), stays put in eval mode, and is counted per use when a layer runs twice."""
