@@ -43,8 +43,12 @@ class NoiseSource:
         self.seed, self.step = int(sd["seed"]), int(sd["step"])
 
 
-def _container(bits):
-    return torch.int8 if bits < 8 else torch.int32
+def _container(bits, max_level=None):
+    """int8 for codes of fewer than 8 bits whose largest level fits it (the non-uniform codecs reach 2**b = 128 at 7
+    bits, one past int8; the reference stores that in int8 and wraps: compressors.py:466), int32 otherwise."""
+    if max_level is None:
+        max_level = _levels(bits)
+    return torch.int8 if bits < 8 and max_level <= 127 else torch.int32
 
 
 def _levels(s):
@@ -192,6 +196,10 @@ class NUQSGDMaxNormCompressor(QSGDMaxNormCompressor):
 
     _mode = ops.MODE_NU
 
+    def __init__(self, device, quantization_level=8, noise=None):
+        super().__init__(device, quantization_level, noise)
+        self._dtype = _container(quantization_level, 1 << quantization_level)
+
     def _s(self):
         return 1 << self._quantization_level
 
@@ -208,7 +216,7 @@ class NUQSGDModCompressor(_Codec):
     def __init__(self, device, quantization_level=8, noise=None):
         super().__init__(device, noise)
         self._quantization_level = quantization_level
-        self._dtype = _container(quantization_level)
+        self._dtype = _container(quantization_level, 1 << quantization_level)
 
     def compress(self, tensor):
         s = 1 << self._quantization_level

@@ -281,10 +281,10 @@ class FusedEngine:
                  "v_total": voff,
                  "tab": torch.tensor(mats or [[0] * 8], dtype=torch.int64, device=dev),
                  "vtab": torch.tensor(vecs or [[0] * 3], dtype=torch.int64, device=dev),
-                 "stage": torch.empty(plan["p_total"] + voff, device=dev),
-                 "reduced": torch.empty(plan["p_total"] + voff, device=dev),
+                 "stage": torch.zeros(plan["p_total"] + voff, device=dev),       # zeroed: the alignment gaps are never written
+                 "reduced": torch.zeros(plan["p_total"] + voff, device=dev),
                  "max_rows": max([n for (_, n, _, _, _, _) in plan["hi"]] or [1]),
-                 "q_local": torch.empty(max(plan["q_total"], 1) * nat.cuda().gc_cuda_psgd_q_chunks(
+                 "q_local": torch.zeros(max(plan["q_total"], 1) * nat.cuda().gc_cuda_psgd_q_chunks(
                      max([n for (_, n, _, _, _, _) in plan["hi"]] or [1])), device=dev)}
         reducer._psgd_cache = cache
         return cache
@@ -334,7 +334,7 @@ class FusedEngine:
                                                1.0 / reducer.n_workers, st()), "psgd_out")
         reducer.p_memory = c["reduced"][:p_total]
         self._finish(flat, grad_out, dest, tmp)
-        bits = 32 * (p_total + q_total + c["v_total"])
+        bits = 32 * (plan["p_elems"] + plan["q_elems"] + c["v_total"])
         reducer.last_wire_bits = bits
         return bits
 

@@ -153,6 +153,15 @@ class Reducer:
             dist.all_reduce(tensor, op=op if op is not None else dist.ReduceOp.SUM, group=self._group)
         return tensor
 
+    def _all_reduce_levels(self, levels):
+        """Sum of integer quantisation levels over the workers.  Levels of fewer than 8 bits travel in int8 containers, and
+        a sum of W of them leaves int8 as soon as s * W > 127 (the reference all-reduces the int8 tensor and wraps,
+        reducer.py:537): the collective therefore runs on an int32 copy (neither gloo nor NCCL sums int16).
+        ``reference_compat=True`` keeps the container, wrap included."""
+        if self.n_workers > 1 and levels.dtype == torch.int8 and not self._compat:
+            levels = levels.to(torch.int32)
+        return self._all_reduce(levels)
+
     def _all_gather(self, tensor):
         if self.n_workers == 1:
             return [tensor]

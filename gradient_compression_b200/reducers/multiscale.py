@@ -38,8 +38,8 @@ class QSGDMaxNormTwoScaleReducer(Reducer):
                 dist.all_reduce(mask, op=dist.ReduceOp.MIN, group=self._group)
             levels = torch.where(mask.bool(), hi, lo)
         with self._timer("reduce.reduce.vector", verbosity=2):
-            self._all_reduce(levels)
-        bits = 32 + n_bits(mask) + n_bits(levels)
+            wire_levels, levels = levels, self._all_reduce_levels(levels)
+        bits = 32 + n_bits(mask) + n_bits(wire_levels)
         mb, pb = ops.packed_sizes(values.numel(), self._lower_quantization_level)
         self.last_wire_bits = 32 + 8 * (mb + 2 * pb)
         with self._timer("reduce.decompress", verbosity=2):
@@ -95,8 +95,8 @@ class QSGDMaxNormMultiScaleReducer(Reducer):
                 dist.all_reduce(mask, op=dist.ReduceOp.MIN, group=self._group)
             levels = self._compressor.compress(mask)
         with self._timer("reduce.reduce.vector", verbosity=2):
-            self._all_reduce(levels)
-        bits = 32 + n_bits(mask) + n_bits(levels)
+            wire_levels, levels = levels, self._all_reduce_levels(levels)
+        bits = 32 + n_bits(mask) + n_bits(wire_levels)
         self.last_wire_bits = bits
         with self._timer("reduce.decompress", verbosity=2):
             values = self._compressor.decompress(max_norm, levels, mask, self.n_workers)

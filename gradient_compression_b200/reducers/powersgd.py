@@ -50,7 +50,9 @@ class RankKReducer(Reducer):
         key = tuple(tuple(t.shape) for t in grad_in)
         if self._layout is not None and self._layout["key"] == key:
             return self._layout
-        hi, lo, p_off, q_off = [], [], 0, 0
+        # every matrix's P and Q block starts on a 16-byte boundary of p_memory / q_memory (the kernels read them in
+        # quads); p_total / q_total are the sizes of those buffers, p_elems / q_elems the floats that carry information
+        hi, lo, p_off, q_off, p_elems, q_elems = [], [], 0, 0, 0, 0
         for i, t in enumerate(grad_in):
             if t.dim() <= 1:
                 lo.append(i)
@@ -58,9 +60,12 @@ class RankKReducer(Reducer):
             n, m = t.shape[0], t.numel() // t.shape[0]
             r = min(n, m, self.rank_r)
             hi.append((i, n, m, r, p_off, q_off))
-            p_off += n * r
-            q_off += m * r
-        self._layout = {"key": key, "hi": hi, "lo": lo, "p_total": p_off, "q_total": q_off}
+            p_off += (n * r + 3) // 4 * 4
+            q_off += (m * r + 3) // 4 * 4
+            p_elems += n * r
+            q_elems += m * r
+        self._layout = {"key": key, "hi": hi, "lo": lo, "p_total": p_off, "q_total": q_off, "p_elems": p_elems,
+                        "q_elems": q_elems}
         return self._layout
 
     def reduce(self, grad_in, grad_out):
@@ -70,8 +75,8 @@ class RankKReducer(Reducer):
         with self._timer("reduce.allocate_memory", verbosity=2):
             fresh = self.p_memory is None
             if fresh:
-                self.p_memory = torch.empty(plan["p_total"], device=dev)
-                self.q_memory = torch.empty(plan["q_total"], device=dev)
+                self.p_memory = torch.zeros(plan["p_total"], device=dev)
+                self.q_memory = torch.zeros(plan["q_total"], device=dev)
             if self._memory is None:
                 self._memory = torch.zeros_like(flat.buffer)
         if self._use_fused():
@@ -94,7 +99,7 @@ class RankKReducer(Reducer):
                 torch.matmul(M, q, out=p)
         with self._timer("reduce.p", verbosity=2):
             self._all_reduce(self.p_memory)
-        bits = n_bits(self.p_memory)
+        bits = 32 * plan["p_elems"]
         with self._timer("reduce.rank1.pack", verbosity=2):
             rank1 = torch.cat([flat[i].reshape(-1) for i in plan["lo"]]) if plan["lo"] else flat.buffer.new_zeros(0)
         with self._timer("reduce.rank1.all_reduce", verbosity=2):
@@ -109,7 +114,7 @@ class RankKReducer(Reducer):
         with self._timer("reduce.q", verbosity=2):
             self._all_reduce(self.q_memory)
             self.q_memory.mul_(1.0 / self.n_workers)
-        bits += n_bits(self.q_memory)
+        bits += 32 * plan["q_elems"]
         self.last_wire_bits = bits
         with self._timer("reduce.outerprod", verbosity=2):
             self._memory.copy_(flat.buffer)

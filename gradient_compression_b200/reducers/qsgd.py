@@ -69,8 +69,8 @@ class _MaxNormReducer(Reducer):
                 local = self._compressor.decompress(max_norm, levels) if not self._compat else levels.float()
                 torch.sub(flat.buffer, local, out=self._memory)
         with self._timer("reduce.reduce.vector", verbosity=2):
-            self._all_reduce(levels)
-        bits = 32 + n_bits(levels)
+            wire_levels, levels = levels, self._all_reduce_levels(levels)
+        bits = 32 + n_bits(wire_levels)
         self.last_wire_bits = self._wire_bits(flat.buffer.numel())
         with self._timer("reduce.decompress", verbosity=2):
             values = self._compressor.decompress(max_norm, levels, self.n_workers)

@@ -60,8 +60,8 @@ class GlobalRandKMaxNormReducer(Reducer):
         with self._timer("reduce.compress", verbosity=2):
             levels = self._compressor.compress(max_norm, values)
         with self._timer("reduce.reduce.vector", verbosity=2):
-            self._all_reduce(levels)
-        bits = 32 + n_bits(levels)
+            wire_levels, levels = levels, self._all_reduce_levels(levels)
+        bits = 32 + n_bits(wire_levels)
         mb, pb = ops.packed_sizes(values.numel(), self._quantization_level)
         self.last_wire_bits = 32 + 8 * (mb + pb)
         with self._timer("reduce.decompress", verbosity=2):

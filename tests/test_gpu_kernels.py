@@ -125,7 +125,7 @@ def test_powersgd_fused_matches_cpu_reference_path(rank):
             bits = red.reduce([t.clone() for t in grads], out)
         outs[dev] = torch.cat([o.reshape(-1).cpu() for o in out])
         mems[dev] = red._memory.cpu()
-        assert bits == 32 * (red._layout["p_total"] + red._layout["q_total"] + 64 + 64 + 128 + 10)
+        assert bits == 32 * (red._layout["p_elems"] + red._layout["q_elems"] + 64 + 64 + 128 + 10)
     assert torch.allclose(outs["cpu"], outs["cuda"], rtol=1e-3, atol=1e-6)
     assert torch.allclose(mems["cpu"], mems["cuda"], rtol=1e-3, atol=1e-6)
 

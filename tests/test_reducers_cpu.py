@@ -184,7 +184,7 @@ def test_powersgd_matches_dense_restatement():
         assert torch.allclose(red._memory[s:e].view(n, m), M - approx, atol=1e-5)
     for i in red._layout["lo"]:
         assert torch.equal(out[i], grads[i])
-    total = red._layout["p_total"] + red._layout["q_total"] + sum(grads[i].numel() for i in red._layout["lo"])
+    total = red._layout["p_elems"] + red._layout["q_elems"] + sum(grads[i].numel() for i in red._layout["lo"])
     assert bits == 32 * total
     # error feedback: second step adds the memory first
     g2 = _grads(5)
@@ -329,5 +329,35 @@ def _reference_body(rank, world):
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_DIR, "reducer.py")), reason="reference sources not mounted")
+def _near_max_body(rank, world):
+    # every rank holds the same tensor with most entries at +-max: each contributes level +-63 at 6 bits, the sum of four
+    # (252) does not fit the int8 container the levels are produced in
+    g = torch.Generator().manual_seed(3)
+    x = torch.where(torch.rand(4096, generator=g) < 0.5, -1.0, 1.0) * 2.5
+    x[::7] = torch.randn(586, generator=g).clamp(-2.5, 2.5)[: x[::7].numel()]
+    out = [torch.empty_like(x)]
+    spike = torch.zeros(4096)
+    spike[5], spike[77] = 10.0, -1e-3          # one entry carries the whole L2 norm: its non-uniform level is 2**7 = 128
+    for cls, kw, s in ((R.QSGDMaxNormReducer, {"quantization_level": 6}, 63), (R.NUQSGDMaxNormReducer, {"quantization_level": 7}, 128)):
+        red = cls("cpu", seed=11, **kw)
+        x = x if s == 63 else spike
+        red.reduce([x.clone()], out)
+        norm = x.abs().max() if s == 63 else torch.norm(x)
+        mode = ops.MODE_STOCHASTIC if s == 63 else ops.MODE_NU
+        tot = sum(ops.quantize_levels(x, norm, s, 11, philox.stream_id(r, philox.PURPOSE_ROUND), 0, mode=mode, dtype=torch.int32)
+                  for r in range(world))
+        assert int(tot.abs().max()) > 127
+        assert torch.equal(out[0], ops.dequantize_levels(tot, norm, s, world))
+    # the reference's behaviour (the int8 sum wraps) stays available
+    x = torch.full((256,), 2.5)
+    wrapped = [torch.empty_like(x)]
+    R.QSGDMaxNormReducer("cpu", seed=11, quantization_level=6, reference_compat=True).reduce([x.clone()], wrapped)
+    assert float((wrapped[0] - x).abs().max()) > 2.0
+
+
+def test_level_sums_do_not_wrap_in_their_container(dist_runner):
+    dist_runner(_near_max_body, world=4)
+
+
 def test_parity_with_reference_reducers(dist_runner):
     dist_runner(_reference_body, world=2)
