@@ -101,15 +101,19 @@ class _DgradWeights:
                 for _, _, th, tw in _s2_classes(r, pad):
                     if th and tw:
                         n = cin * len(th) * len(tw) * cout
-                        sub = w.detach()[:, :, th][:, :, :, tw]                       # [Cout, Cin, th, tw]
-                        e[1][off: off + n].view(cin, len(th), len(tw), cout).copy_(sub.permute(1, 2, 3, 0))
+                        dst = e[1][off: off + n].view(cin, len(th), len(tw), cout)
+                        for a, fr in enumerate(th):              # tap by tap: plain strided copies, fine inside a graph capture
+                            for b, fs in enumerate(tw):
+                                dst[:, a, b, :].copy_(w.detach()[:, :, fr, fs].t())
                         off += n
             e[2] = w._version
         return e[1]
 
-    def invalidate(self):
+    def invalidate(self, lo=None, hi=None):
+        """Mark stale the copies of the weights stored in the address range [lo, hi) (all of them without a range)."""
         for e in self.entries.values():
-            e[2] = -1
+            if lo is None or lo <= e[3] < hi:
+                e[2] = -1
 
     @staticmethod
     def _rows(e, tiles):
@@ -165,9 +169,10 @@ class _DgradWeights:
 _dgrad_weights = _DgradWeights()
 
 
-def weights_written_raw():
-    """Called by kernels that rewrite parameters through raw pointers (version counters do not move)."""
-    _dgrad_weights.invalidate()
+def weights_written_raw(lo=None, hi=None):
+    """Called by kernels that rewrite parameters through raw pointers (version counters do not move); ``[lo, hi)``: the
+    address range they wrote, so that another model's copies stay valid."""
+    _dgrad_weights.invalidate(lo, hi)
 
 
 def refresh_transposed(owner, params):

@@ -258,7 +258,7 @@ def sgd_step(p, g, m, lr=None, momentum=0.9, weight_decay=0.0, nesterov=True, hy
                                                   int(bool(nesterov)), nat.stream_ptr()), "sgd_step")
         from . import conv                     # raw-pointer write: cached transposes of these weights are stale
 
-        conv.weights_written_raw()
+        conv.weights_written_raw(p.data_ptr(), p.data_ptr() + 4 * n)
     else:
         if hyper is not None:
             lr, momentum, weight_decay = (float(v) for v in hyper.tolist())
