@@ -193,8 +193,10 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
   const int P = N * s.Ho * s.Wo, No = R * R * Cin;
   int bw, bh, bn;
   box_for(TBK, s.Ho, s.Wo, &bw, &bh, &bn);
-  int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : 64);      // a tile's columns stay inside one filter tap
-  if (gctc::tile_choice && Cin % gctc::tile_choice == 0) tile = gctc::tile_choice;
+  // a tile's columns stay inside one filter tap, except at Cin = 64: there a tile of 192 columns holds three taps side by
+  // side (64-column MMAs leave the issuing thread, not the tensor pipe, as the limit)
+  int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : ((Cin == 64 && No % 192 == 0) ? 192 : 64));
+  if (gctc::tile_choice && (Cin % gctc::tile_choice == 0 || (Cin == 64 && No % gctc::tile_choice == 0))) tile = gctc::tile_choice;
   CUtensorMap ma, mb, mc;
   if (make_map_mn(&ma, dy, P, Cout, Cout) != 0 || make_map_nhwc(&mb, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) != 0 ||
       make_map(&mc, dw, Cout, No, No, BM) != 0)
@@ -204,6 +206,7 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
   switch (tile) {
     case 64: return launch_tn_maps<64>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
     case 128: return launch_tn_maps<128>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
+    case 192: return launch_tn_maps<192>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
     case 256: return launch_tn_maps<256>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
     default: return (int)cudaErrorInvalidValue;
   }

@@ -602,7 +602,7 @@ struct TnSmem {
   static constexpr int STAGING_OFF = RING_BYTES;
   static constexpr int BAR_OFF = STAGING_OFF + NSLAB * SLAB_BYTES;
   static constexpr int TOTAL = 1024 + BAR_OFF + 256;
-  static constexpr int TMEM_COLS = BN;
+  static constexpr int TMEM_COLS = BN == 192 ? 256 : BN;    // TMEM is allocated in powers of two
   static_assert(TOTAL <= 232448, "shared memory of one CTA");
 };
 
@@ -669,17 +669,24 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       // a stage is BM / 32 + BN / 32 boxes of 32 floats x TBK rows; producer warp p fills the stages k == p (mod PRODUCER_WARPS)
       if (lane == 0) {
         if (tma_mode & 1) { tma_prefetch_map(&tma_a); tma_prefetch_map(&tma_b); }
-        int co[4] = {0, 0, 0, 0}, c0 = 0, tap = 0;
+        // weight gradient of an R x S convolution: column n of dW[Cout, taps * Cin] belongs to filter tap n / Cin, channel
+        // n % Cin; a tile narrower than Cin stays inside one tap, a wider one (Cin = 64) covers several taps side by side.
+        // Box c of a stage reads the pixels of its tap, shifted by (fr, fs), for the TBK output positions of the k-block.
+        int co[4] = {0, 0, 0, 0};
+        int box_ch[BN / 32], box_fr[BN / 32], box_fs[BN / 32];
         if (ca.taps != 0) {
-          // weight gradient of an R x S convolution: the columns n0 .. n0 + BN of dW[Cout, taps * Cin] belong to one
-          // filter tap; the TBK output positions of a k-block read that tap's shifted pixels
           const int cin = ca.cblocks * 32;
-          tap = n0 / cin;
-          c0 = n0 - tap * cin;
+#pragma unroll
+          for (int c = 0; c < BN / 32; ++c) {
+            const int n = n0 + c * 32, tap = n / cin;
+            box_ch[c] = n - tap * cin;
+            box_fr[c] = tap / ca.fs;
+            box_fs[c] = tap - box_fr[c] * ca.fs;
+          }
         }
-        // boxes that lie wholly beyond the matrix (Mo < 128: the 64-channel layers; No < BN) are not loaded at all: the
+        // boxes that lie wholly beyond the matrix (Mo < 128: the 64-channel layers; No < n0 + BN) are not loaded at all: the
         // rows and columns of the accumulator they feed are never stored
-        int a_boxes = (Mo - m0 + 31) / 32, b_boxes = ((ca.taps == 0 ? No - n0 : BN) + 31) / 32;
+        int a_boxes = (Mo - m0 + 31) / 32, b_boxes = (No - n0 + 31) / 32;
         a_boxes = a_boxes < BM / 32 ? a_boxes : BM / 32;
         b_boxes = b_boxes < BN / 32 ? b_boxes : BN / 32;
         const uint32_t stage_tx = (uint32_t)((a_boxes + b_boxes) * S::CHUNK_BYTES);
@@ -697,10 +704,12 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             for (int c = 0; c < BN / 32; ++c)
               if (c < b_boxes) tma_load_2d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, n0 + c * 32, row0, &full[s]);
           } else {
-            conv_box(ca, (int64_t)row0, tap, 0, co);
+            conv_box(ca, (int64_t)row0, 0, 0, co);           // the k-block's first position at tap (0, 0)
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
-              tma_load_4d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, c0 + c * 32, co[1], co[2], co[3], &full[s]);
+              if (c < b_boxes)
+                tma_load_4d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, box_ch[c], co[1] + box_fs[c], co[2] + box_fr[c], co[3],
+                            &full[s]);
           }
         }
       }
