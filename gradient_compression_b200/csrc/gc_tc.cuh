@@ -873,7 +873,7 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
   return (int)cudaGetLastError();
 }
 
-// Launch the split-K TN kernel on ready-made tensor maps.  About tn_ctas_per_sm CTAs per SM over all tiles, at least
+// Launch the split-K TN kernel on ready-made tensor maps.  At most tn_ctas_per_sm CTAs per SM over all tiles, at least
 // tn_min_kblocks k-blocks each so that the pipeline fills.  One CTA per SM measured 10-25 % faster than two on the
 // 131072- and 32768-position weight gradients of ResNet-50 (fewer partial tiles to add, longer pipelines), equal below.
 template <int BN>
@@ -889,7 +889,9 @@ int launch_tn_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
   int tiles_m = (Mo + BM - 1) / BM, tiles_n = (No + BN - 1) / BN;
   int tiles = tiles_m * tiles_n;
   int total_k = (P + TBK - 1) / TBK;
-  int splits = (gctc::tn_ctas_per_sm * sm_count() + tiles - 1) / tiles;
+  // never more CTAs than fit at once (one per SM at this shared-memory size): a second, nearly empty wave would double the
+  // kernel's time (measured: 153 CTAs on 148 SMs ran 37 us with the SMs 62 % busy)
+  int splits = gctc::tn_ctas_per_sm * sm_count() / tiles;
   if (splits > (total_k + gctc::tn_min_kblocks - 1) / gctc::tn_min_kblocks) splits = (total_k + gctc::tn_min_kblocks - 1) / gctc::tn_min_kblocks;
   if (splits < 1) splits = 1;
   int per = (total_k + splits - 1) / splits;
