@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(256) psgd_gs_kernel(float* __restrict__ p, con
 // ------------------------------------------------------------------------------------------ Q' = M^T P
 // Block = one 128-column tile of one matrix; thread (c = tid % 32, rl = tid / 32) owns columns 4c..4c+3 of the
 // tile and rows rl, rl + 8, ...; the eight row lanes are combined through shared memory in a fixed order.
-constexpr int Q_ROWCHUNK = 1024;   // rows per block along grid.y
+constexpr int Q_ROWCHUNK = 256;    // rows per block along grid.y (1024 left ResNet-50 with ~700 blocks at 1.3 TB/s)
 
 __global__ void __launch_bounds__(256) psgd_q_kernel(const float* __restrict__ e /* holds M = G + E */,
                                                      const int64_t* __restrict__ tab, int n_mats,
