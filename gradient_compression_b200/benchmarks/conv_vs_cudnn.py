@@ -68,15 +68,15 @@ def main():
             gemm.configure("auto", 0)
             row["fwd_sweep_us"] = sw
         if stride == 1:
-            wd = conv._dgrad_weights.get(w)
             dx = torch.empty_like(x)
-            row["dgrad_us"] = round(_median_us(lambda: conv.conv_forward(dy, wd, None, 1, r - 1 - pad, out=dx), flush), 1)
+            lib1 = conv.nat.cuda()
+            row["dgrad_us"] = round(_median_us(lambda: lib1.gc_cuda_conv_dgrad(
+                dy.data_ptr(), w.data_ptr(), dx.data_ptr(), n, hw, hw, cin, cout, r, pad, 0, conv._err(x.device), conv.nat.stream_ptr()), flush), 1)
         elif conv.nat.cuda().gc_cuda_conv_dgrad_s2_supported(n, hw, hw, cin, cout, r, pad):
-            wd2 = conv._dgrad_weights.get(w, 2, pad)            # per-parity-class filter layout
             dx = torch.empty_like(x)
             lib2 = conv.nat.cuda()
             row["dgrad_us"] = round(_median_us(lambda: lib2.gc_cuda_conv_dgrad_s2(
-                dy.data_ptr(), wd2.data_ptr(), dx.data_ptr(), n, hw, hw, cin, cout, r, pad, conv._err(x.device), conv.nat.stream_ptr()), flush), 1)
+                dy.data_ptr(), w.data_ptr(), dx.data_ptr(), n, hw, hw, cin, cout, r, pad, conv._err(x.device), conv.nat.stream_ptr()), flush), 1)
         row["dgrad_cudnn_us"] = round(_median_us(lambda: torch.ops.aten.convolution_backward(
             dy, x, w, None, [stride, stride], [pad, pad], [1, 1], False, [0, 0], 1, [True, False, False]), flush), 1)
         row["wgrad_us"] = round(_median_us(lambda: conv.conv_wgrad(dy, x, r, stride, pad), flush), 1)

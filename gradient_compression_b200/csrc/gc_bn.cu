@@ -8,6 +8,8 @@
 // with the lines the preceding reduction touched last and find them in the 126 MB L2.
 // Reductions are deterministic: per-block partial sums go to scratch memory and a small second kernel
 // (32 channels per block, coalesced over the partials) combines them in double precision.
+// Where a 2x2 max-pool follows (vgg.py:101-103 of the reference: conv, bn, relu, ..., MaxPool2d), the *_pool variants fold it
+// in: the forward writes only the pooled map, the backward routes the pooled gradient to each window's winner.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -274,6 +276,156 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_kernel(const float* _
   }
 }
 
+// ---------------------------------------------------------------------------------- BN + ReLU + 2x2 max-pool
+// VGG closes a group of layers with act = relu(bn(conv)) followed by a 2x2 / stride-2 max-pool.  The three kernels below
+// never materialise act: the forward writes only the pooled map, the backward finds each window's winner again from the
+// convolution output (first maximum in row-major window order, as torch's pooling does) and routes the pooled gradient
+// there.  x: [N, H, W, C] convolution output (NHWC), H and W even; pooled tensors: [N, H/2, W/2, C].
+struct PoolGeom { int H, W, Hp, Wp; };
+
+// Rows (in units of C floats) of the four pixels of pooled pixel r.
+__device__ __forceinline__ void pool_rows(const PoolGeom& g, int64_t r, int64_t (&row)[4]) {
+  const int64_t n = r / ((int64_t)g.Hp * g.Wp);
+  const int rem = (int)(r - n * g.Hp * g.Wp);
+  const int hp = rem / g.Wp, wp = rem - hp * g.Wp;
+  row[0] = (n * g.H + 2 * hp) * g.W + 2 * wp;
+  row[1] = row[0] + 1;
+  row[2] = row[0] + g.W;
+  row[3] = row[2] + 1;
+}
+
+__device__ __forceinline__ float bn_act1(float v, float mu, float rs, float gm, float bt, int relu) {
+  const float o = fmaf((v - mu) * rs, gm, bt);
+  return relu ? fmaxf(o, 0.f) : o;
+}
+
+// Winner of one channel of one window: its position 0..3 and activation (first maximum wins, as a scan with > does).
+__device__ __forceinline__ void pool_winner(const float (&a)[4], int& which, float& best) {
+  which = 0; best = a[0];
+#pragma unroll
+  for (int j = 1; j < 4; ++j)
+    if (a[j] > best) { best = a[j]; which = j; }
+}
+
+__global__ void __launch_bounds__(BN_THREADS) bn_apply_pool_kernel(const float* __restrict__ x, PoolGeom g, int64_t Mp, int C,
+                                                                   const float* __restrict__ stats, const float* __restrict__ gamma,
+                                                                   const float* __restrict__ beta, int relu, float* __restrict__ y) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int vec = C >> 2;
+  const int64_t nq = Mp * vec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nq; i += stride) {
+    const int64_t q = nq - 1 - i;
+    const int64_t r = q / vec;
+    const int c4 = (int)(q - r * vec) * 4;
+    int64_t row[4];
+    pool_rows(g, r, row);
+    const float4 mu = ld4(stats + c4), rs = ld4(stats + C + c4), gm = ld4(gamma + c4), bt = ld4(beta + c4);
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = ld4(x + row[j] * C + c4);
+    float4 o;
+    o.x = fmaxf(fmaxf(bn_act1(v[0].x, mu.x, rs.x, gm.x, bt.x, relu), bn_act1(v[1].x, mu.x, rs.x, gm.x, bt.x, relu)),
+                fmaxf(bn_act1(v[2].x, mu.x, rs.x, gm.x, bt.x, relu), bn_act1(v[3].x, mu.x, rs.x, gm.x, bt.x, relu)));
+    o.y = fmaxf(fmaxf(bn_act1(v[0].y, mu.y, rs.y, gm.y, bt.y, relu), bn_act1(v[1].y, mu.y, rs.y, gm.y, bt.y, relu)),
+                fmaxf(bn_act1(v[2].y, mu.y, rs.y, gm.y, bt.y, relu), bn_act1(v[3].y, mu.y, rs.y, gm.y, bt.y, relu)));
+    o.z = fmaxf(fmaxf(bn_act1(v[0].z, mu.z, rs.z, gm.z, bt.z, relu), bn_act1(v[1].z, mu.z, rs.z, gm.z, bt.z, relu)),
+                fmaxf(bn_act1(v[2].z, mu.z, rs.z, gm.z, bt.z, relu), bn_act1(v[3].z, mu.z, rs.z, gm.z, bt.z, relu)));
+    o.w = fmaxf(fmaxf(bn_act1(v[0].w, mu.w, rs.w, gm.w, bt.w, relu), bn_act1(v[1].w, mu.w, rs.w, gm.w, bt.w, relu)),
+                fmaxf(bn_act1(v[2].w, mu.w, rs.w, gm.w, bt.w, relu), bn_act1(v[3].w, mu.w, rs.w, gm.w, bt.w, relu)));
+    st4(y + q * 4, o);
+  }
+}
+
+// One channel of one window in the backward pass: g = pooled gradient if the winner's activation passes the ReLU, at the
+// winner's position; returns the position (or -1) and the winner's xhat.
+__device__ __forceinline__ int pool_route(float v0, float v1, float v2, float v3, float mu, float rs, float gm, float bt, int relu,
+                                          float& xh_win) {
+  const float xh[4] = {(v0 - mu) * rs, (v1 - mu) * rs, (v2 - mu) * rs, (v3 - mu) * rs};
+  float a[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float o = fmaf(xh[j], gm, bt);
+    a[j] = relu ? fmaxf(o, 0.f) : o;
+  }
+  int which;
+  float best;
+  pool_winner(a, which, best);
+  xh_win = xh[which];
+  return (relu && !(best > 0.f)) ? -1 : which;
+}
+
+// sums over all N*H*W positions of g and g * xhat, where g is the pooled gradient at each window's winner and 0 elsewhere.
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_pool_kernel(const float* __restrict__ dpool, const float* __restrict__ x,
+                                                                        PoolGeom g, int64_t Mp, int C, int64_t rows_per_block,
+                                                                        const float* __restrict__ stats, const float* __restrict__ gamma,
+                                                                        const float* __restrict__ beta, int relu,
+                                                                        float* __restrict__ partials) {
+  pdl_wait();
+  pdl_launch_dependents();
+  int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
+  int64_t r1 = r0 + rows_per_block < Mp ? r0 + rows_per_block : Mp;
+  const int col = threadIdx.x % (C >> 2);
+  const float4 mu = ld4(stats + 4 * col), rs = ld4(stats + C + 4 * col);
+  const float4 gm = ld4(gamma + 4 * col), bt = ld4(beta + 4 * col);
+  block_two_sums(Mp, C, r0, r1,
+                 [&](int64_t r, int cc, float4& a, float4& b) {
+                   int64_t row[4];
+                   pool_rows(g, r, row);
+                   const float4 d = ld4(dpool + r * C + 4 * cc);
+                   float4 v[4];
+#pragma unroll
+                   for (int j = 0; j < 4; ++j) v[j] = ld4(x + row[j] * C + 4 * cc);
+                   float xh;
+                   if (pool_route(v[0].x, v[1].x, v[2].x, v[3].x, mu.x, rs.x, gm.x, bt.x, relu, xh) >= 0) { a.x += d.x; b.x = fmaf(d.x, xh, b.x); }
+                   if (pool_route(v[0].y, v[1].y, v[2].y, v[3].y, mu.y, rs.y, gm.y, bt.y, relu, xh) >= 0) { a.y += d.y; b.y = fmaf(d.y, xh, b.y); }
+                   if (pool_route(v[0].z, v[1].z, v[2].z, v[3].z, mu.z, rs.z, gm.z, bt.z, relu, xh) >= 0) { a.z += d.z; b.z = fmaf(d.z, xh, b.z); }
+                   if (pool_route(v[0].w, v[1].w, v[2].w, v[3].w, mu.w, rs.w, gm.w, bt.w, relu, xh) >= 0) { a.w += d.w; b.w = fmaf(d.w, xh, b.w); }
+                 },
+                 partials + (int64_t)blockIdx.x * 2 * C);
+}
+
+// dx at all four positions of every window: gamma * rstd * (g - dbeta / M - xhat * dgamma / M), M = N*H*W.
+__global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_pool_kernel(const float* __restrict__ dpool, const float* __restrict__ x,
+                                                                       PoolGeom g, int64_t Mp, int C, const float* __restrict__ stats,
+                                                                       const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                       const float* __restrict__ sums, int relu, float* __restrict__ dx) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int vec = C >> 2;
+  const int64_t nq = Mp * vec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const float inv_m = 1.0f / (float)(Mp * 4);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nq; i += stride) {
+    const int64_t q = nq - 1 - i;
+    const int64_t r = q / vec;
+    const int c4 = (int)(q - r * vec) * 4;
+    int64_t row[4];
+    pool_rows(g, r, row);
+    const float4 d = ld4(dpool + q * 4);
+    const float4 mu = ld4(stats + c4), rs = ld4(stats + C + c4), gm = ld4(gamma + c4), bt = ld4(beta + c4);
+    const float4 db = ld4(sums + c4), dg = ld4(sums + C + c4);
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = ld4(x + row[j] * C + c4);
+    float xw;
+    const int wx = pool_route(v[0].x, v[1].x, v[2].x, v[3].x, mu.x, rs.x, gm.x, bt.x, relu, xw);
+    const int wy = pool_route(v[0].y, v[1].y, v[2].y, v[3].y, mu.y, rs.y, gm.y, bt.y, relu, xw);
+    const int wz = pool_route(v[0].z, v[1].z, v[2].z, v[3].z, mu.z, rs.z, gm.z, bt.z, relu, xw);
+    const int ww = pool_route(v[0].w, v[1].w, v[2].w, v[3].w, mu.w, rs.w, gm.w, bt.w, relu, xw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 o;
+      o.x = gm.x * rs.x * ((wx == j ? d.x : 0.f) - db.x * inv_m - (v[j].x - mu.x) * rs.x * dg.x * inv_m);
+      o.y = gm.y * rs.y * ((wy == j ? d.y : 0.f) - db.y * inv_m - (v[j].y - mu.y) * rs.y * dg.y * inv_m);
+      o.z = gm.z * rs.z * ((wz == j ? d.z : 0.f) - db.z * inv_m - (v[j].z - mu.z) * rs.z * dg.z * inv_m);
+      o.w = gm.w * rs.w * ((ww == j ? d.w : 0.f) - db.w * inv_m - (v[j].w - mu.w) * rs.w * dg.w * inv_m);
+      st4(dx + row[j] * C + c4, o);
+    }
+  }
+}
+
 int bn_sm_count() {
   static int sms = 0;
   if (sms == 0) {
@@ -381,6 +533,48 @@ int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_
   if (!bn_shape_ok(M, C)) return (int)cudaErrorInvalidValue;
   launch_pdl(bn_bwd_apply_kernel, dim3(apply_grid(M * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, dy, x, y, M, C, stats, gamma,
              beta, sums, relu, dx, dres);
+  return (int)cudaGetLastError();
+}
+
+// 1 when the pooled variants cover the shape: the plain kernels' rules for C, H and W even.
+int gc_cuda_bn_pool_supported(int N, int H, int W, int C) {
+  return N >= 1 && H >= 2 && W >= 2 && !(H & 1) && !(W & 1) && bn_shape_ok((int64_t)N * (H / 2) * (W / 2), C) ? 1 : 0;
+}
+
+// y[N, H/2, W/2, C] = maxpool2x2(act(gamma * (x - mean) * rstd + beta)); x: [N, H, W, C].
+int gc_cuda_bn_apply_pool(const float* x, int N, int H, int W, int C, const float* stats, const float* gamma, const float* beta,
+                          int relu, float* y, void* cs) {
+  if (!gc_cuda_bn_pool_supported(N, H, W, C)) return (int)cudaErrorInvalidValue;
+  const PoolGeom g{H, W, H / 2, W / 2};
+  const int64_t Mp = (int64_t)N * g.Hp * g.Wp;
+  launch_pdl(bn_apply_pool_kernel, dim3(apply_grid(Mp * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, x, g, Mp, C, stats, gamma,
+             beta, relu, y);
+  return (int)cudaGetLastError();
+}
+
+// sums[0:C] = dbeta, sums[C:2C] = dgamma of the layer whose pooled output received the gradient dpool[N, H/2, W/2, C].
+int gc_cuda_bn_bwd_reduce_pool(const float* dpool, const float* x, int N, int H, int W, int C, const float* stats,
+                               const float* gamma, const float* beta, int relu, void* scratch, float* sums, void* cs) {
+  if (!gc_cuda_bn_pool_supported(N, H, W, C)) return (int)cudaErrorInvalidValue;
+  const PoolGeom g{H, W, H / 2, W / 2};
+  const int64_t Mp = (int64_t)N * g.Hp * g.Wp;
+  int64_t rpb;
+  int grid = reduce_grid(Mp, C, &rpb);
+  size_t smem = 2 * BN_THREADS * sizeof(float4);
+  launch_pdl(bn_bwd_reduce_pool_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dpool, x, g, Mp, C, rpb, stats, gamma,
+             beta, relu, (float*)scratch);
+  launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
+  return (int)cudaGetLastError();
+}
+
+// dx[N, H, W, C]: gradient of the convolution output.
+int gc_cuda_bn_bwd_apply_pool(const float* dpool, const float* x, int N, int H, int W, int C, const float* stats,
+                              const float* gamma, const float* beta, const float* sums, int relu, float* dx, void* cs) {
+  if (!gc_cuda_bn_pool_supported(N, H, W, C)) return (int)cudaErrorInvalidValue;
+  const PoolGeom g{H, W, H / 2, W / 2};
+  const int64_t Mp = (int64_t)N * g.Hp * g.Wp;
+  launch_pdl(bn_bwd_apply_pool_kernel, dim3(apply_grid(Mp * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, dpool, x, g, Mp, C,
+             stats, gamma, beta, sums, relu, dx);
   return (int)cudaGetLastError();
 }
 

@@ -175,6 +175,71 @@ int gc_cuda_conv_fwd_splits(int N, int H, int W, int Cin, int Cout, int R, int s
   return splits;
 }
 
+// Map of the forward filter w[Cout][R*R*Cin] as the MN-major B operand of an input-gradient launch with tiles of `tile`
+// columns: one 3-D box per stage when every tap starts on a 32-float chunk (Cin a multiple of 32), else tile / 32 boxes.
+static int filter_map(CUtensorMap* mb, ConvA* ca, const float* w, int Cout, int R, int Cin, int tile) {
+  const int64_t cols = (int64_t)R * R * Cin;
+  if ((Cin & 31) == 0 && make_map_mn3(mb, w, Cout, cols, cols, BK, tile / 32) == 0) {
+    ca->b_mn = 2;
+    return 0;
+  }
+  ca->b_mn = 1;
+  return make_map_mn(mb, w, Cout, cols, cols, BK);
+}
+
+// 1 when the stride-1 input gradient of conv2d(x[N, H, W, Cin], w[Cout, R, R, Cin], pad) can run on the tensor cores reading
+// the forward filter in place: Cout a multiple of 32 (the contraction), Cin a multiple of 4 and >= 32, and -- unless R = 1 with
+// no padding, where dY is read as a plain matrix -- 128 consecutive input positions form one box of dY.
+int gc_cuda_conv_dgrad_supported(int N, int H, int W, int Cin, int Cout, int R, int pad) {
+  if (N < 1 || H < 1 || W < 1 || R < 1 || pad < 0 || pad > R - 1 || (Cout & 31) || (Cin & 3) || Cin < 32) return 0;
+  if ((int64_t)N * H * W > 0x7fffffff || encode_fn() == nullptr) return 0;
+  if (R == 1 && pad == 0) return 1;
+  const int Ho = H + 2 * pad - R + 1, Wo = W + 2 * pad - R + 1;
+  Shape s;
+  return Ho >= 1 && Wo >= 1 && make_shape(N, Ho, Wo, Cout, Cin, R, 1, R - 1 - pad, &s) && s.Ho == H && s.Wo == W && fwd_ok(s) ? 1 : 0;
+}
+
+// dx[N, H, W, Cin] (=, += when accumulate) input gradient of the stride-1 convolution with filter w[Cout][R][R][Cin] (channels-last
+// memory order) given dy[N, Ho, Wo, Cout]: the forward kernel run on dy with the filter taps rotated by 180 degrees, the filter read
+// in place as the MN-major B operand (K = Cout rows of R*R*Cin floats; no transposed copy is kept).
+int gc_cuda_conv_dgrad(const float* dy, const float* w, float* dx, int N, int H, int W, int Cin, int Cout, int R, int pad,
+                       int accumulate, int* error_flag, void* cs) {
+  if (!gc_cuda_conv_dgrad_supported(N, H, W, Cin, Cout, R, pad)) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(w) & 15u) || (reinterpret_cast<uintptr_t>(dx) & 15u))
+    return (int)cudaErrorInvalidValue;
+  const int M = N * H * W, K = R * R * Cout;
+  cudaStream_t st = (cudaStream_t)cs;
+  int tile, splits;
+  plan_persistent(M, Cin, K, accumulate ? 0.0 : zero_cycles((int64_t)M * Cin), &tile, &splits);
+  CUtensorMap ma, mb, mc;
+  ConvA ca{};
+  if (R == 1 && pad == 0) {
+    if (make_map(&ma, dy, M, Cout, Cout, BM) != 0) return (int)cudaErrorInvalidValue;
+  } else {
+    Shape s;
+    make_shape(N, H + 2 * pad - R + 1, W + 2 * pad - R + 1, Cout, Cin, R, 1, R - 1 - pad, &s);
+    int bw, bh, bn;
+    box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn);
+    if (make_map_nhwc(&ma, dy, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0) return (int)cudaErrorInvalidValue;
+    ca = conv_a(s);
+  }
+  ca.b_ldtap = Cin; ca.b_fs = R;
+  ca.b_r0 = R - 1; ca.b_dr = -1; ca.b_s0 = R - 1; ca.b_ds = -1;
+  if (filter_map(&mb, &ca, w, Cout, R, Cin, tile) != 0 || make_map(&mc, dx, M, Cin, Cin, BM) != 0)
+    return (int)cudaErrorInvalidValue;
+  if (splits > 1 && !accumulate) {
+    cudaError_t e = cudaMemsetAsync(dx, 0, (size_t)M * Cin * 4, st);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int acc = (accumulate || splits > 1) ? 1 : 0;
+  switch (tile) {
+    case 64: return launch_persistent_maps<64>(ma, mb, mc, ca, nullptr, M, Cin, K, acc, nullptr, error_flag, st, nullptr, nullptr, splits);
+    case 128: return launch_persistent_maps<128>(ma, mb, mc, ca, nullptr, M, Cin, K, acc, nullptr, error_flag, st, nullptr, nullptr, splits);
+    case 256: return launch_persistent_maps<256>(ma, mb, mc, ca, nullptr, M, Cin, K, acc, nullptr, error_flag, st, nullptr, nullptr, splits);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
 // 1 when the weight gradient of this convolution can run on the tensor cores: Cin a multiple of 64, Cout of 32, and
 // 64 consecutive output positions form one box.
 int gc_cuda_conv_wgrad_supported(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
@@ -247,17 +312,16 @@ int gc_cuda_conv_dgrad_s2_supported(int N, int H, int W, int Cin, int Cout, int 
   return box_for(BM, s.Ho, s.Wo, &bw, &bh, &bn) && encode_fn() != nullptr ? 1 : 0;
 }
 
-// Floats of the per-class filter copies the kernel reads (see gc_cuda_conv_dgrad_s2): R * R * Cin * Cout.
 // dx[N, H, W, Cin] = input gradient of conv2d(x, w, stride 2, pad) given dy[N, H/2, W/2, Cout].  One launch per parity class
-// (ph, pw) of input pixels: the pixels (2i + ph, 2j + pw) receive a stride-1 convolution of dy with the taps
-// r = ph + pad - 2 fr, s = pw + pad - 2 fs, and are written through a 4-D store map over that strided sub-grid of dx.
-// wd: the filter copies class after class in the order (0,0), (0,1), (1,0), (1,1); class c is the matrix
-// [Cin, th * tw * Cout] with wd_c[ci][fr][fs][co] = w[co][ph + pad - 2 fr][pw + pad - 2 fs][ci].  Classes without taps
-// (a 1x1 filter reaches only the even pixels) are zero: dx is cleared first when there is one.
-int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, int H, int W, int Cin, int Cout, int R, int pad,
+// (ph, pw) of input pixels: the pixels (2i + ph, 2j + pw) receive a stride-1 convolution of dy with the filter taps
+// r = ph + pad - 2 fr, s = pw + pad - 2 fs (fr, fs = 0, 1, ...: the offsets at which dy is read), and are written through a 4-D
+// store map over that strided sub-grid of dx.  w: the forward filter [Cout][R][R][Cin] (channels-last memory order), read in
+// place as the MN-major B operand.  Classes without taps (a 1x1 filter reaches only the even pixels) are zero: dx is cleared
+// first when there is one.
+int gc_cuda_conv_dgrad_s2(const float* dy, const float* w, float* dx, int N, int H, int W, int Cin, int Cout, int R, int pad,
                           int* error_flag, void* cs) {
   if (!gc_cuda_conv_dgrad_s2_supported(N, H, W, Cin, Cout, R, pad)) return (int)cudaErrorInvalidValue;
-  if ((reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(wd) & 15u) || (reinterpret_cast<uintptr_t>(dx) & 15u))
+  if ((reinterpret_cast<uintptr_t>(dy) & 15u) || (reinterpret_cast<uintptr_t>(w) & 15u) || (reinterpret_cast<uintptr_t>(dx) & 15u))
     return (int)cudaErrorInvalidValue;
   cudaStream_t st = (cudaStream_t)cs;
   const int Ho = H / 2, Wo = W / 2, M = N * Ho * Wo;
@@ -271,7 +335,6 @@ int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, in
   int bw, bh, bn;
   box_for(BM, Ho, Wo, &bw, &bh, &bn);
   EncodeTiledFn fn = encode_fn();
-  int64_t w_off = 0;
   for (int c = 0; c < 4; ++c) {
     const int ph = c >> 1, pw = c & 1;
     const int th = class_taps(ph, pad, R), tw = class_taps(pw, pad, R);
@@ -279,7 +342,10 @@ int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, in
     const int K = th * tw * Cout;
     const int tile = gctc::tile_choice ? gctc::tile_choice : pick_bn_persistent(M, Cin, K);
     CUtensorMap ma, mb, mc;
-    if (make_map_nhwc(&ma, dy, sy, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0 || make_map(&mb, wd + w_off, Cin, K, K, tile) != 0)
+    ConvA ca{th * tw, tw, Cout / 32, Ho * Wo, Wo, 1, 0};
+    ca.b_ldtap = Cin; ca.b_fs = R;
+    ca.b_r0 = ph + pad; ca.b_dr = -2; ca.b_s0 = pw + pad; ca.b_ds = -2;
+    if (make_map_nhwc(&ma, dy, sy, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B) != 0 || filter_map(&mb, &ca, w, Cout, R, Cin, tile) != 0)
       return (int)cudaErrorInvalidValue;
     {   // pixels (2i + ph, 2j + pw) of dx as the 4-D tensor {Cin, W/2, H/2, N}
       cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)N};
@@ -291,7 +357,6 @@ int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, in
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return (int)cudaErrorInvalidValue;
     }
-    const ConvA ca{th * tw, tw, Cout / 32, Ho * Wo, Wo, 1, 0};
     const ConvC cc{Ho * Wo, Wo};
     int err;
     switch (tile) {
@@ -301,7 +366,6 @@ int gc_cuda_conv_dgrad_s2(const float* dy, const float* wd, float* dx, int N, in
       default: err = (int)cudaErrorInvalidValue;
     }
     if (err != 0) return err;
-    w_off += (int64_t)Cin * K;
   }
   return 0;
 }

@@ -123,6 +123,13 @@ __device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -142,6 +149,13 @@ struct ConvA {
   int hw_out;      // output positions per image
   int w_out;       // output width
   int stride, pad;
+  // B operand given as a matrix W[K rows, taps * ldtap columns] whose N index is the contiguous one (an input gradient
+  // reading the forward filter [Cout][R][S][Cin] in place: K = Cout, N = Cin): b_mn = 1.  The A-side tap (fr, fs) then
+  // multiplies the filter tap (b_r0 + b_dr * fr, b_s0 + b_ds * fs) -- rotation by 180 degrees for a stride-1 input gradient,
+  // every second tap for a parity class of a stride-2 one -- found at column ((r * b_fs + s) * b_ldtap + n).  b_mn = 2: the
+  // map is the 3-D view {32 floats, K rows, columns / 32} of the same matrix (b_ldtap a multiple of 32) and one box loads
+  // a whole stage of B.
+  int b_mn, b_ldtap, b_fs, b_r0, b_dr, b_s0, b_ds;
 };
 
 // Where the rows of the OUTPUT go when it is not a matrix but a strided sub-grid of an NHWC tensor read through a 4-D map
@@ -215,6 +229,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
   d |= (uint64_t)2 << 61;                                // layout type: SWIZZLE_128B
   return d;
 }
+
+// MN-major operand tile: chunks of 32 floats of the M / N dimension x `rows` K rows (128 bytes each), one after the other.
+__device__ __forceinline__ uint64_t make_smem_desc_mn_rows(const void* tile, int rows) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);      // start address
+  d |= (uint64_t)((rows * 128) >> 4) << 16;              // leading byte offset: next 32-float chunk of the M / N dimension
+  d |= (uint64_t)(512 >> 4) << 32;                       // stride byte offset: next group of 4 K rows
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  d |= (uint64_t)1 << 61;                                // layout type: SWIZZLE_128B_BASE32B
+  return d;
+}
+
+__device__ __forceinline__ uint64_t make_smem_desc_mn(const void* tile) { return make_smem_desc_mn_rows(tile, TBK); }
 
 // kind::tf32, fp32 accumulate, both operands K-major, M = 128, N = n.
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
@@ -365,7 +392,21 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
               tma_load_2d(a_tiles + s * S::A_BYTES, &tma_a, kk * BK, m0, &full[s]);
             else
               tma_load_4d(a_tiles + s * S::A_BYTES, &tma_a, cb * 32, box[1] + fs, box[2] + fr, box[3], &full[s]);
-            tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, kk * BK, n0, &full[s]);
+            if (!ca.b_mn) {
+              tma_load_2d(b_tiles + s * S::B_BYTES, &tma_b, kk * BK, n0, &full[s]);
+            } else {
+              // BN / 32 boxes of 32 N-floats x 32 K-rows: the filter read in place (no transposed copy)
+              const int tapcol = ca.taps == 0 ? 0 : ((ca.b_r0 + ca.b_dr * fr) * ca.b_fs + (ca.b_s0 + ca.b_ds * fs)) * ca.b_ldtap;
+              const int krow = (ca.taps == 0 ? kk : cb) * BK;
+              if (ca.b_mn == 2) {
+                // the matrix seen as {32 floats, K rows, N / 32 chunks}: one box brings all BN / 32 chunks of the stage
+                tma_load_3d(b_tiles + s * S::B_BYTES, &tma_b, 0, krow, (tapcol + n0) >> 5, &full[s]);
+              } else {
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c)
+                  tma_load_2d(b_tiles + s * S::B_BYTES + c * (BK * 128), &tma_b, tapcol + n0 + c * 32, krow, &full[s]);
+              }
+            }
           }
           ++kk;
           if (++cb == ca.cblocks) {                             // (never true for a plain matrix: cblocks == 0)
@@ -393,10 +434,18 @@ gemm_tf32_persistent_kernel(const __grid_constant__ CUtensorMap tma_a, const __g
           if (!mbar_wait(&full[s], phase, &abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(a_tiles + s * S::A_BYTES);
-          const uint64_t bdesc = make_smem_desc(b_tiles + s * S::B_BYTES);
+          if (!ca.b_mn) {
+            const uint64_t bdesc = make_smem_desc(b_tiles + s * S::B_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_tf32(tmem_c, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_tf32(tmem_c, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc, (k | kk) != 0 ? 1u : 0u);
+          } else {
+            // B is MN-major: 4 KB chunks of 32 N-floats x 32 K-rows; 8 K-rows = 1024 bytes = 64 address units per MMA
+            const uint64_t bdesc = make_smem_desc_mn_rows(b_tiles + s * S::B_BYTES, BK);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_tf32(tmem_c, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 64), idesc | (1u << 16), (k | kk) != 0 ? 1u : 0u);
+          }
           umma_commit(&empty[s]);
         }
         if (ok) umma_commit(&acc_full[buf]);
@@ -605,16 +654,6 @@ struct TnSmem {
   static constexpr int TMEM_COLS = BN == 192 ? 256 : BN;    // TMEM is allocated in powers of two
   static_assert(TOTAL <= 232448, "shared memory of one CTA");
 };
-
-__device__ __forceinline__ uint64_t make_smem_desc_mn(const void* tile) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);      // start address
-  d |= (uint64_t)((TBK * 128) >> 4) << 16;               // leading byte offset: next 32-float chunk of the M / N dimension
-  d |= (uint64_t)(512 >> 4) << 32;                       // stride byte offset: next group of 4 K rows
-  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
-  d |= (uint64_t)1 << 61;                                // layout type: SWIZZLE_128B_BASE32B
-  return d;
-}
 
 __host__ __device__ constexpr uint32_t make_idesc_mn(int n) {
   return make_idesc(n) | (1u << 15) | (1u << 16);        // A and B are MN-major
@@ -827,12 +866,12 @@ int make_map(CUtensorMap* map, const float* base, int64_t rows, int64_t cols, in
 
 // Row-major [P, D] fp32 matrix as an MN-major operand: box = 32 floats x 32 rows (4 KB), shared-memory layout
 // "128-byte swizzle, 32-byte atoms" (the MN-major layout of 32-bit types).
-int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64_t ld) {
+int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64_t ld, int box_rows = TBK) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)P};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)TBK};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -840,6 +879,21 @@ int make_map_mn(CUtensorMap* map, const float* base, int64_t P, int64_t D, int64
 }
 
 
+
+// The row-major matrix [K, D] (row stride ld floats, D and ld multiples of 32 for whole chunks) as the 3-D tensor
+// {32 floats, K rows, D / 32 chunks}: a box of 32 x box_rows x chunks lands in shared memory chunk after chunk, each chunk
+// box_rows rows of 128 bytes -- the MN-major operand layout -- with ONE copy instruction.
+int make_map_mn3(CUtensorMap* map, const float* base, int64_t K, int64_t D, int64_t ld, int box_rows, int chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[3] = {32, (cuuint64_t)K, (cuuint64_t)((D + 31) / 32)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, 128};
+  cuuint32_t box[3] = {32, (cuuint32_t)box_rows, (cuuint32_t)chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
 
 // Launch the persistent kernel on ready-made tensor maps (ca.taps == 0: ma is a 2-D map of A[M, K]).
 template <int BN>

@@ -49,8 +49,14 @@ class VGG(nn.Module):
             m = mods[i]
             if (isinstance(m, nn.Conv2d) and i + 2 < len(mods) and isinstance(mods[i + 1], nn.BatchNorm2d)
                     and isinstance(mods[i + 2], nn.ReLU)):
-                x = conv_bn_act(m, mods[i + 1], x)      # convolution with BN statistics in its epilogue, BN + ReLU in one pass
-                i += 3
+                # convolution with BN statistics in its epilogue, BN + ReLU in one pass; a 2x2 max-pool that follows is
+                # folded into that pass (the full-resolution activation is never written)
+                nxt = mods[i + 3] if i + 3 < len(mods) else None
+                pool = (isinstance(nxt, nn.MaxPool2d) and nxt.kernel_size in (2, (2, 2)) and nxt.stride in (2, (2, 2))
+                        and nxt.padding in (0, (0, 0)) and nxt.dilation in (1, (1, 1)) and not nxt.ceil_mode
+                        and x.shape[2] % 2 == 0 and x.shape[3] % 2 == 0)
+                x = conv_bn_act(m, mods[i + 1], x, pool=pool)
+                i += 4 if pool else 3
             else:
                 x = m(x)
                 i += 1

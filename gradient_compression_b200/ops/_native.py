@@ -124,6 +124,10 @@ def cuda():
         _declare(lib, "gc_cuda_bn_bwd_reduce", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P, P])
         _declare(lib, "gc_cuda_bn_bwd_fused_limit", None, [c_i64])
         _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_bn_pool_supported", c_int, [c_int] * 4)
+        _declare(lib, "gc_cuda_bn_apply_pool", c_int, [P, c_int, c_int, c_int, c_int, P, P, P, c_int, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_reduce_pool", c_int, [P, P, c_int, c_int, c_int, c_int, P, P, P, c_int, P, P, P])
+        _declare(lib, "gc_cuda_bn_bwd_apply_pool", c_int, [P, P, c_int, c_int, c_int, c_int, P, P, P, P, c_int, P, P])
         _declare(lib, "gc_cuda_head_supported", c_int, [c_int, c_int, c_int, c_int])
         _declare(lib, "gc_cuda_head_scratch_bytes", c_i64, [c_int])
         _declare(lib, "gc_cuda_head_forward", c_int, [P, c_int, c_int, c_int, P, P, c_int, P, P, P, P, P, P, P])
@@ -149,6 +153,8 @@ def cuda():
         _declare(lib, "gc_cuda_tc_tma_mode", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
         _declare(lib, "gc_cuda_conv_fwd_splits", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_conv_dgrad_supported", c_int, [c_int] * 7)
+        _declare(lib, "gc_cuda_conv_dgrad", c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_splits", c_int, [c_int] * 3)
         _declare(lib, "gc_cuda_tc_split_config", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd", c_int, [P, P, P, P] + [c_int] * 9 + [P, P, P, P])

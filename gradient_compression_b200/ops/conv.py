@@ -50,6 +50,8 @@ FUSED_FINALIZE = os.environ.get("GCB200_BN_FUSED_FINALIZE", "0") == "1"
 
 # Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem", "dgrad_s2" (own input gradient of
 # stride-2 convolutions; without it cuDNN computes those).
+# stride-1 input gradients read the forward filter in place (MN-major B operand) instead of a rotated / transposed copy
+DGRAD_IN_PLACE = os.environ.get("GCB200_DGRAD_IN_PLACE", "1") == "1"
 PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem,dgrad_s2").split(","))
 
 
@@ -210,6 +212,12 @@ def _slot_of(w):
     return e[1]
 
 
+def _filter_in_place_ok(w):
+    """The filter can be read by the input-gradient kernels where it lies: [Cout][R][S][Cin] memory order, 16-byte aligned."""
+    return (w.data_ptr() % 16 == 0 and (w.shape[2] * w.shape[3] == 1 and w.is_contiguous() or
+                                        w.is_contiguous(memory_format=torch.channels_last)))
+
+
 def _as_2d(t):
     n, c, h, w = t.shape
     return t.permute(0, 2, 3, 1).reshape(n * h * w, c)
@@ -322,9 +330,9 @@ STEM_K = 32      # row length of the gathered stem operand: R*R*Cin taps padded 
 class _ConvBNAct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, cbias, gamma, beta, residual, running_mean, running_var, training, momentum, eps, relu, link,
-                mode, stride, pad, donate=None):
+                mode, stride, pad, donate=None, pool=False):
         x = _cl(x)
-        ctx.link, ctx.mode, ctx.stride, ctx.pad, ctx.donate = link, mode, stride, pad, donate
+        ctx.link, ctx.mode, ctx.stride, ctx.pad, ctx.donate, ctx.pool = link, mode, stride, pad, donate, bool(pool)
         n, cin, h, wd = x.shape
         cout, r = w.shape[0], w.shape[2]
         ho, wo = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - r) // stride + 1
@@ -367,9 +375,16 @@ class _ConvBNAct(torch.autograd.Function):
                 stats[:cout] = running_mean
                 stats[cout:] = torch.rsqrt(running_var + eps)
             res = _cl(residual) if residual is not None else None
-            out = torch.empty_like(yconv)
-            nat.check(lib.gc_cuda_bn_apply(yconv.data_ptr(), m, cout, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
-                                           nat.ptr(res), int(relu), out.data_ptr(), st()), "bn_apply")
+            if pool:
+                # act = relu(bn(yconv)) is never written: only its 2x2 max-pooled map is
+                assert res is None
+                out = torch.empty((n, cout, ho // 2, wo // 2), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+                nat.check(lib.gc_cuda_bn_apply_pool(yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(), gamma.data_ptr(),
+                                                    beta.data_ptr(), int(relu), out.data_ptr(), st()), "bn_apply_pool")
+            else:
+                out = torch.empty_like(yconv)
+                nat.check(lib.gc_cuda_bn_apply(yconv.data_ptr(), m, cout, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                               nat.ptr(res), int(relu), out.data_ptr(), st()), "bn_apply")
         ctx.relu, ctx.has_res, ctx.has_cbias = bool(relu), residual is not None, cbias is not None
         ctx.save_for_backward(x, w, yconv, gamma, beta, stats, out if (residual is not None and relu) else None, gathered)
         return out
@@ -387,13 +402,24 @@ class _ConvBNAct(torch.autograd.Function):
         dconv = torch.empty_like(yconv)
         dres = own_grad(torch.empty_like(yconv)) if (ctx.has_res and ctx.needs_input_grad[5]) else None
         with torch.cuda.device(x.device):
-            nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
-                                                gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),
-                                                _scratch_for(x.device, cout).data_ptr(), sums.data_ptr(), _fin_ptr(x.device, cout), st()), "bn_bwd_reduce")
-            nat.count_launch()
-            nat.check(lib.gc_cuda_bn_bwd_apply(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
-                                               gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),
-                                               dconv.data_ptr(), nat.ptr(dres), st()), "bn_bwd_apply")
+            if ctx.pool:
+                # dy is the gradient of the pooled map: both kernels find each window's winner again from yconv
+                nat.check(lib.gc_cuda_bn_bwd_reduce_pool(dy.data_ptr(), yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(),
+                                                         gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),
+                                                         _scratch_for(x.device, cout).data_ptr(), sums.data_ptr(), st()),
+                          "bn_bwd_reduce_pool")
+                nat.count_launch()
+                nat.check(lib.gc_cuda_bn_bwd_apply_pool(dy.data_ptr(), yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(),
+                                                        gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),
+                                                        dconv.data_ptr(), st()), "bn_bwd_apply_pool")
+            else:
+                nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
+                                                    gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),
+                                                    _scratch_for(x.device, cout).data_ptr(), sums.data_ptr(), _fin_ptr(x.device, cout), st()), "bn_bwd_reduce")
+                nat.count_launch()
+                nat.check(lib.gc_cuda_bn_bwd_apply(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
+                                                   gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),
+                                                   dconv.data_ptr(), nat.ptr(dres), st()), "bn_bwd_apply")
             dx = None
             link = ctx.link
             if ctx.needs_input_grad[0]:
@@ -403,9 +429,20 @@ class _ConvBNAct(torch.autograd.Function):
                     if not (link.stash_owned and acc.shape == x.shape and acc.dtype == torch.float32
                             and acc.is_contiguous(memory_format=torch.channels_last)):
                         acc = acc.contiguous(memory_format=torch.channels_last).clone()     # not ours to write into
+                h_in, w_in = x.shape[2], x.shape[3]
+                in_place = (stride == 1 and mode in ("gemm", "conv") and DGRAD_IN_PLACE and _filter_in_place_ok(w)
+                            and lib.gc_cuda_conv_dgrad_supported(n, h_in, w_in, cin, cout, r, pad))
                 tc_dgrad = mode == "gemm" or (mode == "conv" and stride == 1 and
                                               lib.gc_cuda_conv_fwd_supported(n, ho, wo, cout, cin, r, 1, r - 1 - pad))
-                if tc_dgrad:
+                if in_place:
+                    # dX = dY (*) rot(W) with the forward filter read in place as the MN-major operand: no transposed copy
+                    accumulate = acc is not None and gemm.can_accumulate(_as_2d(acc))
+                    dx = acc if accumulate else torch.empty_like(x)
+                    nat.check(lib.gc_cuda_conv_dgrad(dconv.data_ptr(), w.data_ptr(), dx.data_ptr(), n, h_in, w_in, cin, cout, r, pad,
+                                                     int(accumulate), _err(x.device), st()), "conv_dgrad")
+                    if acc is not None and not accumulate:
+                        dx += acc
+                elif tc_dgrad:
                     wd_ = _dgrad_weights.get(w)           # [Cin, taps * Cout]: the K-major operand of dX = dY (*) rot(W)
                     accumulate = acc is not None and gemm.can_accumulate(_as_2d(acc))
                     dx = acc if accumulate else torch.empty_like(x)
@@ -415,12 +452,12 @@ class _ConvBNAct(torch.autograd.Function):
                         conv_forward(dconv, wd_, None, 1, r - 1 - pad, out=dx, accumulate=accumulate)
                     if acc is not None and not accumulate:
                         dx += acc
-                elif (mode == "conv" and stride == 2 and "dgrad_s2" in PATHS
+                elif (mode == "conv" and stride == 2 and "dgrad_s2" in PATHS and _filter_in_place_ok(w)
                       and lib.gc_cuda_conv_dgrad_s2_supported(n, x.shape[2], x.shape[3], cin, cout, r, pad)):
                     # one launch per parity class of input pixels, each a stride-1 convolution of dY written through a
                     # strided 4-D store map
                     dx = torch.empty_like(x)
-                    nat.check(lib.gc_cuda_conv_dgrad_s2(dconv.data_ptr(), _dgrad_weights.get(w, 2, pad).data_ptr(), dx.data_ptr(), n,
+                    nat.check(lib.gc_cuda_conv_dgrad_s2(dconv.data_ptr(), w.data_ptr(), dx.data_ptr(), n,
                                                         x.shape[2], x.shape[3], cin, cout, r, pad, _err(x.device), st()),
                               "conv_dgrad_s2")
                     if acc is not None:
@@ -457,7 +494,7 @@ class _ConvBNAct(torch.autograd.Function):
             # a bias in front of a training-mode batch norm has no effect on the output: its gradient is the sum of
             # dconv over all positions, which the batch norm's backward makes zero up to rounding
             dcb = torch.zeros(cout, dtype=torch.float32, device=x.device) if ctx.has_cbias else None
-        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None, None
+        return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None, None, None
 
 
 def _mode(conv, bn, x):
@@ -496,14 +533,22 @@ def _mode(conv, bn, x):
     return mode if mode in PATHS else None
 
 
-def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None, donate=None):
+def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None, donate=None, pool=False):
     """``act(bn(conv(x)) + residual)`` on the tensor-core kernels where the layer qualifies (cuDNN + the fused BN kernels
     otherwise).  ``link``: see ``GradLink``.  ``donate``: the ``GradLink`` of an earlier-created layer that reads the same
     ``x`` (a block's first convolution, when this layer is the projection shortcut): this layer's input gradient is then
-    handed to that layer's input-gradient kernel to add onto."""
+    handed to that layer's input-gradient kernel to add onto.  ``pool=True``: a 2x2 / stride-2 max-pool of the result, folded
+    into the BN kernels (no residual)."""
     mode = _mode(conv, bn, x)
+    if mode is not None and pool:
+        n, _, h, w = x.shape
+        r, sd, pd = conv.kernel_size[0], conv.stride[0], conv.padding[0]
+        ho, wo = (h + 2 * pd - r) // sd + 1, (w + 2 * pd - r) // sd + 1
+        if residual is not None or not nat.cuda().gc_cuda_bn_pool_supported(n, ho, wo, conv.out_channels):
+            return torch.nn.functional.max_pool2d(conv_bn_act(conv, bn, x, residual, relu, link, donate), 2, 2)
     if mode is None:
-        return bn_act(bn, conv(x), residual=residual, relu=relu)
+        y = bn_act(bn, conv(x), residual=residual, relu=relu)
+        return torch.nn.functional.max_pool2d(y, 2, 2) if pool else y
     if link is not None:
         link.armed = LINK_ENABLED and torch.is_grad_enabled() and x.requires_grad
     training = bn.training or bn.running_mean is None
@@ -514,4 +559,4 @@ def conv_bn_act(conv, bn, x, residual=None, relu=True, link=None, donate=None):
     rv = bn.running_var if bn.track_running_stats else None
     return _ConvBNAct.apply(x, conv.weight, conv.bias, bn.weight, bn.bias, residual, rm, rv, training, momentum,
                             bn.eps, relu, link if (link is not None and link.armed) else None, mode, conv.stride[0],
-                            conv.padding[0], donate if (donate is not None and donate.armed) else None)
+                            conv.padding[0], donate if (donate is not None and donate.armed) else None, bool(pool))

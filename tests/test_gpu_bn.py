@@ -174,12 +174,24 @@ def test_conv1x1_bn_act_matches_torch(tc_conv, shape, residual, relu):
     assert torch.allclose(bn_a.running_var, bn_b.running_var, rtol=5e-3, atol=1e-3)
 
 
-def test_input_gradient_follows_weight_updates(tc_conv):
-    """The input-gradient GEMM reads cached transposed weights.  They must follow (a) the fused SGD kernel, which
-    writes parameters through raw pointers and re-transposes all of them in one launch, and (b) in-place torch
-    updates, which the version counter reveals."""
+@pytest.mark.parametrize("in_place", [False, True])
+def test_input_gradient_follows_weight_updates(tc_conv, in_place):
+    """The input-gradient kernels read the filter where it lies (``in_place``) or, for shapes that path does not cover,
+    cached transposed copies.  The copies must follow (a) the fused SGD kernel, which writes parameters through raw pointers
+    and re-transposes all of them in one launch, and (b) in-place torch updates, which the version counter reveals."""
+    from gradient_compression_b200.ops import conv as convmod
     from gradient_compression_b200.ops.conv import conv_bn_act
     from gradient_compression_b200.parallel.arena import FlatArena, FlatSGD
+
+    old = convmod.DGRAD_IN_PLACE
+    convmod.DGRAD_IN_PLACE = in_place
+    try:
+        _input_gradient_follows(conv_bn_act, FlatArena, FlatSGD, in_place)
+    finally:
+        convmod.DGRAD_IN_PLACE = old
+
+
+def _input_gradient_follows(conv_bn_act, FlatArena, FlatSGD, in_place):
 
     cl = torch.channels_last
     torch.manual_seed(5)
@@ -208,7 +220,8 @@ def test_input_gradient_follows_weight_updates(tc_conv):
             with torch.no_grad():                        # in-place torch update: the version counter moves
                 for c in convs:
                     c.weight.add_(torch.randn_like(c.weight) * 0.3)
-    assert getattr(arena, "_dgrad_weight_table", None) is not None and arena._dgrad_weight_table[1].shape[0] == 2
+    if not in_place:
+        assert getattr(arena, "_dgrad_weight_table", None) is not None and arena._dgrad_weight_table[1].shape[0] == 2
 
 
 @pytest.mark.parametrize("owned", [True, False])

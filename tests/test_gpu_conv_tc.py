@@ -182,6 +182,39 @@ def test_conv_input_gradient_exact_on_small_integers(shape):
     _same(acc, base + ref)
 
 
+@pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[6] == 1] + [(6, 16, 16, 96, 64, 3, 1, 1), (4, 7, 9, 64, 160, 1, 1, 0),
+                                                                     (128, 4, 4, 2048, 512, 1, 1, 0), (5, 8, 8, 64, 64, 3, 1, 0)])
+def test_conv_input_gradient_reading_the_filter_in_place(shape, tile_n):
+    """dX with the forward filter [Cout][R][S][Cin] as the MN-major B operand (taps rotated by the kernel's addressing, no
+    transposed copy); plain, accumulating, and with the contraction split where the cost model says so."""
+    from gradient_compression_b200.ops import conv, gemm
+
+    n, h, w, cin, cout, r, stride, pad = shape
+    if tile_n and tile_n // 2 >= cin:
+        pytest.skip("tile wider than the output")
+    g = torch.Generator().manual_seed(sum(shape) + 12)
+    x = _cl(_ints((n, cin, h, w), g).cuda())
+    wt = _cl(_ints((cout, cin, r, r), g, -2, 3).cuda())
+    ho, wo = h + 2 * pad - r + 1, w + 2 * pad - r + 1
+    dy = _cl(_ints((n, cout, ho, wo), g).cuda())
+    lib = conv.nat.cuda()
+    assert lib.gc_cuda_conv_dgrad_supported(n, h, w, cin, cout, r, pad)
+    ref = _conv_backward64(dy, x, wt, 1, pad, 0)
+    base = _cl(_ints((n, cin, h, w), g).cuda())
+    dx, acc = torch.full_like(x, 7.0), base.clone(memory_format=torch.preserve_format)
+    gemm.configure("auto", tile_n)
+    try:
+        for out, accumulate in ((dx, 0), (acc, 1)):
+            conv.nat.check(lib.gc_cuda_conv_dgrad(dy.data_ptr(), wt.data_ptr(), out.data_ptr(), n, h, w, cin, cout, r, pad, accumulate,
+                                                  gemm._error_flag(x.device).data_ptr(), conv.nat.stream_ptr()), "conv_dgrad")
+    finally:
+        gemm.configure("auto", 0)
+    gemm.check()
+    _same(dx, ref)
+    _same(acc, base + ref)
+
+
 def test_dgrad_filter_refresh_kernel_matches_torch():
     """The batched kernel that rebuilds rotated / transposed filters after an optimiser step."""
     from gradient_compression_b200.ops import conv
@@ -208,7 +241,8 @@ def test_dgrad_filter_refresh_kernel_matches_torch():
 
 @pytest.mark.parametrize("shape", [s for s in SHAPES if s[6] == 2] + [(3, 8, 8, 64, 96, 3, 2, 1), (5, 4, 4, 128, 64, 1, 2, 0)])
 def test_conv_stride2_input_gradient_exact_on_small_integers(shape):
-    """Four launches, one per parity class of input pixels, each storing through a strided 4-D map."""
+    """Four launches, one per parity class of input pixels, each storing through a strided 4-D map and reading its taps of the
+    forward filter in place."""
     from gradient_compression_b200.ops import conv, gemm
 
     n, h, w, cin, cout, r, stride, pad = shape
@@ -219,9 +253,8 @@ def test_conv_stride2_input_gradient_exact_on_small_integers(shape):
     lib = conv.nat.cuda()
     assert lib.gc_cuda_conv_dgrad_s2_supported(n, h, w, cin, cout, r, pad)
     ref = _conv_backward64(dy, x, wt, 2, pad, 0)
-    wd = conv._dgrad_weights.get(wt, 2, pad)
     dx = torch.full_like(x, 7.0)
-    conv.nat.check(lib.gc_cuda_conv_dgrad_s2(dy.data_ptr(), wd.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, pad,
+    conv.nat.check(lib.gc_cuda_conv_dgrad_s2(dy.data_ptr(), wt.data_ptr(), dx.data_ptr(), n, h, w, cin, cout, r, pad,
                                              gemm._error_flag(x.device).data_ptr(), conv.nat.stream_ptr()), "conv_dgrad_s2")
     gemm.check()
     _same(dx, ref)
@@ -325,6 +358,90 @@ def test_conv_bn_act_matches_unfused_modules(cin, cout, r, stride, hw, bias, res
         assert close(resid.grad, resid_r.grad, 6e-2)
     if bias:
         assert float(conv_.bias.grad.abs().max()) == 0.0 and float(conv_r.bias.grad.abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("cin,cout,hw,n,training", [(64, 64, 32, 4, True), (128, 256, 8, 16, True), (512, 512, 2, 32, True),
+                                                     (3, 64, 32, 8, True), (256, 256, 4, 8, False)])
+def test_conv_bn_relu_maxpool_in_one_pass(cin, cout, hw, n, training):
+    """VGG's conv + BN + ReLU + 2x2 max-pool with the pool folded into the BN kernels (the full-resolution activation is never
+    written; the backward routes the pooled gradient to each window's winner) against the four modules in float64."""
+    from gradient_compression_b200.ops import conv, gemm
+
+    torch.manual_seed(cin + cout + hw)
+    conv_, bn_ = _block(cin, cout, 3, 1, True)
+    conv_, bn_ = conv_.cuda().to(memory_format=torch.channels_last), bn_.cuda()
+    conv_r, bn_r = _block(cin, cout, 3, 1, True)
+    conv_r, bn_r = conv_r.cuda().double(), bn_r.cuda().double()
+    conv_r.load_state_dict(conv_.state_dict())
+    bn_r.load_state_dict(bn_.state_dict())
+    for mod in (conv_, bn_, conv_r, bn_r):
+        mod.train(training)
+    x = _cl(torch.randn(n, cin, hw, hw, device="cuda")).requires_grad_(cin > 3 and training)
+    xr = x.detach().double().requires_grad_(cin > 3 and training)
+    with torch.set_grad_enabled(training):          # (an eval-mode layer takes the kernels only where no gradient is asked for)
+        assert conv._mode(conv_, bn_, x) is not None and conv.nat.cuda().gc_cuda_bn_pool_supported(n, hw, hw, cout)
+        y = conv.conv_bn_act(conv_, bn_, x, pool=True)
+        yr = F.max_pool2d(F.relu(bn_r(conv_r(xr))), 2, 2)
+    assert y.shape == yr.shape
+
+    def close(a, b, tol):
+        a, b = a.detach().double(), b.detach().double()
+        err = float((a - b).norm() / b.norm().clamp_min(1e-30))
+        assert err <= tol, f"relative Frobenius error {err} above {tol}"
+
+    close(y, yr, 5e-3)
+    if training:
+        gy = _cl(torch.randn_like(y))
+        y.backward(gy)
+        yr.backward(gy.double())
+        gemm.check()
+        close(conv_.weight.grad, conv_r.weight.grad, 6e-2)
+        close(bn_.weight.grad, bn_r.weight.grad, 6e-2)
+        close(bn_.bias.grad, bn_r.bias.grad, 6e-2)
+        close(bn_.running_var, bn_r.running_var, 5e-3)
+        if cin > 3:
+            close(x.grad, xr.grad, 6e-2)
+
+
+def test_bn_pool_kernels_match_the_unfused_kernels_exactly():
+    """Same arithmetic as BN apply followed by torch's max-pool: the pooled forward is bit-identical; the backward equals the
+    plain BN backward fed with torch's max-pool backward up to the order of the channel sums."""
+    from gradient_compression_b200.ops import bn as bnmod
+    from gradient_compression_b200.ops import _native as nat
+
+    lib, st = nat.cuda(), nat.stream_ptr
+    n, c, h, w = 6, 128, 12, 20
+    g = torch.Generator().manual_seed(4)
+    y = _cl(torch.randn(n, c, h, w, generator=g).cuda() * 2 + 0.3)
+    gamma, beta = torch.randn(c, generator=g).cuda(), torch.randn(c, generator=g).cuda()
+    mean, var = y.mean((0, 2, 3)), y.var((0, 2, 3), unbiased=False)
+    stats = torch.cat([mean, torch.rsqrt(var + 1e-5)]).contiguous()
+    m = n * h * w
+    act = torch.empty_like(y)
+    nat.check(lib.gc_cuda_bn_apply(y.data_ptr(), m, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), None, 1, act.data_ptr(), st()), "a")
+    pooled = torch.empty(n, c, h // 2, w // 2, device="cuda").contiguous(memory_format=torch.channels_last)
+    nat.check(lib.gc_cuda_bn_apply_pool(y.data_ptr(), n, h, w, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), 1,
+                                        pooled.data_ptr(), st()), "b")
+    ref_pool = F.max_pool2d(act, 2, 2)
+    assert torch.equal(pooled, ref_pool)
+    # backward: route dpool with torch's pooling backward, then the plain kernels
+    dpool = _cl(torch.randn(n, c, h // 2, w // 2, generator=g).cuda())
+    a = act.clone().requires_grad_(True)
+    F.max_pool2d(a, 2, 2).backward(dpool)
+    dfull = _cl(a.grad)
+    scratch = bnmod._scratch_for(y.device, c)
+    sums_a, sums_b = torch.empty(2 * c, device="cuda"), torch.empty(2 * c, device="cuda")
+    dx_a, dx_b = torch.empty_like(y), torch.empty_like(y)
+    nat.check(lib.gc_cuda_bn_bwd_reduce(dfull.data_ptr(), y.data_ptr(), None, m, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), 1,
+                                        scratch.data_ptr(), sums_a.data_ptr(), None, st()), "c")
+    nat.check(lib.gc_cuda_bn_bwd_apply(dfull.data_ptr(), y.data_ptr(), None, m, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                       sums_a.data_ptr(), 1, dx_a.data_ptr(), None, st()), "d")
+    nat.check(lib.gc_cuda_bn_bwd_reduce_pool(dpool.data_ptr(), y.data_ptr(), n, h, w, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), 1,
+                                             scratch.data_ptr(), sums_b.data_ptr(), st()), "e")
+    nat.check(lib.gc_cuda_bn_bwd_apply_pool(dpool.data_ptr(), y.data_ptr(), n, h, w, c, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                            sums_b.data_ptr(), 1, dx_b.data_ptr(), st()), "f")
+    assert torch.allclose(sums_a, sums_b, rtol=1e-5, atol=1e-4)
+    assert torch.allclose(dx_a, dx_b, rtol=1e-4, atol=1e-5)
 
 
 @pytest.mark.parametrize("m,n,k", [(131072, 64, 64), (4096, 256, 128), (2048, 2048, 512), (1000, 96, 64), (128 * 300, 512, 32)])

@@ -160,6 +160,30 @@ def test_fused_allreduce_emulated(world, n):
         grp.close()
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_one_shot_launches_of_alternating_sizes_share_one_arena(world):
+    """PowerSGD's P and Q sums, Rand-K windows and bucketed reducers launch one-shot kernels of different sizes on one arena,
+    back to back and with no closing round.  The two parity regions sit a fixed distance apart (a function of the arena,
+    not of the call), so a small launch after a large one must not land in the region the previous launch's readers may
+    still use: every result of a long alternating sequence has to be exact."""
+    n = (1 << 18) + 3
+    grp, fo = _group(world, n)
+    try:
+        sizes = [n, 7, 4099, n, 129, 65537, 5, n, 4099, 7]
+        g = torch.Generator().manual_seed(world)
+        for step, m in enumerate(sizes * 2):
+            xs = [torch.randn(m, generator=g) for _ in range(world)]
+            outs = [torch.empty(m, device="cuda") for _ in range(world)]
+            fo.small_sum([x.cuda() for x in xs], outs, alpha=0.25)
+            acc = torch.zeros(m)
+            for x in xs:
+                acc += x
+            assert all(torch.equal(o.cpu(), acc * 0.25) for o in outs), (step, m)
+        fo.check()
+    finally:
+        grp.close()
+
+
 @pytest.mark.parametrize("world", [1, 2, 8])
 @pytest.mark.parametrize("hi", [0, 6])
 @pytest.mark.parametrize("zero", [False, True])
