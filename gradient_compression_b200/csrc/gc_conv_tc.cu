@@ -263,16 +263,19 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
   int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : ((Cin == 64 && No % 192 == 0) ? 192 : 64));
   if (gctc::tile_choice && (Cin % gctc::tile_choice == 0 || (Cin == 64 && No % gctc::tile_choice == 0))) tile = gctc::tile_choice;
   CUtensorMap ma, mb, mc;
-  if (make_map_mn(&ma, dy, P, Cout, Cout) != 0 || make_map_nhwc(&mb, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) != 0 ||
+  int box3d = 0;        // dy as one 3-D box per stage where the driver accepts that view, else four 2-D boxes
+  if (make_map_mn3(&ma, dy, P, Cout, Cout, TBK, BM / 32) == 0) box3d = 1;
+  else if (make_map_mn(&ma, dy, P, Cout, Cout) != 0) return (int)cudaErrorInvalidValue;
+  if (make_map_nhwc(&mb, x, s, bw, bh, bn, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) != 0 ||
       make_map(&mc, dw, Cout, No, No, BM) != 0)
     return (int)cudaErrorInvalidValue;
   const ConvA ca = conv_a(s);
   cudaStream_t st = (cudaStream_t)cs;
   switch (tile) {
-    case 64: return launch_tn_maps<64>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
-    case 128: return launch_tn_maps<128>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
-    case 192: return launch_tn_maps<192>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
-    case 256: return launch_tn_maps<256>(ma, mb, mc, ca, P, Cout, No, error_flag, st);
+    case 64: return launch_tn_maps<64>(ma, mb, mc, ca, P, Cout, No, error_flag, st, box3d);
+    case 128: return launch_tn_maps<128>(ma, mb, mc, ca, P, Cout, No, error_flag, st, box3d);
+    case 192: return launch_tn_maps<192>(ma, mb, mc, ca, P, Cout, No, error_flag, st, box3d);
+    case 256: return launch_tn_maps<256>(ma, mb, mc, ca, P, Cout, No, error_flag, st, box3d);
     default: return (int)cudaErrorInvalidValue;
   }
 }

@@ -283,10 +283,14 @@ template <int BN>
 int launch_tn(const float* A, const float* B, float* C, int P, int Mo, int No, int64_t lda, int64_t ldb, int64_t ldc,
               int* error_flag, cudaStream_t st) {
   CUtensorMap ma, mb, mc;
-  if (make_map_mn(&ma, A, P, Mo, lda) != 0 || make_map_mn(&mb, B, P, No, ldb) != 0 ||
-      make_map(&mc, C, Mo, No, ldc, BM) != 0)
+  int box3d = 0;        // whole-operand 3-D boxes where the matrix is made of whole 32-float chunks
+  if ((Mo & 31) == 0 && make_map_mn3(&ma, A, P, Mo, lda, TBK, BM / 32) == 0) box3d |= 1;
+  else if (make_map_mn(&ma, A, P, Mo, lda) != 0) return (int)cudaErrorInvalidValue;
+  if ((No & 31) == 0 && make_map_mn3(&mb, B, P, No, ldb, TBK, BN / 32) == 0) box3d |= 2;
+  else if (make_map_mn(&mb, B, P, No, ldb) != 0) return (int)cudaErrorInvalidValue;
+  if (make_map(&mc, C, Mo, No, ldc, BM) != 0)
     return (int)cudaErrorInvalidValue;
-  return launch_tn_maps<BN>(ma, mb, mc, ConvA{}, P, Mo, No, error_flag, st);
+  return launch_tn_maps<BN>(ma, mb, mc, ConvA{}, P, Mo, No, error_flag, st, box3d);
 }
 
 // 0 = choose, 1 = one tile per CTA, 2 = persistent;  tile width 0 = choose

@@ -663,7 +663,7 @@ template <int BN>
 __global__ void __launch_bounds__(TN_THREADS, 1)
 gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const __grid_constant__ CUtensorMap tma_c, const ConvA ca, int P, int Mo, int No, int tiles_n, int splits,
-                    int kblocks_per_split, int* __restrict__ error_flag, int tma_mode) {
+                    int kblocks_per_split, int* __restrict__ error_flag, int tma_mode, int box3d) {
   using S = TnSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -728,17 +728,26 @@ gemm_tn_tf32_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
         int a_boxes = (Mo - m0 + 31) / 32, b_boxes = (No - n0 + 31) / 32;
         a_boxes = a_boxes < BM / 32 ? a_boxes : BM / 32;
         b_boxes = b_boxes < BN / 32 ? b_boxes : BN / 32;
-        const uint32_t stage_tx = (uint32_t)((a_boxes + b_boxes) * S::CHUNK_BYTES);
+        // box3d bit 0 / 1: the A / B map is the 3-D view {32 floats, rows, chunks} of the matrix and ONE box brings the whole
+        // operand of a stage (chunks beyond the matrix arrive as zeros and count as bytes)
+        const bool a3 = (box3d & 1) != 0, b3 = (box3d & 2) != 0 && ca.taps == 0;
+        const uint32_t stage_tx = (uint32_t)((a3 ? BM / 32 : a_boxes) * S::CHUNK_BYTES + (b3 ? BN / 32 : b_boxes) * S::CHUNK_BYTES);
         for (int k = warp; k < num_k; k += PRODUCER_WARPS) {
           const int s = k % S::STAGES;
           const uint32_t phase = (uint32_t)(k / S::STAGES) & 1u;
           if (!mbar_wait(&empty[s], phase ^ 1u, &abort_flag)) break;
           mbar_expect_tx(&full[s], stage_tx);
           const int row0 = (k_begin + k) * TBK;
+          if (a3) {
+            tma_load_3d(a_tiles + s * S::A_BYTES, &tma_a, 0, row0, m0 >> 5, &full[s]);
+          } else {
 #pragma unroll
-          for (int c = 0; c < BM / 32; ++c)
-            if (c < a_boxes) tma_load_2d(a_tiles + s * S::A_BYTES + c * S::CHUNK_BYTES, &tma_a, m0 + c * 32, row0, &full[s]);
-          if (ca.taps == 0) {
+            for (int c = 0; c < BM / 32; ++c)
+              if (c < a_boxes) tma_load_2d(a_tiles + s * S::A_BYTES + c * S::CHUNK_BYTES, &tma_a, m0 + c * 32, row0, &full[s]);
+          }
+          if (b3) {
+            tma_load_3d(b_tiles + s * S::B_BYTES, &tma_b, 0, row0, n0 >> 5, &full[s]);
+          } else if (ca.taps == 0) {
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
               if (c < b_boxes) tma_load_2d(b_tiles + s * S::B_BYTES + c * S::CHUNK_BYTES, &tma_b, n0 + c * 32, row0, &full[s]);
@@ -932,7 +941,7 @@ int launch_persistent_maps(const CUtensorMap& ma, const CUtensorMap& mb, const C
 // 131072- and 32768-position weight gradients of ResNet-50 (fewer partial tiles to add, longer pipelines), equal below.
 template <int BN>
 int launch_tn_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const ConvA& ca, int P, int Mo, int No,
-                   int* error_flag, cudaStream_t st) {
+                   int* error_flag, cudaStream_t st, int box3d = 0) {
   using S = TnSmem<BN>;
   static bool configured = false;
   if (!configured) {
@@ -951,7 +960,7 @@ int launch_tn_maps(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorM
   int per = (total_k + splits - 1) / splits;
   splits = (total_k + per - 1) / per;
   gemm_tn_tf32_kernel<BN><<<(unsigned)(tiles * splits), TN_THREADS, S::TOTAL, st>>>(ma, mb, mc, ca, P, Mo, No, tiles_n, splits, per,
-                                                                                     error_flag, gctc::tma_mode);
+                                                                                     error_flag, gctc::tma_mode, box3d);
   return (int)cudaGetLastError();
 }
 
