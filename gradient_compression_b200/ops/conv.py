@@ -493,7 +493,10 @@ class _ConvBNAct(torch.autograd.Function):
                                                              [0, 0], 1, [False, True, False])[1]
             # a bias in front of a training-mode batch norm has no effect on the output: its gradient is the sum of
             # dconv over all positions, which the batch norm's backward makes zero up to rounding
-            dcb = torch.zeros(cout, dtype=torch.float32, device=x.device) if ctx.has_cbias else None
+            # (where the weight's owner keeps a zeroed flat gradient buffer -- the slot offer above -- the bias' place in it
+            # already holds that zero, and returning nothing saves a fill and an accumulation per layer)
+            dcb = (torch.zeros(cout, dtype=torch.float32, device=x.device)
+                   if ctx.has_cbias and not (WGRAD_ENABLED and _slot_of(w) is not None) else None)
         return dx, dw, dcb, sums[cout:], sums[:cout], dres, None, None, None, None, None, None, None, None, None, None, None, None
 
 
