@@ -40,8 +40,23 @@ __device__ __forceinline__ void block_two_sums(int64_t M, int C, int64_t row_beg
   const int rofs = threadIdx.x / vec;
   const int rstep = BN_THREADS / vec;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  if (row_end >= 0) {
 #pragma unroll 4
-  for (int64_t r = row_begin + rofs; r < row_end; r += rstep) f(r, col, a, b);
+    for (int64_t r = row_begin + rofs; r < row_end; r += rstep) f(r, col, a, b);
+  } else {
+    // interleaved mode (row_end < 0): the grid walks the tensor from its END in chunks of 4 * rstep rows, block b taking the
+    // chunks b, b + gridDim.x, ...: the kernel that runs before a backward reduction wrote the gradient it reads, and the
+    // end of that tensor is what the L2 still holds
+    const int64_t chunk = (int64_t)rstep * 4;
+    for (int64_t hi = M - (int64_t)blockIdx.x * chunk; hi > 0; hi -= (int64_t)gridDim.x * chunk) {
+      const int64_t lo = hi - chunk;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int64_t r = lo + rofs + (int64_t)k * rstep;
+        if (r >= 0) f(r, col, a, b);
+      }
+    }
+  }
   float4* sa = reinterpret_cast<float4*>(smem);
   float4* sb = sa + BN_THREADS;
   sa[threadIdx.x] = a;
@@ -196,11 +211,13 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_reduce_kernel(const float* 
                                                                    int64_t rows_per_block, const float* __restrict__ stats,
                                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                    int relu, float* __restrict__ partials, double* __restrict__ acc,
-                                                                   unsigned int* __restrict__ ticket, float* __restrict__ sums) {
+                                                                   unsigned int* __restrict__ ticket, float* __restrict__ sums,
+                                                                   int g_interleave) {
   pdl_wait();
   pdl_launch_dependents();
   int64_t r0 = (int64_t)blockIdx.x * rows_per_block;
   int64_t r1 = r0 + rows_per_block < M ? r0 + rows_per_block : M;
+  if (g_interleave) r1 = -1;                      // block_two_sums: chunks from the end of the tensor, round-robin over blocks
   const int col = threadIdx.x % (C >> 2);
   const float4 mu = ld4(stats + 4 * col), rs = ld4(stats + C + 4 * col);
   const float4 gm = ld4(gamma + 4 * col), bt = ld4(beta + 4 * col);
@@ -457,6 +474,7 @@ inline int reduce_grid(int64_t M, int C, int64_t* rows_per_block) {
 }
 
 int64_t g_bwd_fused_atomics_limit = 200000;
+int g_bwd_reduce_interleave = 1;
 
 inline int apply_grid(int64_t nq) {
   int64_t need = (nq + BN_THREADS - 1) / BN_THREADS;
@@ -517,7 +535,7 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
   double* acc = fused ? reinterpret_cast<double*>(static_cast<uint8_t*>(fin_scratch) + 256) : nullptr;
   unsigned int* ticket = fused ? static_cast<unsigned int*>(fin_scratch) : nullptr;
   launch_pdl(bn_bwd_reduce_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dy, x, y, M, C, rpb, stats, gamma, beta,
-             relu, (float*)scratch, acc, ticket, sums);
+             relu, (float*)scratch, acc, ticket, sums, g_bwd_reduce_interleave);
   if (!fused)
     launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
   return (int)cudaGetLastError();
@@ -526,6 +544,10 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
 // Above this many atomics per launch (blocks x 2C) the backward reduction keeps its separate finalize kernel: with many
 // blocks on a wide, short activation the atomics would cost more than the second launch.
 void gc_cuda_bn_bwd_fused_limit(int64_t atomics) { g_bwd_fused_atomics_limit = atomics; }
+
+// For measurements: 1 = the backward reduction walks the tensor from its end in interleaved chunks, 0 = one contiguous row
+// range per block.
+void gc_cuda_bn_bwd_reduce_interleave(int on) { g_bwd_reduce_interleave = on ? 1 : 0; }
 
 int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
                          const float* gamma, const float* beta, const float* sums, int relu, float* dx, float* dres,
