@@ -338,6 +338,8 @@ def run_reference(args, world, rank, local_rank):
         red = cls(device, timer, rank=args.rank)
     elif args.reducer in ("TopKReducer", "GlobalTopKReducer"):
         red = cls(device, timer, K=args.K)
+    elif args.reducer in ("TopKReducerRatio", "GlobalTopKReducerRatio"):
+        red = cls(device, timer)                 # compression 1 / 100, the reference's default (reducer.py:1234)
     else:
         red = cls(device, timer, quantization_level=args.bits)
     model = RefCIFAR(device, timer, args.model, 42 + local_rank)
