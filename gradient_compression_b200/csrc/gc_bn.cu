@@ -474,7 +474,7 @@ inline int reduce_grid(int64_t M, int C, int64_t* rows_per_block) {
 }
 
 int64_t g_bwd_fused_atomics_limit = 200000;
-int g_bwd_reduce_interleave = 1;
+int g_bwd_reduce_interleave = 0;   // measured inside the ResNet-50 step: 7.47 ms with, 7.46 ms without
 
 inline int apply_grid(int64_t nq) {
   int64_t need = (nq + BN_THREADS - 1) / BN_THREADS;
@@ -545,8 +545,8 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
 // blocks on a wide, short activation the atomics would cost more than the second launch.
 void gc_cuda_bn_bwd_fused_limit(int64_t atomics) { g_bwd_fused_atomics_limit = atomics; }
 
-// For measurements: 1 = the backward reduction walks the tensor from its end in interleaved chunks, 0 = one contiguous row
-// range per block.
+// For measurements: 1 = the backward reduction walks the tensor from its end in interleaved chunks, 0 (default) = one
+// contiguous row range per block.
 void gc_cuda_bn_bwd_reduce_interleave(int on) { g_bwd_reduce_interleave = on ? 1 : 0; }
 
 int gc_cuda_bn_bwd_apply(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats,
