@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from ..ops.bn import defer_batch_counters
+from ..ops.bn import defer_batch_counters, flush_batch_counters
 from ..ops.conv import GradLink, conv_bn_act
 from ..ops.head import head_loss
 from .layers import bn, conv, head_pool, linear
@@ -89,6 +89,7 @@ class ResNet(nn.Module):
         """``(loss, logits, [cross-entropy, top-1, top-5])``: pooling, the linear layer, the loss and the batch metrics in
         one kernel when the final map is 4 x 4 (``F.avg_pool2d(out, 4)`` then covers it whole, models/resnet.py:106)."""
         f = self.features(x)
+        flush_batch_counters()          # (the forward hook that batches the BN step counters only fires for __call__)
         if f.shape[2] == 4 and f.shape[3] == 4:
             return head_loss(f, self.linear, labels)
         return head_loss(head_pool(f, 4)[:, :, None, None], self.linear, labels)

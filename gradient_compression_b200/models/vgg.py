@@ -5,6 +5,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
+from ..ops.bn import defer_batch_counters, flush_batch_counters
 from ..ops.conv import conv_bn_act
 from ..ops.head import head_loss
 from .layers import bn, conv, linear
@@ -30,6 +31,7 @@ class VGG(nn.Module):
         layers.append(nn.AvgPool2d(kernel_size=1, stride=1))
         self.features = nn.Sequential(*layers)
         self.classifier = linear(512, 10)
+        defer_batch_counters(self)
 
     def forward(self, x):
         return self.classifier(self._features(x).flatten(1))
@@ -38,6 +40,7 @@ class VGG(nn.Module):
         """``(loss, logits, [cross-entropy, top-1, top-5])`` with the linear layer, the loss and the batch metrics in one kernel
         (the feature map is 1 x 1 after the fifth max-pool: models/vgg.py:88,109 of the reference)."""
         f = self._features(x)
+        flush_batch_counters()          # (the forward hook that batches the BN step counters only fires for __call__)
         if f.shape[2] * f.shape[3] != 1:
             f = f.flatten(1)[:, :, None, None]
         return head_loss(f, self.classifier, labels)

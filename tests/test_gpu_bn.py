@@ -289,6 +289,24 @@ def test_projection_block_hands_its_input_gradient_to_the_first_convolution(tc_c
         assert float((a - b).norm() / b.norm()) < 1e-5
 
 
+@pytest.mark.parametrize("name", ["ResNet18", "VGG11"])
+def test_batch_counters_follow_the_fused_loss_path(name):
+    """``forward_loss`` (the path the trainer and the graphed step take) does not go through ``__call__``: the deferred
+    ``num_batches_tracked`` increments must still land, once per training forward."""
+    from gradient_compression_b200 import models
+    from gradient_compression_b200.ops import bn as bnmod
+
+    model = getattr(models, name)().cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(4, 3, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (4,), device="cuda")
+    model.train()
+    for _ in range(3):
+        model.forward_loss(x, y)
+    assert not bnmod._pending_counters
+    counters = [m.num_batches_tracked for m in model.modules() if isinstance(m, torch.nn.BatchNorm2d)]
+    assert len(counters) >= 8 and all(int(c) == 3 for c in counters)
+
+
 def test_batch_counters_are_batched_but_exact():
     """``num_batches_tracked`` of every batch norm of a zoo model moves by one per training forward (one multi-tensor
     launch at the end of the forward), stays put in eval mode, and is counted per use when a layer runs twice."""
