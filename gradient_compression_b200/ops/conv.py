@@ -11,13 +11,15 @@
   then the GEMM with K = 32.
 
 The epilogue of each emits the per-channel sums the batch norm needs, so the activation is written once and read once
-(by the apply pass).  Backward: fused BN backward kernels; input gradient on the same kernels with the filter rotated
-by 180 degrees and its channel axes swapped (one batched kernel refreshes those copies after every optimiser step;
-in identity blocks the product is added straight onto the skip connection's gradient: ``GradLink``); weight gradient
-``dY^T X`` on the split-K kernel with MN-major operands, per filter tap from shifted boxes.  The input gradient of a
-stride-2 convolution is four launches of the forward kernel, one per parity class of input pixels, each writing its
-pixels through a strided 4-D store map.  Grouped convolutions and shapes the tilings exclude use cuDNN through
-``bn_act(bn, conv(x))`` or ``aten.convolution_backward``.
+(by the apply pass; ``pool=True`` folds a following 2x2 max-pool into that pass and its backward).  Backward: fused BN
+backward kernels; input gradient on the same kernel run on dY, reading the forward filter in place as an MN-major operand
+whose taps the kernel addresses rotated by 180 degrees (for shapes that path does not cover: a rotated / transposed copy
+that one batched kernel refreshes after every optimiser step); in residual blocks the product is added straight onto the
+skip connection's or projection shortcut's gradient (``GradLink``); weight gradient ``dY^T X`` on the split-K kernel with
+MN-major operands, per filter tap from shifted boxes, added straight into the owner's flat gradient buffer.  The input
+gradient of a stride-2 convolution is four launches of the forward kernel, one per parity class of input pixels, each
+writing its pixels through a strided 4-D store map.  Grouped convolutions and shapes the tilings exclude use cuDNN
+through ``bn_act(bn, conv(x))`` or ``aten.convolution_backward``.
 
 The reference builds the same layers from ``nn.Conv2d`` + ``nn.BatchNorm2d`` + ``F.relu`` module calls
 (models/resnet.py:45-76, models/vgg.py:96-110 of the reference).
