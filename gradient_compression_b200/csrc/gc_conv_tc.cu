@@ -240,6 +240,10 @@ int gc_cuda_conv_dgrad(const float* dy, const float* w, float* dx, int N, int H,
   }
 }
 
+// For measurements: 1 = weight gradients at Cin = 128 use 256-column tiles that hold two filter taps (measured slower than
+// one tap per 128-column tile: 35.8 vs 33.8 us at 16x16, 25.6 vs 21.5 us at 8x8 -- two 96 KB stages do not hide the loads).
+void gc_cuda_conv_wgrad_two_taps(int on) { gctc::wgrad_two_taps = on ? 1 : 0; }
+
 // 1 when the weight gradient of this convolution can run on the tensor cores: Cin a multiple of 64, Cout of 32, and
 // 64 consecutive output positions form one box.
 int gc_cuda_conv_wgrad_supported(int N, int H, int W, int Cin, int Cout, int R, int stride, int pad) {
@@ -261,6 +265,7 @@ int gc_cuda_conv_wgrad(const float* dy, const float* x, float* dw, int N, int H,
   // a tile's columns stay inside one filter tap, except at Cin = 64: there a tile of 192 columns holds three taps side by
   // side (64-column MMAs leave the issuing thread, not the tensor pipe, as the limit)
   int tile = (Cin % 256 == 0) ? 256 : ((Cin % 128 == 0) ? 128 : ((Cin == 64 && No % 192 == 0) ? 192 : 64));
+  if (gctc::wgrad_two_taps && Cin == 128 && R > 1) tile = 256;            // two taps side by side: MMAs of 256 columns
   if (gctc::tile_choice && (Cin % gctc::tile_choice == 0 || (Cin == 64 && No % gctc::tile_choice == 0))) tile = gctc::tile_choice;
   CUtensorMap ma, mb, mc;
   int box3d = 0;        // dy as one 3-D box per stage where the driver accepts that view, else four 2-D boxes

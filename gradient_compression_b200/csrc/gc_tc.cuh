@@ -27,6 +27,7 @@ namespace gctc {
 inline int tile_choice = 0;
 inline int tn_ctas_per_sm = 1;
 inline int tn_min_kblocks = 4;
+inline int wgrad_two_taps = 0;
 inline int split_choice = 0;   // contraction splits of the persistent kernel: 0 = modelled, 1 = never, n = n where a product allows it
 inline int tma_mode = 1;   // bit 0: prefetch the tensor maps at kernel start; bit 2: epilogue warps sleep between polls while a tile is being accumulated
 }  // namespace gctc

@@ -154,6 +154,7 @@ def cuda():
         _declare(lib, "gc_cuda_tc_tma_mode", None, [c_int])
         _declare(lib, "gc_cuda_conv_fwd_supported", c_int, [c_int] * 8)
         _declare(lib, "gc_cuda_conv_fwd_splits", c_int, [c_int] * 8)
+        _declare(lib, "gc_cuda_conv_wgrad_two_taps", None, [c_int])
         _declare(lib, "gc_cuda_conv_dgrad_supported", c_int, [c_int] * 7)
         _declare(lib, "gc_cuda_conv_dgrad", c_int, [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P])
         _declare(lib, "gc_cuda_gemm_tf32_splits", c_int, [c_int] * 3)
