@@ -19,7 +19,8 @@ def main(argv=None):
     ap.add_argument("--norm-scope", default="global", choices=["global", "bucket"],
                     help="bucket: per-bucket reduces on a side stream beside backward")
     ap.add_argument("--bucket-mb", type=float, default=25.0)
-    ap.add_argument("--timeline", type=int, default=0, help="also print the first N kernels of one step with start time and stream")
+    ap.add_argument("--timeline", type=int, default=0,
+                    help="also print, with their start times inside the last step, its first N kernels and every reducer / optimiser kernel")
     ap.add_argument("--eager-ops", action="store_true",
                     help="run the step eagerly and list the torch operators by device time (which op launches which kernels)")
     args = ap.parse_args(argv)
@@ -74,8 +75,7 @@ def main(argv=None):
         t0 = one[0].time_range.start
         print(f"timeline of the last step ({per_step} kernels): start us, duration us, name")
         picked = [e for e in one if "fused" in e.name or "sgd" in e.name or "multi_tensor" in e.name]
-        for e in (one[: args.timeline] if args.timeline < per_step else one):
-            pass
+        picked = sorted(set(picked + one[: args.timeline]), key=lambda e: e.time_range.start)
         for e in picked:
             print(f"{e.time_range.start - t0:10.1f} {e.device_time:8.1f}  {e.name[:70]}")
         print(f"{one[-1].time_range.end - t0:10.1f} end of step")
