@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_fwd_kernel(const float* __r
                                                                 unsigned int* __restrict__ ticket, float* __restrict__ out3) {
   __shared__ __align__(16) float sp[HEAD_MAX_CHANNELS];
   __shared__ float slog[HEAD_MAX_CLASSES];
+  __shared__ float spart[HEAD_THREADS / 32][HEAD_MAX_CLASSES];
   __shared__ int last;
   const int n = blockIdx.x;
   const float* xn = x + (int64_t)n * positions * C;
@@ -49,20 +50,34 @@ __global__ void __launch_bounds__(HEAD_THREADS) head_fwd_kernel(const float* __r
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int k = warp; k < K; k += HEAD_THREADS / 32) {
-    float acc = 0.f;
-    const float* wk = W + (int64_t)k * C;
-#pragma unroll 4
-    for (int c = lane * 4; c < C; c += 128) {                // C is a multiple of 4: whole quads, several loads in flight
-      const float4 wv = *reinterpret_cast<const float4*>(wk + c);
+  {
+    // every warp takes 128-channel slices of the pooled vector and all K classes at once (K independent 16-byte loads of
+    // W in flight per lane); the eight warps' partial dot products meet in shared memory in a fixed order
+    float acc[HEAD_MAX_CLASSES];
+#pragma unroll
+    for (int k = 0; k < HEAD_MAX_CLASSES; ++k) acc[k] = 0.f;
+    for (int c = warp * 128 + lane * 4; c < C; c += (HEAD_THREADS / 32) * 128) {
       const float4 pv = *reinterpret_cast<const float4*>(sp + c);
-      acc = fmaf(pv.x, wv.x, acc); acc = fmaf(pv.y, wv.y, acc); acc = fmaf(pv.z, wv.z, acc); acc = fmaf(pv.w, wv.w, acc);
+#pragma unroll
+      for (int k = 0; k < HEAD_MAX_CLASSES; ++k)
+        if (k < K) {
+          const float4 wv = *reinterpret_cast<const float4*>(W + (int64_t)k * C + c);
+          acc[k] = fmaf(pv.x, wv.x, fmaf(pv.y, wv.y, fmaf(pv.z, wv.z, fmaf(pv.w, wv.w, acc[k]))));
+        }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      acc += bias != nullptr ? bias[k] : 0.f;
-      slog[k] = acc;
-      logits[(int64_t)n * K + k] = acc;
+#pragma unroll
+    for (int k = 0; k < HEAD_MAX_CLASSES; ++k)
+      if (k < K) {
+        const float v = warp_sum(acc[k]);
+        if (lane == 0) spart[warp][k] = v;
+      }
+    __syncthreads();
+    if (threadIdx.x < K) {
+      float v = bias != nullptr ? bias[threadIdx.x] : 0.f;
+#pragma unroll
+      for (int w = 0; w < HEAD_THREADS / 32; ++w) v += spart[w][threadIdx.x];
+      slog[threadIdx.x] = v;
+      logits[(int64_t)n * K + threadIdx.x] = v;
     }
   }
   __syncthreads();
