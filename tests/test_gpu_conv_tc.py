@@ -184,7 +184,8 @@ def test_conv_input_gradient_exact_on_small_integers(shape):
 
 @pytest.mark.parametrize("tile_n", [0, 64, 128, 256])
 @pytest.mark.parametrize("shape", [s for s in SHAPES if s[6] == 1] + [(6, 16, 16, 96, 64, 3, 1, 1), (4, 7, 9, 64, 160, 1, 1, 0),
-                                                                     (128, 4, 4, 2048, 512, 1, 1, 0), (5, 8, 8, 64, 64, 3, 1, 0)])
+                                                                     (128, 4, 4, 2048, 512, 1, 1, 0), (5, 8, 8, 64, 64, 3, 1, 0),
+                                                                     (4, 8, 8, 48, 64, 3, 1, 1), (6, 8, 8, 80, 96, 1, 1, 0)])
 def test_conv_input_gradient_reading_the_filter_in_place(shape, tile_n):
     """dX with the forward filter [Cout][R][S][Cin] as the MN-major B operand (taps rotated by the kernel's addressing, no
     transposed copy); plain, accumulating, and with the contraction split where the cost model says so."""

@@ -211,3 +211,46 @@ def test_device_timeout_surfaces_within_two_steps_and_falls_back():
         finally:
             torch.cuda.synchronize()
             grp.close()
+
+
+ZOO = ["LeNet", "ResNet18", "ResNet50", "PreActResNet18", "densenet_cifar", "MobileNet", "MobileNetV2", "SENet18", "PNASNetB",
+       "EfficientNetB0", "RegNetX_200MF", "ShuffleNetG2", "ShuffleNetV2_x0_5", "ResNeXt29_32x4d", "GoogLeNet", "DPN26", "VGG11",
+       "VGG16"]
+
+
+@pytest.mark.parametrize("name", ZOO)
+def test_zoo_model_gradients_on_the_kernels_match_the_torch_path(name):
+    """One forward + backward of a zoo model on the GPU with this library's convolution / BN / pooling kernels wherever a layer
+    qualifies, against the same model and weights on cuDNN + torch ops in fp32.  Deep batch-norm networks at random
+    initialisation amplify TF32 rounding a lot (cuDNN's own TF32 gradients of ResNet-50 differ from its fp32 ones by half their
+    norm), so the yardstick is torch's TF32 run: this library's distance to the fp32 gradients must be of the same size.
+    Catches a layer shape that a kernel accepts but mishandles."""
+    from gradient_compression_b200 import models
+    from gradient_compression_b200.ops import conv as convmod
+    from gradient_compression_b200.ops import gemm
+
+    torch.manual_seed(3)
+    net = getattr(models, name)().cuda().to(memory_format=torch.channels_last)
+    x = torch.randn(16, 3, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (16,), device="cuda")
+    state = {k: v.clone() for k, v in net.state_dict().items()}
+
+    def run(kernels, tf32):
+        net.load_state_dict(state)
+        net.zero_grad(set_to_none=True)
+        old = (convmod.ENABLED, torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32)
+        convmod.ENABLED, torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = kernels, tf32, tf32
+        try:
+            loss = torch.nn.functional.cross_entropy(net(x), y)
+            loss.backward()
+        finally:
+            convmod.ENABLED, torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+        return float(loss.detach()), torch.cat([p.grad.reshape(-1) for p in net.parameters() if p.grad is not None])
+
+    (la, ga), (lb, gb), (lc, gc) = run(True, True), run(False, True), run(False, False)
+    gemm.check()
+    assert ga.shape == gc.shape and torch.isfinite(ga).all() and la == la
+    ours = float((ga - gc).norm() / gc.norm())
+    torch_tf32 = float((gb - gc).norm() / gc.norm())
+    assert ours <= 1.3 * torch_tf32 + 0.05, (ours, torch_tf32)
+    assert abs(la - lc) <= 3.0 * abs(lb - lc) + 2e-2 * max(1.0, abs(lc)), (la, lb, lc)
