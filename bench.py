@@ -73,6 +73,12 @@ class ClockSampler:
         self.idx = device_index
         self.proc = None
         self.lines = []
+        self.first = 0
+
+    def mark(self):
+        """The timed region starts here: samples taken before (the sampler is started ahead of the warm-up steps, so that the
+        process is up and printing when the clock starts) are not counted, unless the region is too short to catch one."""
+        self.first = len(self.lines)
 
     def start(self):
         try:
@@ -98,7 +104,8 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        lines = self.lines[self.first:] or self.lines[-1:]        # a region shorter than the 50 ms period: the sample just before it
+        for line in lines:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 8:
                 continue
@@ -226,12 +233,13 @@ def run_ours(args, world, rank, local_rank):
     # first calls of the step function; run them before the W official warm-up steps
     for i in range(6 if args.graph else 2):
         step_fn(dev_batches[i % 4])
-    for i in range(args.warmup):
-        step_fn(dev_batches[i % 4])
-    barrier_sync()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        step_fn(dev_batches[i % 4])
+    barrier_sync()
+    sampler.mark()
     launches0 = ops.launches()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -361,12 +369,13 @@ def run_reference(args, world, rank, local_rank):
     gen = torch.Generator(device=device).manual_seed(1234 + rank)
     dev_batches = [(torch.randn(args.batch, 3, 32, 32, device=device, generator=gen),
                     torch.randint(0, 10, (args.batch,), device=device, generator=gen)) for _ in range(4)]
-    for i in range(args.warmup):
-        ref_step(dev_batches[i % 4])
-    barrier_sync()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        ref_step(dev_batches[i % 4])
+    barrier_sync()
+    sampler.mark()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for i in range(args.steps):
