@@ -75,6 +75,12 @@ class ClockSampler:
         self.lines = []
         self.first = 0
 
+    def wait_ready(self, timeout=3.0):
+        """Returns once nvidia-smi has printed its first sample (its start-up takes a few hundred milliseconds)."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
+
     def mark(self):
         """The timed region starts here: samples taken before (the sampler is started ahead of the warm-up steps, so that the
         process is up and printing when the clock starts) are not counted, unless the region is too short to catch one."""
@@ -236,6 +242,7 @@ def run_ours(args, world, rank, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_ready()
     for i in range(args.warmup):
         step_fn(dev_batches[i % 4])
     barrier_sync()
@@ -372,6 +379,7 @@ def run_reference(args, world, rank, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        sampler.wait_ready()
     for i in range(args.warmup):
         ref_step(dev_batches[i % 4])
     barrier_sync()
