@@ -9,11 +9,12 @@
 //                                do not meet the TMA store rules (plain-store epilogue).
 //   gemm_tn_tf32_kernel          C[Mo, No] += A[P, Mo]^T * B[P, No]: both operands MN-major, split-K.  Weight gradients.
 //
-// Common structure, no clusters, no multicast:
-//   warp 0   TMA producer: cp.async.bulk.tensor.2d (128-byte swizzle) into a ring of shared-memory stages
-//   warp 1   allocates TMEM, issues tcgen05.mma (one elected thread), commits stages back to the producer
-//   warps 2+ epilogue: tcgen05.ld of the fp32 accumulator from TMEM, bias add, 32-column slabs staged in shared
-//            memory (128-byte swizzled, bank-conflict free) and written with TMA stores / TMA reduce stores
+// Common structure, no clusters, no multicast (the persistent and the TN kernel are templates in gc_tc.cuh, shared with the
+// convolution entry points of gc_conv_tc.cu; they run two producer warps, the tile kernel in this file one):
+//   producer warps  TMA loads (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages
+//   MMA warp        allocates TMEM, issues tcgen05.mma (one elected thread), commits stages back to the producers
+//   epilogue warps  tcgen05.ld of the fp32 accumulator from TMEM, bias add, 32-column slabs staged in shared
+//                   memory (128-byte swizzled, bank-conflict free) and written with TMA stores / TMA reduce stores
 // Every mbarrier wait is bounded; when one runs out the CTA sets *error_flag, abandons its tile, frees
 // its TMEM and returns.
 #include <cuda.h>
