@@ -104,29 +104,39 @@ __device__ __forceinline__ void finish_two_sums(int C, double* __restrict__ acc,
   if (threadIdx.x == 0) *ticket = 0u;
 }
 
-// Combine the per-block partials of 32 consecutive channels (both sums) in double precision.
-// block = (32, FIN_Y, 2): x = channel in the group, y strides over partial blocks, z = which of the two sums.
+// Combine the per-block partials of blockDim.x consecutive channels (both sums) in double precision.
+// block = (channels, FY, 2) with channels * FY <= 512: x = channel in the group, y strides over partial blocks, z = which of
+// the two sums.  (32, 16, 2) by default; (8, 64, 2) when there are many partials of few channels (the 1024 row tiles of a
+// 64- or 256-channel first-stage layer), which cuts the serial loads per thread fourfold.
 constexpr int FIN_Y = 16;
 __device__ __forceinline__ void combine_partials(const float* __restrict__ partials, int nparts, int C, double (&out)[2]) {
-  __shared__ double red[2][FIN_Y][32];
-  int c = blockIdx.x * 32 + threadIdx.x;
+  __shared__ double red[2][512];
+  const int cx = blockDim.x, fy = blockDim.y;
+  int c = blockIdx.x * cx + threadIdx.x;
   double acc = 0.0;
   if (c < C) {
     const float* base = partials + threadIdx.z * C + c;
     int b = threadIdx.y;
-    for (; b + 3 * FIN_Y < nparts; b += 4 * FIN_Y) {   // four independent loads in flight per thread
-      float v0 = base[(int64_t)b * 2 * C], v1 = base[(int64_t)(b + FIN_Y) * 2 * C];
-      float v2 = base[(int64_t)(b + 2 * FIN_Y) * 2 * C], v3 = base[(int64_t)(b + 3 * FIN_Y) * 2 * C];
+    for (; b + 3 * fy < nparts; b += 4 * fy) {   // four independent loads in flight per thread
+      float v0 = base[(int64_t)b * 2 * C], v1 = base[(int64_t)(b + fy) * 2 * C];
+      float v2 = base[(int64_t)(b + 2 * fy) * 2 * C], v3 = base[(int64_t)(b + 3 * fy) * 2 * C];
       acc += ((double)v0 + (double)v1) + ((double)v2 + (double)v3);
     }
-    for (; b < nparts; b += FIN_Y) acc += (double)base[(int64_t)b * 2 * C];
+    for (; b < nparts; b += fy) acc += (double)base[(int64_t)b * 2 * C];
   }
-  red[threadIdx.z][threadIdx.y][threadIdx.x] = acc;
+  red[threadIdx.z][threadIdx.y * cx + threadIdx.x] = acc;
   __syncthreads();
   out[0] = out[1] = 0.0;
   if (threadIdx.y == 0 && threadIdx.z == 0) {
-    for (int k = 0; k < FIN_Y; ++k) { out[0] += red[0][k][threadIdx.x]; out[1] += red[1][k][threadIdx.x]; }
+    for (int k = 0; k < fy; ++k) { out[0] += red[0][k * cx + threadIdx.x]; out[1] += red[1][k * cx + threadIdx.x]; }
   }
+}
+
+// Launch shape of the two finalize kernels for `nparts` partial rows of C channels.
+inline void finalize_shape(int nparts, int C, dim3* grid, dim3* block) {
+  const int cx = (nparts >= 256 && C <= 256) ? 8 : 32;
+  *block = cx == 8 ? dim3(8, 64, 2) : dim3(32, FIN_Y, 2);
+  *grid = dim3((C + cx - 1) / cx);
 }
 
 // ---------------------------------------------------------------------------------- forward statistics
@@ -157,7 +167,7 @@ __global__ void bn_stats_finalize_kernel(const float* __restrict__ partials, con
   pdl_launch_dependents();
   double sums[2];
   combine_partials(partials, nparts, C, sums);
-  int c = blockIdx.x * 32 + threadIdx.x;
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (threadIdx.y != 0 || threadIdx.z != 0 || c >= C) return;
   double dmean = sums[0] / (double)M;              // mean of the shifted values
   double var = sums[1] / (double)M - dmean * dmean;
@@ -247,7 +257,7 @@ __global__ void bn_sums_finalize_kernel(const float* __restrict__ partials, int 
   pdl_launch_dependents();
   double out[2];
   combine_partials(partials, nparts, C, out);
-  int c = blockIdx.x * 32 + threadIdx.x;
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (threadIdx.y != 0 || threadIdx.z != 0 || c >= C) return;
   sums[c] = (float)out[0];
   sums[C + c] = (float)out[1];
@@ -500,7 +510,9 @@ int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* sta
   int grid = reduce_grid(M, C, &rpb);
   size_t smem = 2 * BN_THREADS * sizeof(float4);
   launch_pdl(bn_stats_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, x, M, C, rpb, (float*)scratch);
-  launch_pdl(bn_stats_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, x, grid, M,
+  dim3 fg, fb;
+  finalize_shape(grid, C, &fg, &fb);
+  launch_pdl(bn_stats_finalize_kernel, fg, fb, 0, (cudaStream_t)cs, (const float*)scratch, x, grid, M,
              C, stats, running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }
@@ -508,7 +520,9 @@ int gc_cuda_bn_stats(const float* x, int64_t M, int C, void* scratch, float* sta
 // Statistics from partial column sums produced elsewhere (the GEMM epilogue): partials[nparts][2][C], unshifted.
 int gc_cuda_bn_finalize_partials(const float* partials, int nparts, int64_t M, int C, float* stats, float* running_mean,
                                  float* running_var, float momentum, float eps, void* cs) {
-  launch_pdl(bn_stats_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, partials, (const float*)nullptr,
+  dim3 fg, fb;
+  finalize_shape(nparts, C, &fg, &fb);
+  launch_pdl(bn_stats_finalize_kernel, fg, fb, 0, (cudaStream_t)cs, partials, (const float*)nullptr,
              nparts, M, C, stats, running_mean, running_var, momentum, eps);
   return (int)cudaGetLastError();
 }
@@ -537,7 +551,11 @@ int gc_cuda_bn_bwd_reduce(const float* dy, const float* x, const float* y, int64
   launch_pdl(bn_bwd_reduce_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dy, x, y, M, C, rpb, stats, gamma, beta,
              relu, (float*)scratch, acc, ticket, sums, g_bwd_reduce_interleave);
   if (!fused)
-    launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
+    {
+      dim3 fg, fb;
+      finalize_shape(grid, C, &fg, &fb);
+      launch_pdl(bn_sums_finalize_kernel, fg, fb, 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
+    }
   return (int)cudaGetLastError();
 }
 
@@ -585,7 +603,9 @@ int gc_cuda_bn_bwd_reduce_pool(const float* dpool, const float* x, int N, int H,
   size_t smem = 2 * BN_THREADS * sizeof(float4);
   launch_pdl(bn_bwd_reduce_pool_kernel, dim3(grid), dim3(BN_THREADS), smem, (cudaStream_t)cs, dpool, x, g, Mp, C, rpb, stats, gamma,
              beta, relu, (float*)scratch);
-  launch_pdl(bn_sums_finalize_kernel, dim3((C + 31) / 32), dim3(32, FIN_Y, 2), 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
+  dim3 fg, fb;
+  finalize_shape(grid, C, &fg, &fb);
+  launch_pdl(bn_sums_finalize_kernel, fg, fb, 0, (cudaStream_t)cs, (const float*)scratch, grid, C, sums);
   return (int)cudaGetLastError();
 }
 
