@@ -137,6 +137,7 @@ def cuda():
         _declare(lib, "gc_cuda_psgd_p", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, c_i64, P])
         _declare(lib, "gc_cuda_psgd_gs", c_int, [P, P, c_int, c_float, P])
         _declare(lib, "gc_cuda_psgd_q_chunks", c_int, [c_int])
+        _declare(lib, "gc_cuda_psgd_q_blocks", c_i64, [c_int, c_int])
         _declare(lib, "gc_cuda_psgd_q", c_int, [P, P, c_int, c_i64, P, P, c_i64, c_int, P])
         _declare(lib, "gc_cuda_psgd_out", c_int, [P, P, P, c_int, c_i64, P, P, P, c_int, P, c_float, P])
         _declare(lib, "gc_cuda_topk_state_bytes", c_i64, [c_int])

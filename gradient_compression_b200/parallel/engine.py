@@ -270,7 +270,7 @@ class FusedEngine:
         for (i, n, m, r, po, qo) in plan["hi"]:
             mats.append([flat._start_idx[i], n, m, r, po, qo, rows, tiles])
             rows += n
-            tiles += (m + 127) // 128
+            tiles += int(nat.cuda().gc_cuda_psgd_q_blocks(n, m))        # 128-column tiles x row chunks of this matrix
         vecs, voff = [], 0
         for i in plan["lo"]:
             ln = flat._end_idx[i] - flat._start_idx[i]
