@@ -336,7 +336,7 @@ int gc_cuda_psgd_p(const float* g, float* e, const int64_t* tab, int n_mats, int
     int64_t cap = (int64_t)psgd_sms() * 8;
     psgd_p_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, st>>>(g, e, tab, n_mats, total_rows, q, stage);
   }
-  if (n_vecs > 0) psgd_pack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 128, 0, st>>>(g, vtab, n_vecs, stage + vec_base);
+  if (n_vecs > 0) psgd_pack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 512, 0, st>>>(g, vtab, n_vecs, stage + vec_base);
   return (int)cudaGetLastError();
 }
 
@@ -374,7 +374,7 @@ int gc_cuda_psgd_out(float* g, float* e, const int64_t* tab, int n_mats, int64_t
     psgd_out_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, st>>>(g, e, tab, n_mats, total_rows, p, q);
   }
   if (n_vecs > 0)
-    psgd_unpack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 128, 0, st>>>(g, e, vtab, n_vecs, summed_vecs, alpha);
+    psgd_unpack_vec_kernel<<<n_vecs < 256 ? n_vecs : 256, 512, 0, st>>>(g, e, vtab, n_vecs, summed_vecs, alpha);
   return (int)cudaGetLastError();
 }
 
