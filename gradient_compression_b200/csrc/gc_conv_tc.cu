@@ -83,30 +83,38 @@ bool wgrad_ok(const Shape& s) {
 
 // A[p][k] = x[n, h + r - pad, w + s - pad, c] with k = (r * R + s) * Cin + c (zero outside the image and for
 // k >= R*R*Cin), stride 1; wpad[co][k] = w[co][k] padded to Kp columns.  One thread per (position, 4 columns).
+constexpr int IM2COL_MAX_KP = 128;
+
 __global__ void __launch_bounds__(256) im2col_small_kernel(const float* __restrict__ x, float* __restrict__ A, int N, int H, int W,
                                                            int Cin, int R, int pad, int Kp, const float* __restrict__ w,
                                                            float* __restrict__ wpad, int Cout, int64_t quads) {
   const int K = R * R * Cin;
   const int qpr = Kp >> 2;
-  for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t p = q / qpr;
-    const int k0 = (int)(q - p * qpr) * 4;
-    const int wo = (int)(p % W), ho = (int)((p / W) % H);
-    const int64_t n = p / ((int64_t)W * H);
+  // column k -> (row offset, column offset, channel) of its filter tap, once per block (no divisions per element); -1: padding
+  __shared__ int tap_dh[IM2COL_MAX_KP], tap_dw[IM2COL_MAX_KP], tap_c[IM2COL_MAX_KP];
+  for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+    const int tap = k / Cin;
+    tap_c[k] = k < K ? k - tap * Cin : -1;
+    tap_dh[k] = tap / R - pad;
+    tap_dw[k] = tap % R - pad;
+  }
+  __syncthreads();
+  const uint32_t uq = (uint32_t)quads, uqpr = (uint32_t)qpr, uW = (uint32_t)W, uH = (uint32_t)H;      // host: quads < 2^31
+  for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < uq; q += gridDim.x * blockDim.x) {
+    const uint32_t p = q / uqpr;
+    const int k0 = (int)(q - p * uqpr) * 4;
+    const uint32_t row = p / uW;
+    const int wo = (int)(p - row * uW);
+    const uint32_t n = row / uH;
+    const int ho = (int)(row - n * uH);
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int k = k0 + j;
-      float val = 0.f;
-      if (k < K) {
-        const int tap = k / Cin, c = k - tap * Cin;
-        const int r = tap / R, s = tap - r * R;
-        const int hi = ho + r - pad, wi = wo + s - pad;
-        if (hi >= 0 && hi < H && wi >= 0 && wi < W) val = x[((n * H + hi) * W + wi) * Cin + c];
-      }
-      v[j] = val;
+      const int c = tap_c[k], hi = ho + tap_dh[k], wi = wo + tap_dw[k];
+      v[j] = (c >= 0 && hi >= 0 && hi < H && wi >= 0 && wi < W) ? x[(((int64_t)n * H + hi) * W + wi) * Cin + c] : 0.f;
     }
-    *reinterpret_cast<float4*>(A + p * Kp + k0) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(A + (int64_t)p * Kp + k0) = make_float4(v[0], v[1], v[2], v[3]);
   }
   if (wpad != nullptr) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < Cout * Kp; i += gridDim.x * blockDim.x) {
@@ -384,6 +392,7 @@ int gc_cuda_im2col_small(const float* x, float* A, int N, int H, int W, int Cin,
                          float* wpad, int Cout, void* cs) {
   if (N < 1 || H < 1 || W < 1 || Cin < 1 || R < 1 || pad < 0 || Kp < R * R * Cin || (Kp & 3) || 2 * pad != R - 1) return (int)cudaErrorInvalidValue;
   const int64_t quads = (int64_t)N * H * W * (Kp >> 2);
+  if (Kp > IM2COL_MAX_KP || quads > 0x7fffffff) return (int)cudaErrorInvalidValue;
   int64_t blocks = (quads + 255) / 256;
   if (blocks > (int64_t)sm_count() * 16) blocks = (int64_t)sm_count() * 16;
   im2col_small_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)cs>>>(x, A, N, H, W, Cin, R, pad, Kp, w, wpad, Cout, quads);
