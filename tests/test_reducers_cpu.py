@@ -328,7 +328,6 @@ def _reference_body(rank, world):
         assert ours.reduce([t.clone() for t in mine], o) == theirs.reduce([t.clone() for t in mine], o), name
 
 
-@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_DIR, "reducer.py")), reason="reference sources not mounted")
 def _near_max_body(rank, world):
     # every rank holds the same tensor with most entries at +-max: each contributes level +-63 at 6 bits, the sum of four
     # (252) does not fit the int8 container the levels are produced in
@@ -359,5 +358,6 @@ def test_level_sums_do_not_wrap_in_their_container(dist_runner):
     dist_runner(_near_max_body, world=4)
 
 
+@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_DIR, "reducer.py")), reason="reference sources not mounted")
 def test_parity_with_reference_reducers(dist_runner):
     dist_runner(_reference_body, world=2)
