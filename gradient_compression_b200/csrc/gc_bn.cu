@@ -453,6 +453,189 @@ __global__ void __launch_bounds__(BN_THREADS) bn_bwd_apply_pool_kernel(const flo
   }
 }
 
+// ---------------------------------------------------------------------------------- small activations: one kernel per direction
+// For the last stages of the networks (4x4 and 2x2 maps at batch 128: M <= 2048 rows) every BN kernel above runs for about
+// three microseconds of launch and drain around a few hundred kilobytes of work, and a layer needs five to seven of them.
+// Here a block owns 8 channels for ALL rows, so the statistics (forward) or the two gradient sums (backward) are complete
+// inside the block and the apply pass follows in the same kernel: statistics + finalize + apply forward, reduce + finalize +
+// apply backward.  256 threads = 2 channel quads x 128 row lanes.
+constexpr int SMALL_THREADS = 256;
+constexpr int SMALL_CH = 8;
+constexpr int SMALL_MAX_ROWS = 2048;
+
+// Sum of two float4 per-thread values over the 128 row lanes of each quad (fixed order); every thread leaves with the totals
+// of its own quad in (a, b).
+__device__ __forceinline__ void small_block_sums(float4& a, float4& b, float4* __restrict__ sm /* [2 * SMALL_THREADS] */) {
+  sm[threadIdx.x] = a;
+  sm[SMALL_THREADS + threadIdx.x] = b;
+  __syncthreads();
+  for (int s = SMALL_THREADS >> 1; s >= 2; s >>= 1) {          // thread t and t + s share the quad (s is even)
+    if ((int)threadIdx.x < s) {
+      const float4 o = sm[threadIdx.x + s], p = sm[SMALL_THREADS + threadIdx.x + s];
+      float4 m = sm[threadIdx.x], q = sm[SMALL_THREADS + threadIdx.x];
+      m.x += o.x; m.y += o.y; m.z += o.z; m.w += o.w;
+      q.x += p.x; q.y += p.y; q.z += p.z; q.w += p.w;
+      sm[threadIdx.x] = m;
+      sm[SMALL_THREADS + threadIdx.x] = q;
+    }
+    __syncthreads();
+  }
+  a = sm[threadIdx.x & 1];
+  b = sm[SMALL_THREADS + (threadIdx.x & 1)];
+  __syncthreads();
+}
+
+// Forward: y = act(gamma * (x - mean) * rstd + beta [+ residual]) with the batch statistics computed here -- from the
+// convolution kernel's per-tile partial sums when given (partials[nparts][2][C], unshifted), else from x itself (shifted sums).
+// Writes stats[0:C] = mean, stats[C:2C] = rstd and updates the running statistics.
+__global__ void __launch_bounds__(SMALL_THREADS) bn_small_fwd_kernel(const float* __restrict__ x, int M, int C,
+                                                                     const float* __restrict__ partials, int nparts,
+                                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                     const float* __restrict__ residual, int relu,
+                                                                     float* __restrict__ running_mean, float* __restrict__ running_var,
+                                                                     float momentum, float eps, float* __restrict__ stats,
+                                                                     float* __restrict__ y) {
+  __shared__ float4 sm[2 * SMALL_THREADS];
+  __shared__ float s_mean[SMALL_CH], s_rstd[SMALL_CH];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int qd = threadIdx.x & 1, rl = threadIdx.x >> 1;
+  const int c4 = blockIdx.x * SMALL_CH + 4 * qd;
+  const bool live = c4 < C;                                     // C % 4 == 0: a quad is whole or absent
+  if (partials == nullptr) {
+    const float4 k = live ? ld4(x + c4) : make_float4(0.f, 0.f, 0.f, 0.f);     // shift: the channel's value in row 0
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (live)
+      for (int r = rl; r < M; r += SMALL_THREADS / 2) {
+        float4 v = ld4(x + (int64_t)r * C + c4);
+        v.x -= k.x; v.y -= k.y; v.z -= k.z; v.w -= k.w;
+        a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        b.x = fmaf(v.x, v.x, b.x); b.y = fmaf(v.y, v.y, b.y); b.z = fmaf(v.z, v.z, b.z); b.w = fmaf(v.w, v.w, b.w);
+      }
+    small_block_sums(a, b, sm);
+    // (a, b) hold this thread's quad totals: lanes rl == 0 publish per-channel values
+    if (rl == 0 && live) {
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w}, kv[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const double dmean = (double)av[j] / (double)M;
+        double var = (double)bv[j] / (double)M - dmean * dmean;
+        if (var < 0.0) var = 0.0;
+        const double mean = (double)kv[j] + dmean;
+        const int c = c4 + j;
+        s_mean[4 * qd + j] = (float)mean;
+        s_rstd[4 * qd + j] = (float)(1.0 / sqrt(var + (double)eps));
+        stats[c] = (float)mean;
+        stats[C + c] = s_rstd[4 * qd + j];
+        if (running_mean != nullptr) {
+          const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+          running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * (float)mean;
+          running_var[c] = (1.0f - momentum) * running_var[c] + momentum * (float)unbiased;
+        }
+      }
+    }
+  } else if (threadIdx.x < SMALL_CH) {
+    const int c = blockIdx.x * SMALL_CH + threadIdx.x;
+    if (c < C) {
+      double sum = 0.0, sq = 0.0;
+      for (int t = 0; t < nparts; ++t) {
+        sum += (double)partials[((int64_t)t * 2) * C + c];
+        sq += (double)partials[((int64_t)t * 2 + 1) * C + c];
+      }
+      const double mean = sum / (double)M;
+      double var = sq / (double)M - mean * mean;
+      if (var < 0.0) var = 0.0;
+      s_mean[threadIdx.x] = (float)mean;
+      s_rstd[threadIdx.x] = (float)(1.0 / sqrt(var + (double)eps));
+      stats[c] = (float)mean;
+      stats[C + c] = s_rstd[threadIdx.x];
+      if (running_mean != nullptr) {
+        const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+        running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * (float)mean;
+        running_var[c] = (1.0f - momentum) * running_var[c] + momentum * (float)unbiased;
+      }
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  const float4 mu = make_float4(s_mean[4 * qd], s_mean[4 * qd + 1], s_mean[4 * qd + 2], s_mean[4 * qd + 3]);
+  const float4 rs = make_float4(s_rstd[4 * qd], s_rstd[4 * qd + 1], s_rstd[4 * qd + 2], s_rstd[4 * qd + 3]);
+  const float4 g = ld4(gamma + c4), bt = ld4(beta + c4);
+  for (int r = rl; r < M; r += SMALL_THREADS / 2) {
+    const int64_t at = (int64_t)r * C + c4;
+    const float4 v = ld4(x + at);
+    float4 o;
+    o.x = fmaf((v.x - mu.x) * rs.x, g.x, bt.x);
+    o.y = fmaf((v.y - mu.y) * rs.y, g.y, bt.y);
+    o.z = fmaf((v.z - mu.z) * rs.z, g.z, bt.z);
+    o.w = fmaf((v.w - mu.w) * rs.w, g.w, bt.w);
+    if (residual != nullptr) {
+      const float4 rr = ld4(residual + at);
+      o.x += rr.x; o.y += rr.y; o.z += rr.z; o.w += rr.w;
+    }
+    if (relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+    st4(y + at, o);
+  }
+}
+
+// Backward: sums[0:C] = dbeta, sums[C:2C] = dgamma, dx = gamma * rstd * (g - dbeta / M - xhat * dgamma / M), dres = g
+// (g = dy masked by the ReLU: from the saved output y when given, else recomputed from x).
+__global__ void __launch_bounds__(SMALL_THREADS) bn_small_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                                                     const float* __restrict__ y, int M, int C,
+                                                                     const float* __restrict__ stats, const float* __restrict__ gamma,
+                                                                     const float* __restrict__ beta, int relu,
+                                                                     float* __restrict__ sums, float* __restrict__ dx,
+                                                                     float* __restrict__ dres) {
+  __shared__ float4 sm[2 * SMALL_THREADS];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int qd = threadIdx.x & 1, rl = threadIdx.x >> 1;
+  const int c4 = blockIdx.x * SMALL_CH + 4 * qd;
+  const bool live = c4 < C;
+  float4 mu = make_float4(0.f, 0.f, 0.f, 0.f), rs = mu, gm = mu, bt = mu;
+  if (live) { mu = ld4(stats + c4); rs = ld4(stats + C + c4); gm = ld4(gamma + c4); bt = ld4(beta + c4); }
+  auto masked = [&](int64_t at, const float4& xh) {
+    float4 d = ld4(dy + at);
+    if (relu) {
+      if (y != nullptr) {
+        const float4 o = ld4(y + at);
+        d.x = o.x > 0.f ? d.x : 0.f; d.y = o.y > 0.f ? d.y : 0.f; d.z = o.z > 0.f ? d.z : 0.f; d.w = o.w > 0.f ? d.w : 0.f;
+      } else {
+        d.x = fmaf(xh.x, gm.x, bt.x) > 0.f ? d.x : 0.f; d.y = fmaf(xh.y, gm.y, bt.y) > 0.f ? d.y : 0.f;
+        d.z = fmaf(xh.z, gm.z, bt.z) > 0.f ? d.z : 0.f; d.w = fmaf(xh.w, gm.w, bt.w) > 0.f ? d.w : 0.f;
+      }
+    }
+    return d;
+  };
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+  if (live)
+    for (int r = rl; r < M; r += SMALL_THREADS / 2) {
+      const int64_t at = (int64_t)r * C + c4;
+      const float4 v = ld4(x + at);
+      const float4 xh = make_float4((v.x - mu.x) * rs.x, (v.y - mu.y) * rs.y, (v.z - mu.z) * rs.z, (v.w - mu.w) * rs.w);
+      const float4 d = masked(at, xh);
+      a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+      b.x = fmaf(d.x, xh.x, b.x); b.y = fmaf(d.y, xh.y, b.y); b.z = fmaf(d.z, xh.z, b.z); b.w = fmaf(d.w, xh.w, b.w);
+    }
+  small_block_sums(a, b, sm);                                   // a = dbeta quad, b = dgamma quad
+  if (!live) return;
+  if (rl == 0) { st4(sums + c4, a); st4(sums + C + c4, b); }
+  const float inv_m = 1.0f / (float)M;
+  for (int r = rl; r < M; r += SMALL_THREADS / 2) {
+    const int64_t at = (int64_t)r * C + c4;
+    const float4 v = ld4(x + at);
+    const float4 xh = make_float4((v.x - mu.x) * rs.x, (v.y - mu.y) * rs.y, (v.z - mu.z) * rs.z, (v.w - mu.w) * rs.w);
+    const float4 d = masked(at, xh);
+    if (dres != nullptr) st4(dres + at, d);
+    float4 o;
+    o.x = gm.x * rs.x * (d.x - a.x * inv_m - xh.x * b.x * inv_m);
+    o.y = gm.y * rs.y * (d.y - a.y * inv_m - xh.y * b.y * inv_m);
+    o.z = gm.z * rs.z * (d.z - a.z * inv_m - xh.z * b.z * inv_m);
+    o.w = gm.w * rs.w * (d.w - a.w * inv_m - xh.w * b.w * inv_m);
+    st4(dx + at, o);
+  }
+}
+
 int bn_sm_count() {
   static int sms = 0;
   if (sms == 0) {
@@ -617,6 +800,28 @@ int gc_cuda_bn_bwd_apply_pool(const float* dpool, const float* x, int N, int H, 
   const int64_t Mp = (int64_t)N * g.Hp * g.Wp;
   launch_pdl(bn_bwd_apply_pool_kernel, dim3(apply_grid(Mp * (C >> 2))), dim3(BN_THREADS), 0, (cudaStream_t)cs, dpool, x, g, Mp, C,
              stats, gamma, beta, sums, relu, dx);
+  return (int)cudaGetLastError();
+}
+
+// 1 when the single-kernel forms cover the activation: at most 2048 rows, C a multiple of 4.
+int gc_cuda_bn_small_supported(int64_t M, int C) { return M >= 1 && M <= SMALL_MAX_ROWS && C >= 4 && (C & 3) == 0 ? 1 : 0; }
+
+// Statistics (from partials[nparts][2][C] when given, else from x) + running-statistics update + apply, one launch.
+int gc_cuda_bn_small_forward(const float* x, int64_t M, int C, const float* partials, int nparts, const float* gamma, const float* beta,
+                             const float* residual, int relu, float* running_mean, float* running_var, float momentum, float eps,
+                             float* stats, float* y, void* cs) {
+  if (!gc_cuda_bn_small_supported(M, C)) return (int)cudaErrorInvalidValue;
+  launch_pdl(bn_small_fwd_kernel, dim3((C + SMALL_CH - 1) / SMALL_CH), dim3(SMALL_THREADS), 0, (cudaStream_t)cs, x, (int)M, C, partials,
+             nparts, gamma, beta, residual, relu, running_mean, running_var, momentum, eps, stats, y);
+  return (int)cudaGetLastError();
+}
+
+// Gradient sums + input gradient (+ residual gradient), one launch.
+int gc_cuda_bn_small_backward(const float* dy, const float* x, const float* y, int64_t M, int C, const float* stats, const float* gamma,
+                              const float* beta, int relu, float* sums, float* dx, float* dres, void* cs) {
+  if (!gc_cuda_bn_small_supported(M, C)) return (int)cudaErrorInvalidValue;
+  launch_pdl(bn_small_bwd_kernel, dim3((C + SMALL_CH - 1) / SMALL_CH), dim3(SMALL_THREADS), 0, (cudaStream_t)cs, dy, x, y, (int)M, C, stats,
+             gamma, beta, relu, sums, dx, dres);
   return (int)cudaGetLastError();
 }
 

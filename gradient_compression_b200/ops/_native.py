@@ -125,6 +125,9 @@ def cuda():
         _declare(lib, "gc_cuda_bn_bwd_fused_limit", None, [c_i64])
         _declare(lib, "gc_cuda_bn_bwd_apply", c_int, [P, P, P, c_i64, c_int, P, P, P, P, c_int, P, P, P])
         _declare(lib, "gc_cuda_bn_bwd_reduce_interleave", None, [c_int])
+        _declare(lib, "gc_cuda_bn_small_supported", c_int, [c_i64, c_int])
+        _declare(lib, "gc_cuda_bn_small_forward", c_int, [P, c_i64, c_int, P, c_int, P, P, P, c_int, P, P, c_float, c_float, P, P, P])
+        _declare(lib, "gc_cuda_bn_small_backward", c_int, [P, P, P, c_i64, c_int, P, P, P, c_int, P, P, P, P])
         _declare(lib, "gc_cuda_bn_pool_supported", c_int, [c_int] * 4)
         _declare(lib, "gc_cuda_bn_apply_pool", c_int, [P, c_int, c_int, c_int, c_int, P, P, P, c_int, P, P])
         _declare(lib, "gc_cuda_bn_bwd_reduce_pool", c_int, [P, P, c_int, c_int, c_int, c_int, P, P, P, c_int, P, P, P])

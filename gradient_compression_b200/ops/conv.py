@@ -52,6 +52,11 @@ FUSED_FINALIZE = os.environ.get("GCB200_BN_FUSED_FINALIZE", "0") == "1"
 
 # Which paths may be taken (for measurements): any subset of "gemm", "conv", "stem", "dgrad_s2" (own input gradient of
 # stride-2 convolutions; without it cuDNN computes those).
+# activations of at most 2048 rows (the 4x4 / 2x2 stages at batch 128): BN statistics + apply, and BN backward, in one launch each
+SMALL_BN = os.environ.get("GCB200_BN_SMALL", "1") == "1"
+# ... and at most this many values: measured on one B200, VGG-16 89.9 k img/s without, 90.7 k with a limit of 1 Mi, 91.1 k with
+# 256 Ki; ResNet-50 17.22 k / 17.19 k / 17.22 k (its 2048-row x 2048-channel maps are better streamed row by row)
+SMALL_BN_ELEMENTS = int(os.environ.get("GCB200_BN_SMALL_ELEMENTS", str(1 << 18)))
 # stride-1 input gradients read the forward filter in place (MN-major B operand) instead of a rotated / transposed copy
 DGRAD_IN_PLACE = os.environ.get("GCB200_DGRAD_IN_PLACE", "1") == "1"
 PATHS = set(os.environ.get("GCB200_TC_CONV_PATHS", "gemm,conv,stem,dgrad_s2").split(","))
@@ -362,31 +367,43 @@ class _ConvBNAct(torch.autograd.Function):
                 nat.check(lib.gc_cuda_im2col_small(x.data_ptr(), gathered.data_ptr(), n, h, wd, cin, r, pad, STEM_K,
                                                    w.data_ptr(), wpad.data_ptr(), cout, st()), "im2col_small")
                 gemm.gemm_tf32(gathered, wpad, bias=cbias, out=_as_2d(yconv), col_partials=partials, bn_fin=fin)
-            if partials is not None:
-                nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), partials.shape[0], m, cout, stats.data_ptr(),
-                                                           nat.ptr(running_mean), nat.ptr(running_var), float(momentum),
-                                                           float(eps), st()), "bn_finalize_partials")
-            elif training and fin is None:
-                # the convolution ran as a split contraction (few output tiles, long filters): its statistics take a pass
-                # of their own over the small output
-                nat.check(lib.gc_cuda_bn_stats(yconv.data_ptr(), m, cout, _scratch_for(x.device, cout).data_ptr(), stats.data_ptr(),
-                                               nat.ptr(running_mean), nat.ptr(running_var), float(momentum), float(eps), st()),
-                          "bn_stats")
-                nat.count_launch()
-            elif not training:
-                stats[:cout] = running_mean
-                stats[cout:] = torch.rsqrt(running_var + eps)
             res = _cl(residual) if residual is not None else None
-            if pool:
-                # act = relu(bn(yconv)) is never written: only its 2x2 max-pooled map is
-                assert res is None
-                out = torch.empty((n, cout, ho // 2, wo // 2), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
-                nat.check(lib.gc_cuda_bn_apply_pool(yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(), gamma.data_ptr(),
-                                                    beta.data_ptr(), int(relu), out.data_ptr(), st()), "bn_apply_pool")
-            else:
+            small = (SMALL_BN and training and fin is None and not pool and m * cout <= SMALL_BN_ELEMENTS
+                     and lib.gc_cuda_bn_small_supported(m, cout))
+            if small:
+                # a few hundred kilobytes of activation: statistics (from the convolution's partial sums, or from yconv after a
+                # split contraction), running-statistics update and apply in ONE launch instead of two or three
                 out = torch.empty_like(yconv)
-                nat.check(lib.gc_cuda_bn_apply(yconv.data_ptr(), m, cout, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
-                                               nat.ptr(res), int(relu), out.data_ptr(), st()), "bn_apply")
+                nat.check(lib.gc_cuda_bn_small_forward(yconv.data_ptr(), m, cout, nat.ptr(partials),
+                                                       partials.shape[0] if partials is not None else 0, gamma.data_ptr(),
+                                                       beta.data_ptr(), nat.ptr(res), int(relu), nat.ptr(running_mean),
+                                                       nat.ptr(running_var), float(momentum), float(eps), stats.data_ptr(),
+                                                       out.data_ptr(), st()), "bn_small_forward")
+            else:
+                if partials is not None:
+                    nat.check(lib.gc_cuda_bn_finalize_partials(partials.data_ptr(), partials.shape[0], m, cout, stats.data_ptr(),
+                                                               nat.ptr(running_mean), nat.ptr(running_var), float(momentum),
+                                                               float(eps), st()), "bn_finalize_partials")
+                elif training and fin is None:
+                    # the convolution ran as a split contraction (few output tiles, long filters): its statistics take a pass
+                    # of their own over the small output
+                    nat.check(lib.gc_cuda_bn_stats(yconv.data_ptr(), m, cout, _scratch_for(x.device, cout).data_ptr(), stats.data_ptr(),
+                                                   nat.ptr(running_mean), nat.ptr(running_var), float(momentum), float(eps), st()),
+                              "bn_stats")
+                    nat.count_launch()
+                elif not training:
+                    stats[:cout] = running_mean
+                    stats[cout:] = torch.rsqrt(running_var + eps)
+                if pool:
+                    # act = relu(bn(yconv)) is never written: only its 2x2 max-pooled map is
+                    assert res is None
+                    out = torch.empty((n, cout, ho // 2, wo // 2), dtype=torch.float32, device=x.device, memory_format=torch.channels_last)
+                    nat.check(lib.gc_cuda_bn_apply_pool(yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(), gamma.data_ptr(),
+                                                        beta.data_ptr(), int(relu), out.data_ptr(), st()), "bn_apply_pool")
+                else:
+                    out = torch.empty_like(yconv)
+                    nat.check(lib.gc_cuda_bn_apply(yconv.data_ptr(), m, cout, stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                                   nat.ptr(res), int(relu), out.data_ptr(), st()), "bn_apply")
         ctx.relu, ctx.has_res, ctx.has_cbias = bool(relu), residual is not None, cbias is not None
         ctx.save_for_backward(x, w, yconv, gamma, beta, stats, out if (residual is not None and relu) else None, gathered)
         return out
@@ -414,6 +431,11 @@ class _ConvBNAct(torch.autograd.Function):
                 nat.check(lib.gc_cuda_bn_bwd_apply_pool(dy.data_ptr(), yconv.data_ptr(), n, ho, wo, cout, stats.data_ptr(),
                                                         gamma.data_ptr(), beta.data_ptr(), sums.data_ptr(), int(ctx.relu),
                                                         dconv.data_ptr(), st()), "bn_bwd_apply_pool")
+            elif SMALL_BN and m * cout <= SMALL_BN_ELEMENTS and lib.gc_cuda_bn_small_supported(m, cout):
+                # small activation: the two gradient sums and the input gradient in one launch (a block owns its channels)
+                nat.check(lib.gc_cuda_bn_small_backward(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
+                                                        gamma.data_ptr(), beta.data_ptr(), int(ctx.relu), sums.data_ptr(),
+                                                        dconv.data_ptr(), nat.ptr(dres), st()), "bn_small_backward")
             else:
                 nat.check(lib.gc_cuda_bn_bwd_reduce(dy.data_ptr(), yconv.data_ptr(), nat.ptr(out), m, cout, stats.data_ptr(),
                                                     gamma.data_ptr(), beta.data_ptr(), int(ctx.relu),

@@ -289,6 +289,65 @@ def test_projection_block_hands_its_input_gradient_to_the_first_convolution(tc_c
         assert float((a - b).norm() / b.norm()) < 1e-5
 
 
+@pytest.mark.parametrize("m,c", [(2048, 512), (777, 140), (128, 2048), (32, 64), (1, 8)])
+@pytest.mark.parametrize("relu", [False, True])
+@pytest.mark.parametrize("residual", [False, True])
+@pytest.mark.parametrize("from_partials", [False, True])
+def test_small_activation_kernels_match_float64(m, c, relu, residual, from_partials):
+    """Statistics + running-statistics update + apply in one launch, and both gradient sums + input gradient (+ residual
+    gradient) in one launch, for activations of at most 2048 rows, against torch in float64."""
+    from gradient_compression_b200.ops import _native as nat
+
+    lib, st = nat.cuda(), nat.stream_ptr
+    assert lib.gc_cuda_bn_small_supported(m, c)
+    g = torch.Generator().manual_seed(m + c)
+    x = (torch.randn(m, c, generator=g) * 1.7 + 3.0).cuda()
+    res = torch.randn(m, c, generator=g).cuda() if residual else None
+    gamma, beta = (torch.rand(c, generator=g) + 0.5).cuda(), torch.randn(c, generator=g).cuda()
+    rm, rv = torch.zeros(c, device="cuda"), torch.ones(c, device="cuda")
+    stats, y = torch.empty(2 * c, device="cuda"), torch.empty(m, c, device="cuda")
+    partials = None
+    if from_partials:          # what a convolution kernel's epilogue emits: per 128-row tile, column sums and sums of squares
+        tiles = (m + 127) // 128
+        partials = torch.zeros(tiles, 2, c, device="cuda")
+        for t in range(tiles):
+            blk = x[t * 128:(t + 1) * 128].double()
+            partials[t, 0], partials[t, 1] = blk.sum(0).float(), (blk * blk).sum(0).float()
+    nat.check(lib.gc_cuda_bn_small_forward(x.data_ptr(), m, c, nat.ptr(partials), 0 if partials is None else partials.shape[0],
+                                           gamma.data_ptr(), beta.data_ptr(), nat.ptr(res), int(relu), rm.data_ptr(), rv.data_ptr(), 0.1,
+                                           1e-5, stats.data_ptr(), y.data_ptr(), st()), "small_fwd")
+    xd = x.double().requires_grad_(True)
+    rd = res.double().requires_grad_(True) if residual else None
+    rm_r, rv_r = torch.zeros(c, dtype=torch.float64, device="cuda"), torch.ones(c, dtype=torch.float64, device="cuda")
+    gd, bd = gamma.double().requires_grad_(True), beta.double().requires_grad_(True)
+    if m > 1:
+        yr = F.batch_norm(xd, rm_r, rv_r, gd, bd, True, 0.1, 1e-5)
+    else:                      # torch refuses a single value per channel in training mode; the kernel's definition: var = 0
+        yr = (xd - xd) * gd / (1e-5 ** 0.5) + bd
+    if residual:
+        yr = yr + rd
+    if relu:
+        yr = F.relu(yr)
+    tol = 2e-3 if from_partials else 2e-4        # unshifted fp32 sums of squares around a mean of 3 lose a few digits
+    assert torch.allclose(y.double(), yr, rtol=tol, atol=tol)
+    if m > 1:
+        assert torch.allclose(rm.double(), rm_r, rtol=1e-4, atol=1e-5) and torch.allclose(rv.double(), rv_r, rtol=tol, atol=1e-5)
+    dy = torch.randn(m, c, generator=g).cuda()
+    sums, dx = torch.empty(2 * c, device="cuda"), torch.empty(m, c, device="cuda")
+    dres = torch.empty(m, c, device="cuda") if residual else None
+    nat.check(lib.gc_cuda_bn_small_backward(dy.data_ptr(), x.data_ptr(), y.data_ptr() if (residual and relu) else None, m, c,
+                                            stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), int(relu), sums.data_ptr(),
+                                            dx.data_ptr(), nat.ptr(dres), st()), "small_bwd")
+    if m > 1 and not from_partials:
+        yr.backward(dy.double())
+        scale = float(xd.grad.abs().max()) + 1e-6
+        assert float((dx.double() - xd.grad).abs().max()) <= 2e-3 * scale + 1e-5
+        assert torch.allclose(sums[:c].double(), bd.grad, rtol=1e-3, atol=1e-3)
+        assert torch.allclose(sums[c:].double(), gd.grad, rtol=2e-3, atol=2e-3)
+        if residual:
+            assert float((dres.double() - rd.grad).abs().max()) <= 1e-5
+
+
 @pytest.mark.parametrize("name", ["ResNet18", "VGG11"])
 def test_batch_counters_follow_the_fused_loss_path(name):
     """``forward_loss`` (the path the trainer and the graphed step take) does not go through ``__call__``: the deferred
